@@ -1,0 +1,19 @@
+from .attn_decode import AttnDecodeOp
+from .base_op import Op
+from .fused_o_proj_ffn import FusedOProjFfnOp
+from .fused_qk_norm_rope import FusedQkNormRopeOp
+from .gemv import GemvOp
+from .qwen3_dense_decode import Qwen3DenseDecodeOp
+from .rmsnorm import RmsNormOp
+from .utils.roofline import RooflineResult
+
+__all__ = [
+    "AttnDecodeOp",
+    "FusedOProjFfnOp",
+    "FusedQkNormRopeOp",
+    "GemvOp",
+    "Op",
+    "Qwen3DenseDecodeOp",
+    "RmsNormOp",
+    "RooflineResult",
+]

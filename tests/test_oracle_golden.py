@@ -1,0 +1,114 @@
+"""Pin the CPU oracle against outputs of the reference's own ``_ref_forward``
+methods (fixtures made by tests/golden/make_golden.py).  Element-wise paths
+must match bit for bit; paths through a bf16 matmul or SDPA may differ between
+CPU generations by summation order, so they are held to one bf16 ulp on
+(almost) every element and 1e-3 relative Frobenius error."""
+
+import torch
+
+from helpers import frac_within_one_ulp, load_golden, rel_fro
+from oracle import ezops_oracle as orc
+
+
+def _close(actual, expected):
+    assert actual.shape == expected.shape and actual.dtype == expected.dtype
+    assert rel_fro(actual, expected) < 1e-3
+    assert frac_within_one_ulp(actual, expected) > 0.995
+
+
+def test_gemv_matches_reference():
+    g = load_golden("gemv")
+    _close(orc.gemv_ref(g["x"], g["W"]), g["y"])
+    # bf16 output vs the fp32 accumulator: rounding only
+    assert rel_fro(orc.gemv_ref(g["x"], g["W"]), orc.gemv_fp32(g["x"], g["W"])) < 4e-3
+
+
+def test_rmsnorm_f32_matches_reference_exactly():
+    g = load_golden("rmsnorm_f32")
+    out = orc.rmsnorm_f32_ref(g["X"], g["eps"])
+    assert torch.allclose(out, g["Out"], atol=1e-6, rtol=1e-6)
+
+
+def test_qk_norm_rope_matches_reference():
+    for tag in "ab":
+        g = load_golden(f"qk_norm_rope_{tag}")
+        Kc, Vc = g["K0"].clone(), g["V0"].clone()
+        q_out, k_out = orc.qk_norm_rope_ref(g["q"], g["k"], g["v"], g["qw"], g["kw"], g["cos"], g["sin"], Kc, Vc, g["position"])
+        _close(q_out, g["q_out"])
+        _close(k_out, g["k_out"])
+        assert torch.equal(Vc, g["V1"])  # raw v copy and untouched slots: exact
+        _close(Kc, g["K1"])
+        mask = torch.ones(Kc.shape[2], dtype=torch.bool)
+        mask[g["position"]] = False
+        assert torch.equal(Kc[:, :, mask], g["K0"][:, :, mask])
+
+
+def test_qk_norm_rope_per_row_positions_equal_scalar_calls():
+    g = load_golden("qk_norm_rope_a")
+    B = g["q"].shape[0]
+    positions = [3, 30]
+    Kc, Vc = g["K0"].clone(), g["V0"].clone()
+    q_out, k_out = orc.qk_norm_rope_ref(g["q"], g["k"], g["v"], g["qw"], g["kw"], g["cos"], g["sin"], Kc, Vc, positions)
+    for b in range(B):
+        Kb, Vb = g["K0"][b : b + 1].clone(), g["V0"][b : b + 1].clone()
+        qb, kb = orc.qk_norm_rope_ref(g["q"][b : b + 1], g["k"][b : b + 1], g["v"][b : b + 1], g["qw"], g["kw"],
+                                      g["cos"], g["sin"], Kb, Vb, positions[b])
+        assert torch.equal(qb[0], q_out[b]) and torch.equal(kb[0], k_out[b])
+        assert torch.equal(Kb[0], Kc[b]) and torch.equal(Vb[0], Vc[b])
+
+
+def test_attn_decode_matches_reference_and_fp64():
+    g = load_golden("attn_decode")
+    out = orc.attn_decode_ref(g["Q"], g["K"], g["V"])
+    _close(out, g["out"])
+    assert rel_fro(out, orc.attn_decode_fp64(g["Q"], g["K"], g["V"])) < 5e-3
+    lens = [5, 77]
+    ragged = orc.attn_decode_ref(g["Q"], g["K"], g["V"], lens)
+    assert rel_fro(ragged, orc.attn_decode_fp64(g["Q"], g["K"], g["V"], lens)) < 5e-3
+    assert torch.equal(ragged[1], out[1])  # full-length row is unchanged by the extension
+
+
+def test_o_proj_ffn_matches_reference():
+    for tag in "ab":
+        g = load_golden(f"o_proj_ffn_{tag}")
+        args = [g[k] for k in ("attn", "residual", "Wo", "post_norm_w", "Wg", "Wu", "Wd")]
+        out = orc.o_proj_ffn_ref(*args)
+        _close(out, g["out"])
+        assert rel_fro(out, orc.o_proj_ffn_fp64(*args)) < 1e-2
+
+
+def test_decode_layer_matches_reference():
+    for tag in "ab":
+        g = load_golden(f"decode_layer_{tag}")
+        Kc, Vc = g["K0"].clone(), g["V0"].clone()
+        heads = (g["num_heads"], g["num_kv_heads"], g["head_dim"])
+        args = (g["Wqkv"], g["Wo"], g["Wgu"], g["Wd"], *heads)
+        out = orc.qwen3_dense_decode_ref(g["hidden"], Kc, Vc, *args, sdpa_math=True)  # the reference's CPU selection
+        _close(out, g["out"])
+        # free SDPA backend (fp32 softmax, as the reference has on a GPU): same function, other rounding
+        free = orc.qwen3_dense_decode_ref(g["hidden"], g["K0"].clone(), g["V0"].clone(), *args)
+        assert rel_fro(free, g["out"]) < 1e-2
+        _close(Kc, g["K1"])
+        _close(Vc, g["V1"])
+        assert torch.equal(Kc[:, :, :-1], g["K0"][:, :, :-1]) and torch.equal(Vc[:, :, :-1], g["V0"][:, :, :-1])
+        f64 = orc.qwen3_dense_decode_fp64(g["hidden"], g["K0"], g["V0"], g["Wqkv"], g["Wo"], g["Wgu"], g["Wd"], *heads)
+        assert rel_fro(out, f64) < 1e-2
+
+
+def test_tp_shards_reassemble_the_layer_in_fp64():
+    """Sum over ranks of the row-parallel partial products equals the unsharded
+    projection: the algebra the tensor-parallel path relies on."""
+    g = load_golden("decode_layer_a")
+    NH, NKV, D = g["num_heads"], g["num_kv_heads"], g["head_dim"]
+    tp = 2
+    attn = torch.randn(2, NH * D, dtype=torch.float64)
+    h = torch.randn(2, g["Wd"].shape[1], dtype=torch.float64)
+    full_o = attn @ g["Wo"].double().T
+    full_d = h @ g["Wd"].double().T
+    acc_o, acc_d = torch.zeros_like(full_o), torch.zeros_like(full_d)
+    ql, il = NH * D // tp, g["Wd"].shape[1] // tp
+    for r in range(tp):
+        _, Wo_r, _, Wd_r = orc.shard_layer_weights(g["Wqkv"], g["Wo"], g["Wgu"], g["Wd"], NH, NKV, D, tp, r)
+        acc_o += attn[:, r * ql : (r + 1) * ql] @ Wo_r.double().T
+        acc_d += h[:, r * il : (r + 1) * il] @ Wd_r.double().T
+    assert torch.allclose(acc_o, full_o, atol=1e-9) and torch.allclose(acc_d, full_d, atol=1e-9)
