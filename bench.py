@@ -1,0 +1,422 @@
+#!/usr/bin/env python
+"""Headline benchmark: one Qwen3-8B dense decode layer per step (batch 1, KV
+length 4096, bf16), tensor-parallel over N GPUs of one node.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One JSON line on rank 0.  ``value`` is the achieved HBM bandwidth of the whole
+job: algorithmic bytes of one layer step (every weight and every valid KV row
+once; the same total at every N, so scaling is "strong") divided by the device
+time of a step, timed with CUDA events over exactly K steps replayed from a CUDA
+graph, max over ranks.  Steps rotate over four independent sets of layer weights
+and KV caches (1.6 GB), so no step finds its inputs in L2.
+
+Further legs, all outside the timed region of ``value``:
+  e2e          the same layer through the operator API with the step's input in
+               pinned host memory: H2D of hidden, the op call, D2H of the output,
+               stream sync, every step (weights and KV cache are resident state).
+  roofline     the dominant kernel (the weight-streaming GEMV, 4 of the 5
+               launches and 96 % of the bytes) timed alone on a gate/up-sized
+               weight, against the measured HBM copy peak.
+  cpu_baseline the CPU oracle (torch on the host cores) on the same layer.
+``--impl reference`` times that CPU path as its own arm.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+import torch  # noqa: E402
+
+NUM_WEIGHT_SETS = 4
+METRIC = "qwen3_8b_decode_layer_achieved_hbm_gbs"
+UNIT = "GB/s"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=None)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--model", choices=["qwen3-8b", "qwen3-32b"], default="qwen3-8b")
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--seq-len", type=int, default=4096)
+    ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a CUDA graph")
+    ap.add_argument("--skip-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--skip-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return json.loads(path.read_text()), "measured"
+        except Exception:
+            pass
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+# ----------------------------------------------------------------- clocks ---
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while the
+    timed region runs (read-only queries)."""
+
+    BAD = {
+        0x0000000000000008: "hw_slowdown",
+        0x0000000000000040: "hw_thermal_slowdown",
+        0x0000000000000020: "sw_thermal_slowdown",
+    }
+    NOTED = {0x0000000000000004: "sw_power_cap"}
+
+    def __init__(self, index: int, period_s: float = 0.004):
+        self.index, self.period = index, period_s
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._nvml = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = index
+            if visible:
+                ids = [v.strip() for v in visible.split(",") if v.strip()]
+                if index < len(ids) and ids[index].isdigit():
+                    phys = int(ids[index])
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM)
+            self._nvml = pynvml
+        except Exception:
+            self._nvml = None
+
+    def _run(self):
+        nv = self._nvml
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._handle, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._handle)
+                for bit, name in {**self.BAD, **self.NOTED}.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def __enter__(self):
+        if self._nvml is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=1.0)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+# ------------------------------------------------------------- CPU oracle ---
+def cpu_layer_arm(shape, batch, seq_len, budget_s=15.0, max_calls=50, min_calls=3):
+    """Times the CPU oracle of the layer on the host cores with every thread the
+    process may use.  Returns (seconds per call, calls, threads)."""
+    from ezops_b200 import workloads as wl
+    from oracle import ezops_oracle as orc
+
+    cores = len(os.sched_getaffinity(0))
+    torch.set_num_threads(cores)
+    data = wl.decode_layer_inputs(shape, batch, seq_len)
+    heads = (shape.num_heads, shape.num_kv_heads, shape.head_dim)
+    orc.qwen3_dense_decode_ref(*data, *heads)  # warm-up
+    times = []
+    t_start = time.perf_counter()
+    while len(times) < max_calls and (len(times) < min_calls or time.perf_counter() - t_start < budget_s):
+        t0 = time.perf_counter()
+        orc.qwen3_dense_decode_ref(*data, *heads)
+        times.append(time.perf_counter() - t0)
+    times.sort()
+    return times[len(times) // 2], len(times), torch.get_num_threads()
+
+
+def run_reference_arm(args, shape, total_bytes):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from ezops_b200 import workloads as wl
+    from oracle import ezops_oracle as orc
+
+    steps = args.steps if args.steps is not None else 20
+    warmup = args.warmup if args.warmup is not None else 3
+    cores = len(os.sched_getaffinity(0))
+    torch.set_num_threads(cores)
+    data = wl.decode_layer_inputs(shape, args.batch, args.seq_len)
+    heads = (shape.num_heads, shape.num_kv_heads, shape.head_dim)
+    for _ in range(warmup):
+        orc.qwen3_dense_decode_ref(*data, *heads)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        orc.qwen3_dense_decode_ref(*data, *heads)
+    dt = (time.perf_counter() - t0) / steps
+    value = total_bytes / dt / 1e9
+    line = {
+        "impl": "reference",
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
+        "ms_per_step": dt * 1e3, "us_per_layer": dt * 1e6, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded torch.randn, N(0,0.02) weights)",
+        "config": workload_config(args, shape, args.gpus),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": f"{steps} full layer steps of the CPU oracle (the reference's torch _ref_forward restated)"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, shape, n):
+    return {
+        "workload": f"{shape.name} dense decode layer, batch {args.batch}, kv_len {args.seq_len}, bf16, tp{n}",
+        "hidden": shape.hidden, "intermediate": shape.inter, "heads": f"{shape.num_heads}q/{shape.num_kv_heads}kv x {shape.head_dim}",
+        "parallelism": f"tp{n}",
+        "cache_policy": f"inputs larger than L2: steps rotate over {NUM_WEIGHT_SETS} weight+KV sets",
+    }
+
+
+# ------------------------------------------------------------------- main ---
+def main():
+    args = parse_args()
+    from ezops_b200 import workloads as wl
+
+    shape = wl.QWEN3_8B if args.model == "qwen3-8b" else wl.QWEN3_32B
+    total_bytes = shape.algorithmic_bytes(args.batch, args.seq_len)
+
+    if args.impl == "reference":
+        run_reference_arm(args, shape, total_bytes)
+        return
+
+    import torch.distributed as dist
+
+    import ezops_b200 as ez
+    from ezops_b200 import _lib
+    from ezops_b200 import tp as tpm
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run --nproc-per-node N")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+    tp = world
+    steps = args.steps if args.steps is not None else 1000
+    warmup = max(3, args.warmup if args.warmup is not None else 20)
+    B, S, H, I = args.batch, args.seq_len, shape.hidden, shape.inter
+    NH, NKV, D = shape.num_heads, shape.num_kv_heads, shape.head_dim
+
+    # ---- resident state: NUM_WEIGHT_SETS layers' weights and KV caches ----
+    gen = torch.Generator(device=device)
+    sets = []
+    for i in range(NUM_WEIGHT_SETS):
+        gen.manual_seed(1000 + i)  # same seed on every rank: consistent shards
+        rn = lambda *s, std=1.0: (torch.randn(*s, generator=gen, device=device, dtype=torch.float32) * std).to(torch.bfloat16)
+        Wqkv, Wo = rn(shape.q_rows + 2 * shape.kv_rows, H, std=0.02), rn(H, shape.q_rows, std=0.02)
+        Wgu, Wd = rn(2 * I, H, std=0.02), rn(H, I, std=0.02)
+        Kc, Vc = rn(B, NKV, S, D), rn(B, NKV, S, D)
+        if tp > 1:
+            Wqkv, Wo, Wgu, Wd = tpm.shard_layer_weights(Wqkv, Wo, Wgu, Wd, NH, NKV, D, tp, rank)
+            Kc, Vc = tpm.shard_kv_cache(Kc, tp, rank), tpm.shard_kv_cache(Vc, tp, rank)
+        sets.append((Kc, Vc, Wqkv, Wo, Wgu, Wd))
+        torch.cuda.empty_cache()
+    gen.manual_seed(7)
+    hidden0 = torch.randn(B, H, generator=gen, device=device, dtype=torch.float32).to(torch.bfloat16)
+
+    if tp == 1:
+        op = ez.Qwen3DenseDecodeOp(B, S, H, I, NH, D, backend="cuda", num_kv_heads=NKV)
+        kernel = op._kernel
+        launches_per_step = 5
+
+        def layer(hidden, wset, out):
+            return kernel(hidden, *wset, out=out)
+    else:
+        lay = tpm.TensorParallelDecodeLayer(B, S, H, I, NH, D, NKV)
+        launches_per_step = 6
+
+        def layer(hidden, wset, out):
+            return lay(hidden, *wset, out=out)
+
+    # quick self-check of one step against the torch reference on this GPU (tp=1)
+    check = None
+    if tp == 1:
+        ref_op = ez.Qwen3DenseDecodeOp(B, S, H, I, NH, D, backend="ref", num_kv_heads=NKV)
+        Kc, Vc = sets[0][0].clone(), sets[0][1].clone()
+        ref = ref_op._ref_forward(hidden0, Kc, Vc, *sets[0][2:])
+        got = layer(hidden0, (sets[0][0].clone(), sets[0][1].clone()) + sets[0][2:], torch.empty_like(hidden0))
+        check = bool(op.check(got, ref))
+
+    bufs = [torch.empty_like(hidden0) for _ in range(2)]
+
+    def run_steps(n, first=0):
+        h = hidden0
+        for i in range(n):
+            out = bufs[(first + i) & 1]
+            layer(h, sets[(first + i) % NUM_WEIGHT_SETS], out)
+            h = out
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    run_steps(warmup)
+    sync_all()
+
+    unroll = 1
+    graph = None
+    if not args.no_graph:
+        unroll = max(d for d in range(1, 65) if steps % d == 0)
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                run_steps(unroll)
+            graph.replay()  # untimed: first replay pays graph upload
+            sync_all()
+        except Exception as exc:  # pragma: no cover - depends on the runtime
+            print(f"[bench] CUDA graph capture failed ({type(exc).__name__}: {exc}); timing eager launches", file=sys.stderr)
+            graph, unroll = None, 1
+            torch.cuda.synchronize()
+
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    with ClockSampler(local_rank) as clocks:
+        t0.record()
+        if graph is not None:
+            for _ in range(steps // unroll):
+                graph.replay()
+        else:
+            run_steps(steps)
+        t1.record()
+        sync_all()
+    elapsed_ms = torch.tensor([t0.elapsed_time(t1)], device=device)
+    if world > 1:
+        dist.all_reduce(elapsed_ms, op=dist.ReduceOp.MAX)
+    elapsed_ms = elapsed_ms.item()
+    ms_per_step = elapsed_ms / steps
+    value = total_bytes / (ms_per_step * 1e-3) / 1e9
+    status = _lib.device_status()
+
+    # ---- e2e: operator API, step input in pinned host memory ----
+    e2e = None
+    if not args.skip_e2e:
+        n_e2e = min(steps, 300)
+        host_in = torch.empty(B, H, dtype=torch.bfloat16).pin_memory()
+        host_in.copy_(hidden0.cpu())
+        host_out = torch.empty(B, H, dtype=torch.bfloat16).pin_memory()
+        dev_in, dev_out = torch.empty_like(hidden0), torch.empty_like(hidden0)
+        stream = torch.cuda.current_stream()
+
+        def e2e_step(i):
+            dev_in.copy_(host_in, non_blocking=True)
+            layer(dev_in, sets[i % NUM_WEIGHT_SETS], dev_out)
+            host_out.copy_(dev_out, non_blocking=True)
+            stream.synchronize()
+
+        for i in range(10):
+            e2e_step(i)
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(n_e2e):
+            e2e_step(i)
+        e1.record()
+        sync_all()
+        e_ms = torch.tensor([e0.elapsed_time(e1)], device=device)
+        if world > 1:
+            dist.all_reduce(e_ms, op=dist.ReduceOp.MAX)
+        e_step = e_ms.item() / n_e2e
+        e2e = {"value": total_bytes / (e_step * 1e-3) / 1e9, "unit": UNIT, "us_per_step": e_step * 1e3, "steps": n_e2e,
+               "h2d_bytes_per_step": B * H * 2, "d2h_bytes_per_step": B * H * 2,
+               "note": "weights and KV cache are resident device state; per-step input/output cross PCIe"}
+
+    # ---- roofline of the dominant kernel, timed alone (rank 0's shard) ----
+    peaks, peak_kind = measured_peaks()
+    lib = _lib.load()
+    n_roof = 200
+    rows_local = sets[0][4].shape[0]
+    Y = torch.empty(B, rows_local, dtype=torch.bfloat16, device=device)
+    ws = torch.zeros(256, dtype=torch.uint8, device=device)
+    X = hidden0
+
+    def roof_launch(i):
+        W = sets[i % NUM_WEIGHT_SETS][4]
+        _lib.check(lib.ezb_gemv_batched_bf16(X.data_ptr(), W.data_ptr(), Y.data_ptr(), ws.data_ptr(), ws.numel(), B,
+                                             rows_local, H, torch.cuda.current_stream().cuda_stream))
+
+    for i in range(8):
+        roof_launch(i)
+    torch.cuda.synchronize()
+    r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    r0.record()
+    for i in range(n_roof):
+        roof_launch(i)
+    r1.record()
+    torch.cuda.synchronize()
+    launch_s = r0.elapsed_time(r1) * 1e-3 / n_roof
+    kernel_bytes = 2 * (rows_local * H + B * H + B * rows_local)
+    achieved = kernel_bytes / launch_s / 1e9
+    roofline = {
+        "bound": "hbm", "kernel": "gemv_stream_kernel", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+        "frac": achieved / peaks["hbm_gbs"], "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs, burst copy)",
+        "traffic": None, "bytes_per_launch": kernel_bytes, "us_per_launch": launch_s * 1e6,
+        "workload": f"W [{rows_local}, {H}] bf16 (gate/up-sized), batch {B}, {n_roof} back-to-back launches over {NUM_WEIGHT_SETS} weights",
+    }
+
+    # ---- CPU oracle beside it (rank 0, single-GPU run only) ----
+    cpu = None
+    if rank == 0 and world == 1 and not args.skip_cpu:
+        sec, calls, threads = cpu_layer_arm(shape, B, S)
+        cpu = {"value": total_bytes / sec / 1e9, "unit": UNIT, "cores": threads, "kind": "port", "us_per_layer": sec * 1e6,
+               "sample": f"median of {calls} full layer steps of the CPU oracle (torch, bf16 staging of the reference)"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": ms_per_step, "us_per_layer": ms_per_step * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (seeded torch.randn on device: N(0,1) activations/KV, N(0,0.02) weights)",
+            "config": workload_config(args, shape, world),
+            "algorithmic_bytes_per_step": total_bytes,
+            "frac_of_8tbs": value / 8000.0, "frac_of_measured_hbm": value / peaks["hbm_gbs"],
+            "timing": f"CUDA events around {steps} steps " + (f"replayed from a CUDA graph of {unroll} steps" if graph is not None else "launched eagerly") + ", max over ranks",
+            "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": steps * launches_per_step,
+            "roofline": roofline, "cpu_baseline": cpu, "check_vs_torch_ref": check, "device_status": status,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,485 @@
+// The C ABI of the library (declared in include/ezb200.h): argument checks,
+// workspace carving and the kernel chains of the fused operators.
+#include <atomic>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+#include "launchers.h"
+
+namespace ezb {
+
+__device__ unsigned int g_status_word = 0;
+
+static thread_local char t_message[256] = "";
+
+void set_last_message(const char* msg) {
+    std::snprintf(t_message, sizeof(t_message), "%s", msg ? msg : "");
+}
+void set_last_cuda_error(cudaError_t e) {
+    std::snprintf(t_message, sizeof(t_message), "CUDA error %d: %s", (int)e, cudaGetErrorString(e));
+}
+
+static constexpr int kMaxDevices = 64;
+
+static int current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
+    return dev;
+}
+
+int sm_count() {
+    static std::atomic<int> cache[kMaxDevices];
+    const int dev = current_device();
+    int v = cache[dev].load();
+    if (v == 0) {
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+        cache[dev].store(v);
+    }
+    return v;
+}
+
+int max_smem_optin() {
+    static std::atomic<int> cache[kMaxDevices];
+    const int dev = current_device();
+    int v = cache[dev].load();
+    if (v == 0) {
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess || v <= 0) v = 232448;
+        cache[dev].store(v);
+    }
+    return v;
+}
+
+unsigned int* status_ptr() {
+    static std::atomic<unsigned int*> cache[kMaxDevices];
+    const int dev = current_device();
+    unsigned int* p = cache[dev].load();
+    if (!p) {
+        void* addr = nullptr;
+        if (cudaGetSymbolAddress(&addr, g_status_word) != cudaSuccess) return nullptr;
+        p = static_cast<unsigned int*>(addr);
+        cache[dev].store(p);
+    }
+    return p;
+}
+
+static std::atomic<int> g_tuning[EZB_TUNE_COUNT];
+static std::atomic<bool> g_tuning_ready{false};
+static const int kTuningDefaults[EZB_TUNE_COUNT] = {
+    1,    // EZB_TUNE_PDL
+    100,  // EZB_TUNE_GEMV_SMEM_KB
+    0,    // EZB_TUNE_GEMV_PREFETCH (all stages)
+    1,    // EZB_TUNE_GEMV_CTAS_PER_SM
+    256,  // EZB_TUNE_ATTN_MIN_CHUNK
+    16,   // EZB_TUNE_ATTN_WAVES
+    0,    // EZB_TUNE_GEMV_KC (automatic)
+};
+static const char* kTuningEnv[EZB_TUNE_COUNT] = {
+    "EZB_TUNE_PDL",          "EZB_TUNE_GEMV_SMEM_KB",   "EZB_TUNE_GEMV_PREFETCH", "EZB_TUNE_GEMV_CTAS_PER_SM",
+    "EZB_TUNE_ATTN_MIN_CHUNK", "EZB_TUNE_ATTN_WAVES", "EZB_TUNE_GEMV_KC",
+};
+
+static void tuning_init() {
+    if (g_tuning_ready.load()) return;
+    for (int i = 0; i < EZB_TUNE_COUNT; ++i) {
+        int v = kTuningDefaults[i];
+        if (const char* e = std::getenv(kTuningEnv[i])) v = std::atoi(e);
+        g_tuning[i].store(v);
+    }
+    g_tuning_ready.store(true);
+}
+
+int tuning(int key) {
+    tuning_init();
+    return (key >= 0 && key < EZB_TUNE_COUNT) ? g_tuning[key].load() : 0;
+}
+
+static size_t round256(size_t v) { return (v + 255) / 256 * 256; }
+
+// Carves the layer workspace.  The attention part comes first because it holds
+// the counters that must start at zero.
+struct LayerWorkspace {
+    void* attn;
+    bf16 *qkv, *attn_out, *x2, *h, *xn;
+    size_t total;
+};
+
+static LayerWorkspace carve_layer_ws(void* base, int B, int S, int H, int I, int NH, int NKV, int D) {
+    LayerWorkspace w;
+    unsigned char* p = static_cast<unsigned char*>(base);
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        unsigned char* r = p ? p + off : nullptr;
+        off += round256(bytes);
+        return r;
+    };
+    w.attn = take(attn_workspace_bytes(B, NH, NKV, S, D));
+    w.qkv = reinterpret_cast<bf16*>(take((size_t)B * (NH + 2 * NKV) * D * 2));
+    w.attn_out = reinterpret_cast<bf16*>(take((size_t)B * NH * D * 2));
+    w.x2 = reinterpret_cast<bf16*>(take((size_t)B * H * 2));
+    w.h = reinterpret_cast<bf16*>(take((size_t)B * I * 2));
+    w.xn = reinterpret_cast<bf16*>(take((size_t)B * H * 2));
+    w.total = off;
+    return w;
+}
+
+struct FfnWorkspace {
+    bf16 *x2, *h, *xn;
+    size_t total;
+};
+
+static FfnWorkspace carve_ffn_ws(void* base, int B, int H, int I) {
+    FfnWorkspace w;
+    unsigned char* p = static_cast<unsigned char*>(base);
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        unsigned char* r = p ? p + off : nullptr;
+        off += round256(bytes);
+        return r;
+    };
+    w.x2 = reinterpret_cast<bf16*>(take((size_t)B * H * 2));
+    w.h = reinterpret_cast<bf16*>(take((size_t)B * I * 2));
+    w.xn = reinterpret_cast<bf16*>(take((size_t)B * H * 2));
+    w.total = off;
+    return w;
+}
+
+static int check_common_layer_dims(int B, int H, int I, int Q) {
+    EZB_REQUIRE(B >= 1 && H >= 1 && I >= 1 && Q >= 1, "sizes must be positive");
+    EZB_REQUIRE_SHAPE(B <= 64, "batch above 64 is not supported");
+    EZB_REQUIRE_SHAPE(H % 16 == 0, "hidden_size must be divisible by 16");
+    EZB_REQUIRE_SHAPE(I % 16 == 0, "intermediate_size must be divisible by 16");
+    EZB_REQUIRE_SHAPE(Q % 16 == 0, "num_heads * head_dim must be divisible by 16");
+    return EZB_OK;
+}
+
+// o_proj (+residual or fp32 partial), gate/up + SwiGLU, down (+residual or fp32 partial)
+static cudaError_t launch_o_proj(const bf16* attn, const bf16* Wo, int B, int H, int Q, const bf16* residual, void* out,
+                                 bool f32_partial, cudaStream_t stream) {
+    GemvArgs g;
+    g.W0 = Wo, g.ldw = Q, g.N = H, g.K = Q, g.B = B;
+    g.x = attn, g.ldx = Q;
+    g.prologue = PRO_NONE;
+    g.epilogue = f32_partial ? EPI_STORE_F32 : EPI_RESIDUAL;
+    g.residual = residual, g.ldres = H;
+    g.out = out, g.ldout = H;
+    return launch_gemv(g, stream);
+}
+
+static cudaError_t launch_gate_up(const bf16* x, const float* x_add, bf16* x_sum_out, const bf16* norm_w, const bf16* Wg,
+                                  const bf16* Wu, int B, int H, int I, float eps, bf16* h, bf16* xn_scratch,
+                                  cudaStream_t stream) {
+    GemvArgs g;
+    g.W0 = Wg, g.W1 = Wu, g.ldw = H, g.N = I, g.K = H, g.B = B;
+    g.x = x, g.ldx = H;
+    g.x_add = x_add, g.ldadd = H, g.x_sum_out = x_sum_out, g.ldsum = H;
+    g.norm_w = norm_w, g.eps = eps;
+    g.prologue = x_add ? PRO_ADD_RMSNORM : PRO_RMSNORM;
+    g.epilogue = EPI_SWIGLU;
+    g.out = h, g.ldout = I;
+    g.xn_scratch = xn_scratch;
+    return launch_gemv(g, stream);
+}
+
+static cudaError_t launch_down(const bf16* h, const bf16* Wd, int B, int H, int I, const bf16* residual, void* out,
+                               bool f32_partial, cudaStream_t stream) {
+    GemvArgs g;
+    g.W0 = Wd, g.ldw = I, g.N = H, g.K = I, g.B = B;
+    g.x = h, g.ldx = I;
+    g.prologue = PRO_NONE;
+    g.epilogue = f32_partial ? EPI_STORE_F32 : EPI_RESIDUAL;
+    g.residual = residual, g.ldres = H;
+    g.out = out, g.ldout = H;
+    return launch_gemv(g, stream);
+}
+
+static cudaError_t launch_qkv_and_attention(const bf16* hidden, bf16* Kc, bf16* Vc, const bf16* Wqkv, const LayerWorkspace& w,
+                                            int B, int S, int H, int NH, int NKV, int D, float eps, cudaStream_t stream) {
+    const int rows = (NH + 2 * NKV) * D;
+    GemvArgs g;
+    g.W0 = Wqkv, g.ldw = H, g.N = rows, g.K = H, g.B = B;
+    g.x = hidden, g.ldx = H;
+    g.eps = eps, g.prologue = PRO_RMSNORM, g.epilogue = EPI_STORE;
+    g.out = w.qkv, g.ldout = rows;
+    g.xn_scratch = w.xn;
+    cudaError_t e = launch_gemv(g, stream);
+    if (e != cudaSuccess) return e;
+
+    AttnArgs a;
+    a.K = Kc, a.V = Vc;
+    a.Out = w.attn_out, a.o_bstride = (long long)NH * D;
+    a.B = B, a.H = NH, a.NKV = NKV, a.S = S, a.D = D;
+    a.workspace = w.attn;
+    a.fuse_new_token = 1;
+    a.qkv = w.qkv, a.qkv_bstride = rows;
+    a.K_cache_w = Kc, a.V_cache_w = Vc;
+    a.eps = eps;
+    return launch_attn_decode(a, stream);
+}
+
+static int check_layer_args(int B, int S, int H, int I, int NH, int NKV, int D) {
+    EZB_REQUIRE(S >= 1 && NH >= 1 && NKV >= 1, "sizes must be positive");
+    EZB_REQUIRE_SHAPE(D == 64 || D == 128, "head_dim must be 64 or 128");
+    EZB_REQUIRE_SHAPE(NH % NKV == 0, "num_heads must be divisible by num_kv_heads");
+    EZB_REQUIRE_SHAPE(NH / NKV <= 16, "more than 16 query heads per kv head is not supported in the fused layer");
+    return check_common_layer_dims(B, H, I, NH * D);
+}
+
+}  // namespace ezb
+
+using namespace ezb;
+
+extern "C" {
+
+int ezb_version(void) { return 100; }
+
+const char* ezb_strerror(int code) {
+    switch (code) {
+        case EZB_OK: return "ok";
+        case EZB_ERR_INVALID_ARGUMENT: return "invalid argument";
+        case EZB_ERR_UNSUPPORTED_SHAPE: return "unsupported shape";
+        case EZB_ERR_CUDA: return "CUDA runtime error";
+        case EZB_ERR_WORKSPACE: return "workspace missing or too small";
+        case EZB_ERR_DEVICE_FAULT: return "a kernel recorded a device-side fault";
+        default: return "unknown error code";
+    }
+}
+
+const char* ezb_last_error_message(void) { return t_message; }
+
+int ezb_set_tuning(int key, int value) {
+    tuning_init();
+    EZB_REQUIRE(key >= 0 && key < EZB_TUNE_COUNT, "unknown tuning key");
+    g_tuning[key].store(value);
+    return EZB_OK;
+}
+
+int ezb_get_tuning(int key) { return tuning(key); }
+
+int ezb_device_status(unsigned int* status_out_host, int clear) {
+    EZB_REQUIRE(status_out_host != nullptr, "status_out_host is null");
+    EZB_CUDA_TRY(cudaDeviceSynchronize());
+    EZB_CUDA_TRY(cudaMemcpyFromSymbol(status_out_host, g_status_word, sizeof(unsigned int)));
+    if (clear && *status_out_host != 0) {
+        const unsigned int zero = 0;
+        EZB_CUDA_TRY(cudaMemcpyToSymbol(g_status_word, &zero, sizeof(unsigned int)));
+    }
+    return *status_out_host == 0 ? EZB_OK : EZB_ERR_DEVICE_FAULT;
+}
+
+int ezb_gemv_bf16(const void* x, const void* W, void* y, int N, int K, ezb_stream_t stream) {
+    EZB_REQUIRE(x && W && y, "null pointer");
+    EZB_REQUIRE(N >= 1 && K >= 1, "N and K must be positive");
+    EZB_REQUIRE_SHAPE(K % 16 == 0, "K must be divisible by 16");
+    EZB_REQUIRE(aligned16(x) && aligned16(W), "x and W must be 16-byte aligned");
+    GemvArgs g;
+    g.W0 = static_cast<const bf16*>(W), g.ldw = K, g.N = N, g.K = K, g.B = 1;
+    g.x = static_cast<const bf16*>(x), g.ldx = K;
+    g.out = y, g.ldout = N;
+    EZB_CUDA_TRY(launch_gemv(g, stream));
+    return EZB_OK;
+}
+
+size_t ezb_gemv_workspace_bytes(int B, int K) {
+    (void)B, (void)K;
+    return 256;  // no prologue runs in this entry point, so no scratch rows are needed
+}
+
+int ezb_gemv_batched_bf16(const void* X, const void* W, void* Y, void* workspace, size_t workspace_bytes, int B, int N, int K,
+                          ezb_stream_t stream) {
+    (void)workspace, (void)workspace_bytes;
+    EZB_REQUIRE(X && W && Y, "null pointer");
+    EZB_REQUIRE(N >= 1 && K >= 1 && B >= 1, "B, N and K must be positive");
+    EZB_REQUIRE_SHAPE(B <= 64, "batch above 64 is not supported");
+    EZB_REQUIRE_SHAPE(K % 16 == 0, "K must be divisible by 16");
+    EZB_REQUIRE(aligned16(X) && aligned16(W), "X and W must be 16-byte aligned");
+    GemvArgs g;
+    g.W0 = static_cast<const bf16*>(W), g.ldw = K, g.N = N, g.K = K, g.B = B;
+    g.x = static_cast<const bf16*>(X), g.ldx = K;
+    g.out = Y, g.ldout = N;
+    EZB_CUDA_TRY(launch_gemv(g, stream));
+    return EZB_OK;
+}
+
+int ezb_rmsnorm_f32(const float* X, float* Out, int rows, int dim, float eps, ezb_stream_t stream) {
+    EZB_REQUIRE(X && Out, "null pointer");
+    EZB_REQUIRE(rows >= 1 && dim >= 1, "rows and dim must be positive");
+    EZB_REQUIRE(aligned16(X) && aligned16(Out), "X and Out must be 16-byte aligned");
+    EZB_CUDA_TRY(launch_rmsnorm_f32(X, Out, rows, dim, eps, stream));
+    return EZB_OK;
+}
+
+int ezb_rmsnorm_bf16(const void* X, const void* w_or_null, void* Out, int rows, int dim, float eps, ezb_stream_t stream) {
+    EZB_REQUIRE(X && Out, "null pointer");
+    EZB_REQUIRE(rows >= 1 && dim >= 1, "rows and dim must be positive");
+    EZB_REQUIRE_SHAPE(dim % 8 == 0, "dim must be divisible by 8");
+    EZB_REQUIRE(aligned16(X) && aligned16(Out) && aligned16(w_or_null), "pointers must be 16-byte aligned");
+    RowPrepArgs a;
+    a.x = static_cast<const bf16*>(X), a.ldx = dim;
+    a.w = static_cast<const bf16*>(w_or_null);
+    a.y = static_cast<bf16*>(Out), a.ldy = dim;
+    a.rows = rows, a.dim = dim, a.eps = eps, a.normalize = 1;
+    EZB_CUDA_TRY(launch_row_prep(a, stream));
+    return EZB_OK;
+}
+
+int ezb_qk_norm_rope(const void* q, const void* k, const void* v, const void* qw, const void* kw, const void* cos,
+                     const void* sin, void* K_cache, void* V_cache, void* q_out, void* k_out, int B, int NQ, int NKV,
+                     int D, int S, int position, const int* positions_or_null, float eps, ezb_stream_t stream) {
+    EZB_REQUIRE(q && k && v && qw && kw && cos && sin && K_cache && V_cache && q_out && k_out, "null pointer");
+    EZB_REQUIRE(B >= 1 && NQ >= 1 && NKV >= 1 && S >= 1, "sizes must be positive");
+    EZB_REQUIRE_SHAPE(D >= 8 && D <= 512 && (D & (D - 1)) == 0, "head_dim must be a power of two in [8, 512]");
+    EZB_REQUIRE_SHAPE(NQ % NKV == 0, "num_heads must be divisible by num_kv_heads");
+    EZB_REQUIRE(positions_or_null || (position >= 0 && position < S), "position must be in [0, max_seq_len)");
+    RopeArgs a;
+    a.q = static_cast<const bf16*>(q), a.k = static_cast<const bf16*>(k), a.v = static_cast<const bf16*>(v);
+    a.qw = static_cast<const bf16*>(qw), a.kw = static_cast<const bf16*>(kw);
+    a.cos = static_cast<const bf16*>(cos), a.sin = static_cast<const bf16*>(sin);
+    a.K_cache = static_cast<bf16*>(K_cache), a.V_cache = static_cast<bf16*>(V_cache);
+    a.q_out = static_cast<bf16*>(q_out), a.k_out = static_cast<bf16*>(k_out);
+    a.B = B, a.NQ = NQ, a.NKV = NKV, a.D = D, a.S = S, a.position = position;
+    a.positions = positions_or_null, a.eps = eps;
+    EZB_CUDA_TRY(launch_qk_norm_rope(a, stream));
+    return EZB_OK;
+}
+
+size_t ezb_attn_decode_workspace_bytes(int B, int H, int NKV, int S, int D) {
+    if (B < 1 || H < 1 || NKV < 1 || S < 1 || D < 1 || H % NKV) return 0;
+    return attn_workspace_bytes(B, H, NKV, S, D);
+}
+
+int ezb_attn_decode(const void* Q, const void* K, const void* V, void* Out, void* workspace, size_t workspace_bytes, int B,
+                    int H, int NKV, int S, int D, const int* seq_lens_or_null, ezb_stream_t stream) {
+    EZB_REQUIRE(Q && K && V && Out, "null pointer");
+    EZB_REQUIRE(B >= 1 && H >= 1 && NKV >= 1 && S >= 1, "sizes must be positive");
+    EZB_REQUIRE_SHAPE(D == 64 || D == 128, "head_dim must be 64 or 128");
+    EZB_REQUIRE_SHAPE(H % NKV == 0, "num_heads must be divisible by num_kv_heads");
+    EZB_REQUIRE_SHAPE(B <= 65535 && NKV <= 65535, "batch and kv heads are limited to 65535");
+    EZB_REQUIRE(aligned16(Q) && aligned16(K) && aligned16(V), "Q, K and V must be 16-byte aligned");
+    if (!workspace || workspace_bytes < attn_workspace_bytes(B, H, NKV, S, D)) {
+        set_last_message("attention workspace missing or smaller than ezb_attn_decode_workspace_bytes()");
+        return EZB_ERR_WORKSPACE;
+    }
+    AttnArgs a;
+    a.Q = static_cast<const bf16*>(Q), a.q_bstride = (long long)H * D;
+    a.K = static_cast<const bf16*>(K), a.V = static_cast<const bf16*>(V);
+    a.Out = static_cast<bf16*>(Out), a.o_bstride = (long long)H * D;
+    a.seq_lens = seq_lens_or_null;
+    a.B = B, a.H = H, a.NKV = NKV, a.S = S, a.D = D;
+    a.workspace = workspace;
+    EZB_CUDA_TRY(launch_attn_decode(a, stream));
+    return EZB_OK;
+}
+
+size_t ezb_o_proj_ffn_workspace_bytes(int B, int H, int I, int Q) {
+    if (B < 1 || H < 1 || I < 1 || Q < 1) return 0;
+    return carve_ffn_ws(nullptr, B, H, I).total;
+}
+
+int ezb_o_proj_ffn(const void* attn, const void* residual, const void* Wo, const void* post_norm_w, const void* Wg,
+                   const void* Wu, const void* Wd, void* out, void* workspace, size_t workspace_bytes, int B, int H, int I,
+                   int Q, float eps, ezb_stream_t stream) {
+    EZB_REQUIRE(attn && residual && Wo && post_norm_w && Wg && Wu && Wd && out, "null pointer");
+    if (int rc = check_common_layer_dims(B, H, I, Q)) return rc;
+    EZB_REQUIRE(aligned16(attn) && aligned16(residual) && aligned16(Wo) && aligned16(post_norm_w) && aligned16(Wg) &&
+                    aligned16(Wu) && aligned16(Wd) && aligned16(out),
+                "pointers must be 16-byte aligned");
+    FfnWorkspace w = carve_ffn_ws(workspace, B, H, I);
+    if (!workspace || workspace_bytes < w.total) {
+        set_last_message("workspace missing or smaller than ezb_o_proj_ffn_workspace_bytes()");
+        return EZB_ERR_WORKSPACE;
+    }
+    EZB_CUDA_TRY(launch_o_proj(static_cast<const bf16*>(attn), static_cast<const bf16*>(Wo), B, H, Q,
+                               static_cast<const bf16*>(residual), w.x2, false, stream));
+    EZB_CUDA_TRY(launch_gate_up(w.x2, nullptr, nullptr, static_cast<const bf16*>(post_norm_w), static_cast<const bf16*>(Wg),
+                                static_cast<const bf16*>(Wu), B, H, I, eps, w.h, w.xn, stream));
+    EZB_CUDA_TRY(launch_down(w.h, static_cast<const bf16*>(Wd), B, H, I, w.x2, out, false, stream));
+    return EZB_OK;
+}
+
+size_t ezb_qwen3_decode_layer_workspace_bytes(int B, int S, int H, int I, int NH, int NKV, int D) {
+    if (B < 1 || S < 1 || H < 1 || I < 1 || NH < 1 || NKV < 1 || D < 1 || NH % NKV) return 0;
+    return carve_layer_ws(nullptr, B, S, H, I, NH, NKV, D).total;
+}
+
+int ezb_qwen3_decode_layer(const void* hidden, void* K_cache, void* V_cache, const void* Wqkv, const void* Wo,
+                           const void* Wgu, const void* Wd, void* out, void* workspace, size_t workspace_bytes, int B,
+                           int S, int H, int I, int NH, int NKV, int D, float eps, ezb_stream_t stream) {
+    EZB_REQUIRE(hidden && K_cache && V_cache && Wqkv && Wo && Wgu && Wd && out, "null pointer");
+    if (int rc = check_layer_args(B, S, H, I, NH, NKV, D)) return rc;
+    EZB_REQUIRE(aligned16(hidden) && aligned16(K_cache) && aligned16(V_cache) && aligned16(Wqkv) && aligned16(Wo) &&
+                    aligned16(Wgu) && aligned16(Wd) && aligned16(out),
+                "pointers must be 16-byte aligned");
+    LayerWorkspace w = carve_layer_ws(workspace, B, S, H, I, NH, NKV, D);
+    if (!workspace || workspace_bytes < w.total) {
+        set_last_message("workspace missing or smaller than ezb_qwen3_decode_layer_workspace_bytes()");
+        return EZB_ERR_WORKSPACE;
+    }
+    const bf16* hid = static_cast<const bf16*>(hidden);
+    const bf16* wgu = static_cast<const bf16*>(Wgu);
+    EZB_CUDA_TRY(launch_qkv_and_attention(hid, static_cast<bf16*>(K_cache), static_cast<bf16*>(V_cache),
+                                          static_cast<const bf16*>(Wqkv), w, B, S, H, NH, NKV, D, eps, stream));
+    EZB_CUDA_TRY(launch_o_proj(w.attn_out, static_cast<const bf16*>(Wo), B, H, NH * D, hid, w.x2, false, stream));
+    EZB_CUDA_TRY(launch_gate_up(w.x2, nullptr, nullptr, nullptr, wgu, wgu + (size_t)I * H, B, H, I, eps, w.h, w.xn, stream));
+    EZB_CUDA_TRY(launch_down(w.h, static_cast<const bf16*>(Wd), B, H, I, w.x2, out, false, stream));
+    return EZB_OK;
+}
+
+int ezb_qwen3_decode_layer_tp_attn(const void* hidden, void* K_cache, void* V_cache, const void* Wqkv_local,
+                                   const void* Wo_local, float* partial_o, void* workspace, size_t workspace_bytes, int B,
+                                   int S, int H, int NH_local, int NKV_local, int D, float eps, ezb_stream_t stream) {
+    EZB_REQUIRE(hidden && K_cache && V_cache && Wqkv_local && Wo_local && partial_o, "null pointer");
+    if (int rc = check_layer_args(B, S, H, 16, NH_local, NKV_local, D)) return rc;
+    EZB_REQUIRE(aligned16(hidden) && aligned16(K_cache) && aligned16(V_cache) && aligned16(Wqkv_local) &&
+                    aligned16(Wo_local) && aligned16(partial_o),
+                "pointers must be 16-byte aligned");
+    // the caller sized the workspace for its own I; only the attention part and the
+    // activation rows in front of h are used here, which do not depend on I
+    LayerWorkspace w = carve_layer_ws(workspace, B, S, H, 16, NH_local, NKV_local, D);
+    if (!workspace || workspace_bytes < w.total) {
+        set_last_message("workspace missing or smaller than ezb_qwen3_decode_layer_workspace_bytes()");
+        return EZB_ERR_WORKSPACE;
+    }
+    EZB_CUDA_TRY(launch_qkv_and_attention(static_cast<const bf16*>(hidden), static_cast<bf16*>(K_cache),
+                                          static_cast<bf16*>(V_cache), static_cast<const bf16*>(Wqkv_local), w, B, S, H,
+                                          NH_local, NKV_local, D, eps, stream));
+    EZB_CUDA_TRY(launch_o_proj(w.attn_out, static_cast<const bf16*>(Wo_local), B, H, NH_local * D, nullptr, partial_o, true,
+                               stream));
+    return EZB_OK;
+}
+
+int ezb_qwen3_decode_layer_tp_ffn(const void* hidden, const float* summed_o, const void* Wgu_local, const void* Wd_local,
+                                  void* x2, float* partial_d, void* workspace, size_t workspace_bytes, int B, int H,
+                                  int I_local, float eps, ezb_stream_t stream) {
+    EZB_REQUIRE(hidden && summed_o && Wgu_local && Wd_local && x2 && partial_d, "null pointer");
+    if (int rc = check_common_layer_dims(B, H, I_local, 16)) return rc;
+    EZB_REQUIRE(aligned16(hidden) && aligned16(summed_o) && aligned16(Wgu_local) && aligned16(Wd_local) && aligned16(x2) &&
+                    aligned16(partial_d),
+                "pointers must be 16-byte aligned");
+    FfnWorkspace w = carve_ffn_ws(workspace, B, H, I_local);
+    if (!workspace || workspace_bytes < w.total) {
+        set_last_message("workspace missing or smaller than ezb_o_proj_ffn_workspace_bytes()");
+        return EZB_ERR_WORKSPACE;
+    }
+    const bf16* wgu = static_cast<const bf16*>(Wgu_local);
+    EZB_CUDA_TRY(launch_gate_up(static_cast<const bf16*>(hidden), summed_o, static_cast<bf16*>(x2), nullptr, wgu,
+                                wgu + (size_t)I_local * H, B, H, I_local, eps, w.h, w.xn, stream));
+    EZB_CUDA_TRY(launch_down(w.h, static_cast<const bf16*>(Wd_local), B, H, I_local, nullptr, partial_d, true, stream));
+    return EZB_OK;
+}
+
+int ezb_residual_add_f32(const void* x2, const float* summed_d, void* out, int B, int H, ezb_stream_t stream) {
+    EZB_REQUIRE(x2 && summed_d && out, "null pointer");
+    EZB_REQUIRE(B >= 1 && H >= 1, "sizes must be positive");
+    EZB_REQUIRE_SHAPE(H % 8 == 0, "hidden_size must be divisible by 8");
+    EZB_REQUIRE(aligned16(x2) && aligned16(summed_d) && aligned16(out), "pointers must be 16-byte aligned");
+    RowPrepArgs a;
+    a.x = static_cast<const bf16*>(x2), a.ldx = H;
+    a.add = summed_d, a.ldadd = H;
+    a.sum_out = static_cast<bf16*>(out), a.ldsum = H;
+    a.rows = B, a.dim = H, a.normalize = 0;
+    EZB_CUDA_TRY(launch_row_prep(a, stream));
+    return EZB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,399 @@
+// Single-query (decode) attention with grouped queries, split over the KV length.
+//
+// Work item = (batch row, kv head, KV split); one CTA of four warps each.  The
+// CTA streams its keys and values once, 64 keys per tile, through a 3-deep ring
+// of shared-memory stages filled with 16-byte cp.async copies (zero-filled past
+// the row's valid length, XOR-swizzled so that ldmatrix is conflict free).  The
+// G query heads that share the kv head form the rows of a 16-row mma tile
+// (rows >= G are zero), so every K/V byte is used by all G heads while it is on
+// chip: S = Q K^T and O += P V both run on mma.sync m16n8k16 with fp32
+// accumulation, soft-max statistics in fp32 in the exp2 domain.  Each warp owns
+// 16 of the tile's 64 keys with its own running (max, sum, O); the four are
+// merged in shared memory at the end, the split's (max, sum, O) goes to the
+// workspace, and the CTA that finishes last for a (row, kv head) -- found with
+// one atomic counter, no waiting -- folds the splits together in index order
+// and writes the bf16 output.  No spin waits anywhere.
+//
+// Decode-layer mode (fuse_new_token): q, k, v of the token being decoded come
+// straight from the fused QKV projection output; q and k get their unit-weight
+// RMSNorm over the head here, and the CTA whose split holds cache slot S-1
+// writes the new k and v into the cache before it streams that slot.
+#include "launchers.h"
+
+namespace ezb {
+
+static constexpr int kAttnThreads = 128;
+static constexpr int kTileKeys = 64;
+static constexpr int kAttnStages = 3;
+
+struct AttnParams {
+    const bf16* Q;
+    long long q_bstride;
+    const bf16* K;
+    const bf16* V;
+    bf16* Out;
+    long long o_bstride;
+    const int* seq_lens;
+    int B, H, NKV, S, G;
+    int chunk, nchunks, nqt;
+    float scale_log2e;
+    float* part_o;   // [items][16][D]
+    float* part_ml;  // [items][16][2]
+    unsigned int* counters;
+    int fuse_new_token;
+    const bf16* qkv;
+    long long qkv_bstride;
+    int q_rows, kv_rows;
+    bf16* K_cache_w;
+    bf16* V_cache_w;
+    float eps;
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <int D>
+__global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const AttnParams p) {
+    constexpr int CPR = D / 8;                       // 16-byte chunks per key row
+    constexpr int ROW_BYTES = D * 2;
+    constexpr int TILE_BYTES = kTileKeys * ROW_BYTES;  // one K or V tile
+    constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+    constexpr int QS = D + 8;                        // padded query row, elements
+    extern __shared__ __align__(128) unsigned char smem[];
+    unsigned char* stages = smem;
+    bf16* q_s = reinterpret_cast<bf16*>(smem + kAttnStages * STAGE_BYTES);
+    __shared__ int s_is_last;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g4 = lane >> 2, t4 = lane & 3;
+    const int chunk_id = blockIdx.x % p.nchunks, qt = blockIdx.x / p.nchunks;
+    const int kvh = blockIdx.y, b = blockIdx.z;
+    const int G = p.G, g0 = qt * 16, gn = min(16, G - g0);
+    const long long kv_row0 = ((long long)b * p.NKV + kvh) * p.S;
+
+    pdl_trigger();
+    pdl_wait();
+
+    int len = p.S;
+    if (p.seq_lens) len = max(0, min(p.S, p.seq_lens[b]));
+    const int c0 = chunk_id * p.chunk;
+    const int c1 = min(len, c0 + p.chunk);
+    const int nkeys = max(0, c1 - c0);
+    const int ntiles = (nkeys + kTileKeys - 1) / kTileKeys;
+
+    // ---- queries of this kv group into shared memory (rows >= gn are zero) ----
+    {
+        const bf16* qsrc = p.fuse_new_token ? p.qkv : p.Q;
+        const long long qb = p.fuse_new_token ? p.qkv_bstride : p.q_bstride;
+        for (int idx = tid; idx < 16 * CPR; idx += kAttnThreads) {
+            const int row = idx / CPR, c = idx % CPR;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (row < gn) v = *reinterpret_cast<const uint4*>(qsrc + (long long)b * qb + (long long)(kvh * G + g0 + row) * D + c * 8);
+            *reinterpret_cast<uint4*>(q_s + row * QS + c * 8) = v;
+        }
+        __syncthreads();
+        if (p.fuse_new_token) {
+            // unit-weight RMSNorm over the head, fp32 statistics, one rounding
+            for (int row = warp; row < gn; row += 4) {
+                float x[D / 32];
+                float ssq = 0.f;
+#pragma unroll
+                for (int j = 0; j < D / 32; ++j) {
+                    x[j] = __bfloat162float(q_s[row * QS + lane + j * 32]);
+                    ssq += x[j] * x[j];
+                }
+                ssq = warp_sum(ssq);
+                const float r = 1.0f / sqrtf(ssq / (float)D + p.eps);
+#pragma unroll
+                for (int j = 0; j < D / 32; ++j) q_s[row * QS + lane + j * 32] = __float2bfloat16_rn(x[j] * r);
+            }
+            // new token's k (normalised) and v into cache slot S-1, by the CTA that will read it
+            if (qt == 0 && c0 <= p.S - 1 && p.S - 1 < c1) {
+                const long long slot = (kv_row0 + p.S - 1) * D;
+                if (warp == 0) {
+                    const bf16* ksrc = p.qkv + (long long)b * p.qkv_bstride + p.q_rows + kvh * D;
+                    float x[D / 32];
+                    float ssq = 0.f;
+#pragma unroll
+                    for (int j = 0; j < D / 32; ++j) {
+                        x[j] = __bfloat162float(ksrc[lane + j * 32]);
+                        ssq += x[j] * x[j];
+                    }
+                    ssq = warp_sum(ssq);
+                    const float r = 1.0f / sqrtf(ssq / (float)D + p.eps);
+#pragma unroll
+                    for (int j = 0; j < D / 32; ++j) p.K_cache_w[slot + lane + j * 32] = __float2bfloat16_rn(x[j] * r);
+                } else if (warp == 1) {
+                    const bf16* vsrc = p.qkv + (long long)b * p.qkv_bstride + p.q_rows + p.kv_rows + kvh * D;
+#pragma unroll
+                    for (int j = 0; j < D / 32; ++j) p.V_cache_w[slot + lane + j * 32] = vsrc[lane + j * 32];
+                }
+                __threadfence();
+            }
+            __syncthreads();
+        }
+    }
+
+    // ---- A fragments of Q: 16 rows x D, D/16 k-steps ----
+    uint32_t qa[D / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+        const bf16* base = q_s + kk * 16 + t4 * 2;
+        qa[kk][0] = *reinterpret_cast<const uint32_t*>(base + g4 * QS);
+        qa[kk][1] = *reinterpret_cast<const uint32_t*>(base + (g4 + 8) * QS);
+        qa[kk][2] = *reinterpret_cast<const uint32_t*>(base + g4 * QS + 8);
+        qa[kk][3] = *reinterpret_cast<const uint32_t*>(base + (g4 + 8) * QS + 8);
+    }
+
+    auto load_tile = [&](int t) {
+        unsigned char* st = stages + (t % kAttnStages) * STAGE_BYTES;
+        const int key0 = c0 + t * kTileKeys;
+#pragma unroll
+        for (int i = 0; i < (2 * kTileKeys * CPR) / kAttnThreads; ++i) {
+            const int idx = tid + i * kAttnThreads;
+            const int which = idx / (kTileKeys * CPR);
+            const int rem = idx % (kTileKeys * CPR);
+            const int r = rem / CPR, c = rem % CPR;
+            const int key = key0 + r;
+            const bool valid = key < c1;
+            const bf16* src = (which ? p.V : p.K) + (kv_row0 + (valid ? key : 0)) * D + c * 8;
+            const uint32_t dst = smem_u32(st) + which * TILE_BYTES + r * ROW_BYTES + ((c ^ (r & 7)) << 4);
+            cp_async16(dst, src, valid);
+        }
+    };
+
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY};
+    float l_run[2] = {0.f, 0.f};
+
+    for (int t = 0; t < kAttnStages - 1; ++t) {
+        if (t < ntiles) load_tile(t);
+        cp_async_commit();
+    }
+    for (int t = 0; t < ntiles; ++t) {
+        cp_async_wait<kAttnStages - 2>();
+        __syncthreads();
+        if (t + kAttnStages - 1 < ntiles) load_tile(t + kAttnStages - 1);
+        cp_async_commit();
+
+        const unsigned char* st = stages + (t % kAttnStages) * STAGE_BYTES;
+        const uint32_t k_s = smem_u32(st), v_s = k_s + TILE_BYTES;
+        const int kr0 = warp * 16;
+
+        // ---- S = Q K^T for this warp's 16 keys ----
+        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        {
+            const int mi = lane >> 3, rr = lane & 7;
+            const int key_local = kr0 + (mi >> 1) * 8 + rr;
+            const uint32_t row_addr = k_s + key_local * ROW_BYTES;
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+                const int chunk = kk * 2 + (mi & 1);
+                uint32_t b00, b01, b10, b11;
+                ldsm_x4(row_addr + ((chunk ^ (key_local & 7)) << 4), b00, b01, b10, b11);
+                mma_bf16_16816(s[0], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], b00, b01);
+                mma_bf16_16816(s[1], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], b10, b11);
+            }
+        }
+        // ---- online soft-max (exp2 domain) ----
+        const int key_base = c0 + t * kTileKeys + kr0 + t4 * 2;
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = key_base + j * 8 + (e & 1);
+                s[j][e] = (key < c1) ? s[j][e] * p.scale_log2e : -INFINITY;
+                mx[e >> 1] = fmaxf(mx[e >> 1], s[j][e]);
+            }
+        float alpha[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+            const float m_new = fmaxf(m_run[r], mx[r]);
+            const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
+            alpha[r] = fast_exp2(m_run[r] - m_safe);
+            m_run[r] = m_new;
+            float psum = 0.f;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                s[j][2 * r] = fast_exp2(s[j][2 * r] - m_safe);
+                s[j][2 * r + 1] = fast_exp2(s[j][2 * r + 1] - m_safe);
+                psum += s[j][2 * r] + s[j][2 * r + 1];
+            }
+            l_run[r] = l_run[r] * alpha[r] + psum;
+        }
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+            o[i][0] *= alpha[0], o[i][1] *= alpha[0];
+            o[i][2] *= alpha[1], o[i][3] *= alpha[1];
+        }
+        // ---- O += P V ----
+        const uint32_t pa0 = pack_bf16(s[0][0], s[0][1]), pa1 = pack_bf16(s[0][2], s[0][3]);
+        const uint32_t pa2 = pack_bf16(s[1][0], s[1][1]), pa3 = pack_bf16(s[1][2], s[1][3]);
+        {
+            const int mi = lane >> 3, rr = lane & 7;
+            const int key_local = kr0 + (mi & 1) * 8 + rr;
+            const uint32_t row_addr = v_s + key_local * ROW_BYTES;
+#pragma unroll
+            for (int dn = 0; dn < D / 16; ++dn) {
+                const int chunk = dn * 2 + (mi >> 1);
+                uint32_t v0, v1, v2, v3;
+                ldsm_x4_trans(row_addr + ((chunk ^ (key_local & 7)) << 4), v0, v1, v2, v3);
+                mma_bf16_16816(o[2 * dn], pa0, pa1, pa2, pa3, v0, v1);
+                mma_bf16_16816(o[2 * dn + 1], pa0, pa1, pa2, pa3, v2, v3);
+            }
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+
+    // ---- merge the four warps (each saw a quarter of the keys) ----
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    }
+    float* mrg_m = reinterpret_cast<float*>(smem);  // [4][16]
+    float* mrg_l = mrg_m + 64;                      // [4][16]
+    float* mrg_o = mrg_l + 64;                      // [4][16][D]
+    if (t4 == 0) {
+        mrg_m[warp * 16 + g4] = m_run[0], mrg_m[warp * 16 + g4 + 8] = m_run[1];
+        mrg_l[warp * 16 + g4] = l_run[0], mrg_l[warp * 16 + g4 + 8] = l_run[1];
+    }
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+        float* dst = mrg_o + (warp * 16 + g4) * D + i * 8 + t4 * 2;
+        *reinterpret_cast<float2*>(dst) = make_float2(o[i][0], o[i][1]);
+        *reinterpret_cast<float2*>(dst + 8 * D) = make_float2(o[i][2], o[i][3]);
+    }
+    __syncthreads();
+
+    const long long group = ((long long)b * p.NKV + kvh) * p.nqt + qt;
+    const long long item = group * p.nchunks + chunk_id;
+    for (int idx = tid; idx < gn * D; idx += kAttnThreads) {
+        const int row = idx / D, d = idx % D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, mrg_m[w * 16 + row]);
+        float O = 0.f, L = 0.f;
+        if (M != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float f = fast_exp2(mrg_m[w * 16 + row] - M);
+                O += f * mrg_o[(w * 16 + row) * D + d];
+                L += f * mrg_l[w * 16 + row];
+            }
+        }
+        if (p.nchunks == 1) {
+            const float val = (L > 0.f) ? O / L : 0.f;
+            p.Out[(long long)b * p.o_bstride + (long long)(kvh * G + g0 + row) * D + d] = __float2bfloat16_rn(val);
+        } else {
+            p.part_o[(item * 16 + row) * D + d] = O;
+            if (d == 0) {
+                p.part_ml[(item * 16 + row) * 2 + 0] = M;
+                p.part_ml[(item * 16 + row) * 2 + 1] = L;
+            }
+        }
+    }
+    if (p.nchunks == 1) return;
+
+    // ---- the last CTA of this (row, kv head, q tile) folds the splits together ----
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned int prev = atomicAdd(&p.counters[group], 1u);
+        s_is_last = (prev == (unsigned int)(p.nchunks - 1));
+    }
+    __syncthreads();
+    if (!s_is_last) return;
+    __threadfence();
+    for (int idx = tid; idx < gn * D; idx += kAttnThreads) {
+        const int row = idx / D, d = idx % D;
+        float M = -INFINITY;
+        for (int c = 0; c < p.nchunks; ++c) M = fmaxf(M, __ldcg(&p.part_ml[((group * p.nchunks + c) * 16 + row) * 2]));
+        float O = 0.f, L = 0.f;
+        if (M != -INFINITY) {
+            for (int c = 0; c < p.nchunks; ++c) {
+                const long long it = group * p.nchunks + c;
+                const float f = fast_exp2(__ldcg(&p.part_ml[(it * 16 + row) * 2]) - M);
+                L += f * __ldcg(&p.part_ml[(it * 16 + row) * 2 + 1]);
+                O += f * __ldcg(&p.part_o[(it * 16 + row) * D + d]);
+            }
+        }
+        const float val = (L > 0.f) ? O / L : 0.f;
+        p.Out[(long long)b * p.o_bstride + (long long)(kvh * G + g0 + row) * D + d] = __float2bfloat16_rn(val);
+    }
+    if (tid == 0) p.counters[group] = 0u;  // ready for the next call
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+int attn_chunk_keys(int B, int NKV, int S) {
+    const long long total = (long long)B * NKV * S;
+    const long long target = (long long)sm_count() * max(1, tuning(EZB_TUNE_ATTN_WAVES));
+    long long chunk = (total + target - 1) / target;
+    chunk = (chunk + kTileKeys - 1) / kTileKeys * kTileKeys;
+    long long floor_keys = max(kTileKeys, tuning(EZB_TUNE_ATTN_MIN_CHUNK) / kTileKeys * kTileKeys);
+    if (chunk < floor_keys) chunk = floor_keys;
+    const long long cap = ((long long)S + kTileKeys - 1) / kTileKeys * kTileKeys;
+    if (chunk > cap) chunk = cap;
+    return (int)chunk;
+}
+
+static size_t counters_bytes(int B, int NKV, int nqt) { return ((size_t)B * NKV * nqt * 4 + 255) / 256 * 256; }
+
+size_t attn_workspace_bytes(int B, int H, int NKV, int S, int D) {
+    const int G = H / NKV, nqt = (G + 15) / 16;
+    const int chunk = attn_chunk_keys(B, NKV, S);
+    const int nchunks = (S + chunk - 1) / chunk;
+    const size_t items = (size_t)B * NKV * nqt * nchunks;
+    return counters_bytes(B, NKV, nqt) + items * 16 * 2 * sizeof(float) + items * 16 * D * sizeof(float);
+}
+
+template <int D>
+static cudaError_t launch_attn_instance(const AttnParams& p, cudaStream_t stream) {
+    auto kernel = attn_decode_kernel<D>;
+    constexpr size_t smem = (size_t)kAttnStages * 2 * kTileKeys * D * 2 + 16 * (D + 8) * 2;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    return launch_pdl(kernel, dim3(p.nchunks * p.nqt, p.NKV, p.B), dim3(kAttnThreads), smem, stream, p);
+}
+
+cudaError_t launch_attn_decode(const AttnArgs& a, cudaStream_t stream) {
+    AttnParams p;
+    p.Q = a.Q, p.q_bstride = a.q_bstride, p.K = a.K, p.V = a.V, p.Out = a.Out, p.o_bstride = a.o_bstride;
+    p.seq_lens = a.seq_lens;
+    p.B = a.B, p.H = a.H, p.NKV = a.NKV, p.S = a.S, p.G = a.H / a.NKV;
+    p.nqt = (p.G + 15) / 16;
+    p.chunk = attn_chunk_keys(a.B, a.NKV, a.S);
+    p.nchunks = (a.S + p.chunk - 1) / p.chunk;
+    p.scale_log2e = 1.4426950408889634f / sqrtf((float)a.D);
+    unsigned char* ws = reinterpret_cast<unsigned char*>(a.workspace);
+    const size_t items = (size_t)a.B * a.NKV * p.nqt * p.nchunks;
+    p.counters = reinterpret_cast<unsigned int*>(ws);
+    p.part_ml = reinterpret_cast<float*>(ws + counters_bytes(a.B, a.NKV, p.nqt));
+    p.part_o = p.part_ml + items * 16 * 2;
+    p.fuse_new_token = a.fuse_new_token;
+    p.qkv = a.qkv, p.qkv_bstride = a.qkv_bstride;
+    p.q_rows = a.H * a.D, p.kv_rows = a.NKV * a.D;
+    p.K_cache_w = a.K_cache_w, p.V_cache_w = a.V_cache_w;
+    p.eps = a.eps;
+    if (a.D == 128) return launch_attn_instance<128>(p, stream);
+    return launch_attn_instance<64>(p, stream);
+}
+
+}  // namespace ezb

@@ -1,0 +1,237 @@
+// Shared device helpers for the sm_100a kernels of this library: PTX wrappers
+// (mbarrier, 1-D bulk TMA copies, cp.async, ldmatrix, mma, programmatic
+// dependent launch), bf16 packing, the bounded barrier wait and the device
+// status word.  Everything here is header-only and internal to csrc/.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/ezb200.h"
+
+namespace ezb {
+
+typedef __nv_bfloat16 bf16;
+
+// ---------------------------------------------------------------------------
+// Device status word.  A kernel that gives up on a wait stores a non-zero code
+// here (first writer wins) and finishes without touching its outputs further;
+// the host reads it with ezb_device_status().  The word is defined once (in
+// api.cu); kernels receive its device address in their parameter block.
+// ---------------------------------------------------------------------------
+
+enum DeviceFault : unsigned int {
+    FAULT_NONE = 0,
+    FAULT_GEMV_FULL_WAIT = 0x101,   // consumer never saw a weight stage arrive
+    FAULT_GEMV_EMPTY_WAIT = 0x102,  // producer never got a stage back
+    FAULT_GEMV_DRAIN = 0x103,       // copies still in flight at exit
+    FAULT_AR_FLAG_WAIT = 0x201,     // a peer's all-reduce flag never arrived
+};
+
+__device__ __forceinline__ void report_fault(unsigned int* status, unsigned int code) {
+    atomicCAS(status, 0u, code);
+}
+
+// About one second at B200 clocks; no legitimate wait in this library comes
+// within five orders of magnitude of it.
+static constexpr long long kWaitLimitCycles = 2000000000LL;
+
+// ---------------------------------------------------------------------------
+// Address helpers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// ---------------------------------------------------------------------------
+// mbarrier
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Wait for the phase with the given parity, for at most kWaitLimitCycles.
+// `abort_flag` lives in shared memory: once any thread of the CTA has given
+// up, every later wait in the CTA returns at once, so the control flow of all
+// warps (and the named barriers they meet at) stays the same and the CTA runs
+// to its end without hanging.  Returns false when it gave up.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                  unsigned int* status, unsigned int fault_code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    const long long t0 = clock64();
+    for (;;) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > kWaitLimitCycles) {
+            *abort_flag = 1;
+            report_fault(status, fault_code);
+            return false;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// 1-D bulk copy global -> shared through the TMA unit, completion counted in
+// bytes on an mbarrier.  Both addresses 16-byte aligned, size a multiple of 16.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
+        "l"(src), "r"(bytes), "r"(bar)
+        : "memory");
+}
+
+// ---------------------------------------------------------------------------
+// cp.async (16-byte, L2 only) with zero fill when `valid` is false
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src, bool valid) {
+    const int src_bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src), "r"(src_bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// ---------------------------------------------------------------------------
+// Programmatic dependent launch.  `pdl_wait` blocks until every kernel this
+// launch depends on has finished and its writes are visible; `pdl_trigger`
+// lets the next kernel in the stream begin its independent prologue.
+// Both are no-ops when the launch carries no programmatic dependency.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ---------------------------------------------------------------------------
+// Named barrier among a subset of warps
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// ---------------------------------------------------------------------------
+// ldmatrix / mma.sync m16n8k16 bf16 -> fp32
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// ---------------------------------------------------------------------------
+// bf16 helpers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) { return __uint_as_float(bits16 << 16); }
+__device__ __forceinline__ float bf16_lo(uint32_t packed) { return __uint_as_float(packed << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t packed) { return __uint_as_float(packed & 0xffff0000u); }
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// silu in fp32 as torch computes it for a bf16 tensor: x / (1 + exp(-x))
+__device__ __forceinline__ float silu_f32(float x) { return x / (1.0f + expf(-x)); }
+
+}  // namespace ezb
+
+// ---------------------------------------------------------------------------
+// Host-side helpers
+// ---------------------------------------------------------------------------
+#define EZB_CUDA_TRY(expr)                         \
+    do {                                           \
+        cudaError_t _e = (expr);                   \
+        if (_e != cudaSuccess) {                   \
+            ezb::set_last_cuda_error(_e);          \
+            return EZB_ERR_CUDA;                   \
+        }                                          \
+    } while (0)
+
+#define EZB_REQUIRE(cond, msg)                     \
+    do {                                           \
+        if (!(cond)) {                             \
+            ezb::set_last_message(msg);            \
+            return EZB_ERR_INVALID_ARGUMENT;       \
+        }                                          \
+    } while (0)
+
+#define EZB_REQUIRE_SHAPE(cond, msg)               \
+    do {                                           \
+        if (!(cond)) {                             \
+            ezb::set_last_message(msg);            \
+            return EZB_ERR_UNSUPPORTED_SHAPE;      \
+        }                                          \
+    } while (0)
+
+namespace ezb {
+void set_last_cuda_error(cudaError_t e);
+void set_last_message(const char* msg);
+int sm_count();               // SMs of the current device (cached per device)
+int max_smem_optin();         // opt-in shared memory per block of the current device
+int tuning(int key);          // value of a tuning knob (see EZB_TUNE_* in ezb200.h)
+unsigned int* status_ptr();   // device address of the status word on the current device (null on error)
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Launch with the programmatic-stream-serialization attribute, so that the
+// kernel may start while its predecessor in the stream drains; every kernel
+// launched this way calls pdl_wait() before it reads or writes anything the
+// predecessor touches.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                       Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = tuning(EZB_TUNE_PDL) ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+}  // namespace ezb

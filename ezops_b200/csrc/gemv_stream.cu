@@ -1,0 +1,450 @@
+// Weight-streaming GEMV / skinny GEMM for decode:  Y[b, n] = epi( sum_k X[b, k] * W[n, k] ),
+// 1 <= b <= 64, W bf16 row-major, fp32 accumulation.
+//
+// The kernel is bound by reading W from HBM exactly once, so it is built around
+// keeping many bytes in flight per SM with few instructions:
+//   * persistent grid, one CTA per SM; CTA c owns a contiguous range of output
+//     rows balanced to +-1 row, walked in blocks of 16 rows;
+//   * one producer warp streams [16 rows x kc] weight tiles into a ring of
+//     shared-memory stages with 1-D bulk TMA copies (one copy per row segment,
+//     rows padded by 16 bytes so that ldmatrix is bank-conflict free), completion
+//     counted on an mbarrier per stage; consumers hand stages back through a
+//     second mbarrier per stage;
+//   * four consumer warps split the k range of every stage between them and
+//     feed mma.sync m16n8k16 (weights as the 16-row A operand, activations as
+//     the 8-wide B operand, batch padded to a multiple of 8), then combine
+//     their partial tiles through shared memory in a fixed order, which keeps
+//     results bit-reproducible from call to call;
+//   * the activation block stays resident in shared memory when it fits (and
+//     can then be RMS-normalised in the prologue); otherwise its k-chunks ride
+//     along in every stage;
+//   * programmatic dependent launch: the first weight stages are requested
+//     before griddepcontrol.wait, because weights never depend on the kernel in
+//     front; only then are activations read.
+// Every mbarrier wait is bounded (see mbar_wait_bounded).
+#include "launchers.h"
+
+namespace ezb {
+
+static constexpr int kConsumerWarps = 4;
+static constexpr int kConsumerThreads = kConsumerWarps * 32;
+static constexpr int kGemvThreads = 32 + kConsumerThreads;
+static constexpr int kMaxStages = 8;
+static constexpr int kRowBlock = 16;
+static constexpr int kHeaderBytes = 256;  // barriers + abort flag
+
+struct GemvParams {
+    const bf16* W0;
+    const bf16* W1;
+    long long ldw;
+    int N, K, B;
+    const bf16* x;
+    long long ldx;
+    const float* x_add;
+    long long ldadd;
+    bf16* x_sum_out;
+    long long ldsum;
+    const bf16* norm_w;
+    float eps;
+    int prologue, epilogue;
+    const bf16* residual;
+    long long ldres;
+    void* out;
+    long long ldout;
+    int kc;        // k elements per stage (multiple of 16)
+    int nstages;   // ring depth
+    int prefetch;  // stages requested before the dependency wait
+    unsigned int* status;
+};
+
+__host__ __device__ constexpr size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+template <int NT, bool PAIR>
+__host__ __device__ constexpr size_t red_bytes() {
+    return (size_t)kConsumerWarps * (PAIR ? 2 : 1) * NT * 128 * sizeof(float);
+}
+
+// Rows of one stage: 16 (or 32 for gate/up pairs) weight rows, plus NT*8
+// activation rows when the activations are streamed.
+template <int NT, bool XRES, bool PAIR>
+__host__ __device__ constexpr int stage_rows() {
+    return kRowBlock * (PAIR ? 2 : 1) + (XRES ? 0 : NT * 8);
+}
+
+template <int NT, bool XRES, bool PAIR>
+__global__ void __launch_bounds__(kGemvThreads, 1) gemv_stream_kernel(const GemvParams p) {
+    constexpr int M = PAIR ? 2 : 1;
+    constexpr int WROWS = kRowBlock * M;
+    extern __shared__ __align__(128) unsigned char smem[];
+
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem);
+    uint64_t* empty_bar = full_bar + kMaxStages;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 2 * kMaxStages * 8);
+    float* red = reinterpret_cast<float*>(smem + kHeaderBytes);
+    bf16* xs = reinterpret_cast<bf16*>(smem + kHeaderBytes + red_bytes<NT, PAIR>());
+    const int xs_stride = p.K + 8;  // elements; (K+8)*2 bytes keeps rows 16-byte aligned and 4 banks apart
+    const size_t xs_bytes = XRES ? align_up((size_t)p.B * xs_stride * sizeof(bf16), 128) : 0;
+    unsigned char* stage_base = smem + kHeaderBytes + red_bytes<NT, PAIR>() + xs_bytes;
+    const int ws_stride = p.kc + 8;  // elements
+    const uint32_t stage_bytes = (uint32_t)align_up((size_t)stage_rows<NT, XRES, PAIR>() * ws_stride * sizeof(bf16), 128);
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31;
+    const int NS = p.nstages;
+
+    const int r0 = (int)((long long)p.N * blockIdx.x / gridDim.x);
+    const int r1 = (int)((long long)p.N * (blockIdx.x + 1) / gridDim.x);
+    const int nrb = (r1 - r0 + kRowBlock - 1) / kRowBlock;
+    const int nkc = (p.K + p.kc - 1) / p.kc;
+    const int total = nrb * nkc;
+
+    if (tid == 0) {
+        for (int s = 0; s < NS; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), kConsumerWarps);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    pdl_trigger();
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer
+        // Arms the stage's barrier with the byte count of everything that will
+        // land in it, then requests the weight rows (lanes 0..WROWS-1, one row
+        // segment each).
+        auto request_weights = [&](int it) {
+            const int rb = it / nkc, kci = it - rb * nkc, s = it % NS;
+            const int k0 = kci * p.kc;
+            const int len = min(p.kc, p.K - k0);
+            const int row0 = r0 + rb * kRowBlock;
+            const int nr = min(kRowBlock, r1 - row0);
+            const uint32_t bar = smem_u32(&full_bar[s]);
+            const uint32_t bytes = (uint32_t)((nr * M + (XRES ? 0 : p.B)) * len * (int)sizeof(bf16));
+            if (lane == 0) mbar_arrive_expect_tx(bar, bytes);
+            __syncwarp();
+            if (lane < WROWS) {
+                const int m = lane / kRowBlock, r = lane % kRowBlock;
+                if (r < nr) {
+                    const bf16* src = (m ? p.W1 : p.W0) + (long long)(row0 + r) * p.ldw + k0;
+                    const uint32_t dst = smem_u32(stage_base + (size_t)s * stage_bytes) +
+                                         (uint32_t)((m * kRowBlock + r) * ws_stride * (int)sizeof(bf16));
+                    bulk_g2s(dst, src, (uint32_t)(len * (int)sizeof(bf16)), bar);
+                }
+            }
+        };
+        auto request_activations = [&](int it) {
+            if (XRES) return;
+            const int rb = it / nkc, kci = it - rb * nkc, s = it % NS;
+            const int k0 = kci * p.kc;
+            const int len = min(p.kc, p.K - k0);
+            const uint32_t bar = smem_u32(&full_bar[s]);
+            for (int b = lane; b < p.B; b += 32) {
+                const bf16* src = p.x + (long long)b * p.ldx + k0;
+                const uint32_t dst = smem_u32(stage_base + (size_t)s * stage_bytes) +
+                                     (uint32_t)((WROWS + b) * ws_stride * (int)sizeof(bf16));
+                bulk_g2s(dst, src, (uint32_t)(len * (int)sizeof(bf16)), bar);
+            }
+        };
+
+        const int npre = min(min(p.prefetch, NS), total);
+        for (int it = 0; it < npre; ++it) request_weights(it);
+        pdl_wait();
+        for (int it = 0; it < npre; ++it) request_activations(it);
+        int issued = npre;
+        for (int it = npre; it < total; ++it) {
+            const int s = it % NS;
+            const uint32_t parity = (uint32_t)(((it / NS) & 1) ^ 1);
+            if (!mbar_wait_bounded(smem_u32(&empty_bar[s]), parity, abort_flag, p.status, FAULT_GEMV_EMPTY_WAIT)) break;
+            request_weights(it);
+            request_activations(it);
+            issued = it + 1;
+        }
+        // Leave only when nothing is still in flight towards this CTA's shared
+        // memory.  On the normal path the consumers have already waited for
+        // every stage, so these waits return at once.
+        if (*abort_flag) {
+            const int first = max(0, issued - NS);
+            for (int it = first; it < issued; ++it) {
+                const long long t0 = clock64();
+                while (!mbar_try_wait(smem_u32(&full_bar[it % NS]), (uint32_t)((it / NS) & 1))) {
+                    if (clock64() - t0 > kWaitLimitCycles) {
+                        report_fault(p.status, FAULT_GEMV_DRAIN);
+                        break;
+                    }
+                }
+            }
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------- consumers
+    const int cw = warp - 1;
+    const int ct = tid - 32;  // 0..127 among consumer threads
+    pdl_wait();
+
+    if (XRES) {
+        // Bring the activation block into shared memory, optionally adding an
+        // fp32 term first and RMS-normalising (statistics in fp32, one rounding).
+        float* scratch = red;  // 4 floats per use, free until the first row block ends
+        for (int b = 0; b < p.B; ++b) {
+            const bf16* xrow = p.x + (long long)b * p.ldx;
+            bf16* srow = xs + (size_t)b * xs_stride;
+            float ssq = 0.f;
+            for (int i = ct; i < p.K / 8; i += kConsumerThreads) {
+                uint4 raw = *reinterpret_cast<const uint4*>(xrow + i * 8);
+                uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+                if (p.prologue == PRO_ADD_RMSNORM) {
+                    const float4 a0 = *reinterpret_cast<const float4*>(p.x_add + (long long)b * p.ldadd + i * 8);
+                    const float4 a1 = *reinterpret_cast<const float4*>(p.x_add + (long long)b * p.ldadd + i * 8 + 4);
+                    const float add[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        w[e] = pack_bf16(bf16_lo(w[e]) + round_bf16(add[2 * e]), bf16_hi(w[e]) + round_bf16(add[2 * e + 1]));
+                    raw = make_uint4(w[0], w[1], w[2], w[3]);
+                    if (blockIdx.x == 0 && p.x_sum_out)
+                        *reinterpret_cast<uint4*>(p.x_sum_out + (long long)b * p.ldsum + i * 8) = raw;
+                }
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float lo = bf16_lo(w[e]), hi = bf16_hi(w[e]);
+                    ssq += lo * lo + hi * hi;
+                }
+                *reinterpret_cast<uint4*>(srow + i * 8) = raw;
+            }
+            if (p.prologue != PRO_NONE) {
+                ssq = warp_sum(ssq);
+                if (lane == 0) scratch[cw] = ssq;
+                named_bar_sync(1, kConsumerThreads);
+                const float tot = scratch[0] + scratch[1] + scratch[2] + scratch[3];
+                const float r = 1.0f / sqrtf(tot / (float)p.K + p.eps);
+                for (int i = ct; i < p.K / 8; i += kConsumerThreads) {
+                    uint4 raw = *reinterpret_cast<uint4*>(srow + i * 8);
+                    uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+                    uint32_t nw[4] = {0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u};  // bf16 ones
+                    if (p.norm_w) {
+                        const uint4 q = *reinterpret_cast<const uint4*>(p.norm_w + i * 8);
+                        nw[0] = q.x, nw[1] = q.y, nw[2] = q.z, nw[3] = q.w;
+                    }
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        float lo = bf16_lo(w[e]) * r, hi = bf16_hi(w[e]) * r;
+                        if (p.norm_w) lo *= bf16_lo(nw[e]), hi *= bf16_hi(nw[e]);
+                        w[e] = pack_bf16(lo, hi);
+                    }
+                    *reinterpret_cast<uint4*>(srow + i * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+                named_bar_sync(1, kConsumerThreads);  // scratch is reused by the next row
+            }
+        }
+        named_bar_sync(1, kConsumerThreads);
+    }
+
+    const int g4 = lane >> 2, t4 = lane & 3;
+    for (int rb = 0; rb < nrb; ++rb) {
+        float acc[M][NT][4];
+#pragma unroll
+        for (int m = 0; m < M; ++m)
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[m][j][e] = 0.f;
+
+        for (int kci = 0; kci < nkc; ++kci) {
+            const int it = rb * nkc + kci;
+            const int s = it % NS;
+            mbar_wait_bounded(smem_u32(&full_bar[s]), (uint32_t)((it / NS) & 1), abort_flag, p.status, FAULT_GEMV_FULL_WAIT);
+            const int k0 = kci * p.kc;
+            const int len = min(p.kc, p.K - k0);
+            const int nks = len >> 4;
+            const unsigned char* st = stage_base + (size_t)s * stage_bytes;
+            const uint32_t a_base = smem_u32(st) + (uint32_t)(((lane & 15) * ws_stride + (lane >> 4) * 8) * (int)sizeof(bf16));
+            for (int ks = cw; ks < nks; ks += kConsumerWarps) {
+                uint32_t a[M][4];
+#pragma unroll
+                for (int m = 0; m < M; ++m)
+                    ldsm_x4(a_base + (uint32_t)((m * kRowBlock * ws_stride + ks * 16) * (int)sizeof(bf16)), a[m][0], a[m][1],
+                            a[m][2], a[m][3]);
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    const int b = j * 8 + g4;
+                    uint32_t b0 = 0u, b1 = 0u;
+                    if (b < p.B) {
+                        const bf16* xb = XRES ? (xs + (size_t)b * xs_stride + k0 + ks * 16 + t4 * 2)
+                                              : (reinterpret_cast<const bf16*>(st) + (size_t)(WROWS + b) * ws_stride + ks * 16 + t4 * 2);
+                        b0 = *reinterpret_cast<const uint32_t*>(xb);
+                        b1 = *reinterpret_cast<const uint32_t*>(xb + 8);
+                    }
+#pragma unroll
+                    for (int m = 0; m < M; ++m) mma_bf16_16816(acc[m][j], a[m][0], a[m][1], a[m][2], a[m][3], b0, b1);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&empty_bar[s]));
+        }
+
+        // Combine the four warps' partial tiles (fixed order) and apply the epilogue.
+#pragma unroll
+        for (int m = 0; m < M; ++m)
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+                *reinterpret_cast<float4*>(red + ((size_t)((cw * M + m) * NT + j) * 32 + lane) * 4) =
+                    make_float4(acc[m][j][0], acc[m][j][1], acc[m][j][2], acc[m][j][3]);
+        named_bar_sync(1, kConsumerThreads);
+        {
+            const int fl = ct >> 2, e = ct & 3;
+            const int row = (fl >> 2) + ((e >= 2) ? 8 : 0);
+            const int col = (fl & 3) * 2 + (e & 1);
+            const int n = r0 + rb * kRowBlock + row;
+            const bool live = (n < r1) && !(*abort_flag);
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                const int b = j * 8 + col;
+                float v[M];
+#pragma unroll
+                for (int m = 0; m < M; ++m) {
+                    float sum = 0.f;
+#pragma unroll
+                    for (int w = 0; w < kConsumerWarps; ++w) sum += red[(size_t)((w * M + m) * NT + j) * 128 + ct];
+                    v[m] = sum;
+                }
+                if (live && b < p.B) {
+                    const long long o = (long long)b * p.ldout + n;
+                    if (p.epilogue == EPI_STORE_F32) {
+                        reinterpret_cast<float*>(p.out)[o] = v[0];
+                    } else if (p.epilogue == EPI_RESIDUAL) {
+                        const float res = __bfloat162float(p.residual[(long long)b * p.ldres + n]);
+                        reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16_rn(res + round_bf16(v[0]));
+                    } else if (PAIR && p.epilogue == EPI_SWIGLU) {
+                        const float gate = round_bf16(v[0]);
+                        const float up = round_bf16(v[M - 1]);
+                        reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16_rn(round_bf16(silu_f32(gate)) * up);
+                    } else {
+                        reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16_rn(v[0]);
+                    }
+                }
+            }
+        }
+        named_bar_sync(1, kConsumerThreads);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+struct GemvPlan {
+    int NT;
+    bool xres;
+    int kc, nstages, prefetch, grid;
+    size_t smem;
+};
+
+static int pick_nt(int B) { return B <= 8 ? 1 : (B <= 16 ? 2 : (B <= 32 ? 4 : 8)); }
+
+// Resident activations are worth it while they leave room for a useful ring.
+static bool x_fits_resident(int B, int K) { return (size_t)B * (K + 8) * 2 <= 72 * 1024 && B <= 8; }
+
+bool gemv_needs_scratch(int B, int K) { return !x_fits_resident(B, K); }
+
+static GemvPlan plan_gemv(const GemvArgs& a, bool pair) {
+    GemvPlan pl;
+    pl.NT = pick_nt(a.B);
+    pl.xres = x_fits_resident(a.B, a.K);
+    const int M = pair ? 2 : 1;
+    const int rows = kRowBlock * M + (pl.xres ? 0 : pl.NT * 8);
+    int kc = tuning(EZB_TUNE_GEMV_KC);
+    if (kc <= 0) {
+        // about 32 KB per stage
+        kc = (int)(32768 / (2 * rows)) - 8;
+        kc = kc / 64 * 64;
+        if (kc < 64) kc = 64;
+        if (kc > 2048) kc = 2048;
+    }
+    kc = kc / 16 * 16;
+    if (kc > a.K) kc = a.K;
+    pl.kc = kc;
+    const size_t stage = align_up((size_t)rows * (kc + 8) * 2, 128);
+    const size_t red = (size_t)kConsumerWarps * M * pl.NT * 128 * 4;
+    const size_t xs = pl.xres ? align_up((size_t)a.B * (a.K + 8) * 2, 128) : 0;
+    const size_t fixed = kHeaderBytes + red + xs;
+    size_t budget = (size_t)tuning(EZB_TUNE_GEMV_SMEM_KB) * 1024;
+    const size_t cap = (size_t)max_smem_optin();
+    if (budget > cap) budget = cap;
+    int ns = budget > fixed ? (int)((budget - fixed) / stage) : 0;
+    if (ns < 2) ns = 2;
+    if (ns > kMaxStages) ns = kMaxStages;
+    while (ns > 2 && fixed + (size_t)ns * stage > cap) --ns;
+    pl.nstages = ns;
+    int pf = tuning(EZB_TUNE_GEMV_PREFETCH);
+    pl.prefetch = (pf <= 0 || pf > ns) ? ns : pf;
+    pl.smem = fixed + (size_t)ns * stage;
+    int grid = sm_count() * max(1, tuning(EZB_TUNE_GEMV_CTAS_PER_SM));
+    if (grid > a.N) grid = a.N;
+    pl.grid = grid;
+    return pl;
+}
+
+template <int NT, bool XRES, bool PAIR>
+static cudaError_t launch_instance(const GemvParams& p, const GemvPlan& pl, cudaStream_t stream) {
+    auto kernel = gemv_stream_kernel<NT, XRES, PAIR>;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin());
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    return launch_pdl(kernel, dim3(pl.grid), dim3(kGemvThreads), pl.smem, stream, p);
+}
+
+template <bool XRES, bool PAIR>
+static cudaError_t dispatch_nt(const GemvParams& p, const GemvPlan& pl, cudaStream_t stream) {
+    switch (pl.NT) {
+        case 1: return launch_instance<1, XRES, PAIR>(p, pl, stream);
+        case 2: return launch_instance<2, XRES, PAIR>(p, pl, stream);
+        case 4: return launch_instance<4, XRES, PAIR>(p, pl, stream);
+        default: return launch_instance<8, XRES, PAIR>(p, pl, stream);
+    }
+}
+
+cudaError_t launch_gemv(const GemvArgs& a, cudaStream_t stream) {
+    const bool pair = a.epilogue == EPI_SWIGLU;
+    GemvPlan pl = plan_gemv(a, pair);
+
+    GemvParams p;
+    p.W0 = a.W0, p.W1 = a.W1, p.ldw = a.ldw;
+    p.N = a.N, p.K = a.K, p.B = a.B;
+    p.x = a.x, p.ldx = a.ldx;
+    p.x_add = a.x_add, p.ldadd = a.ldadd;
+    p.x_sum_out = a.x_sum_out, p.ldsum = a.ldsum;
+    p.norm_w = a.norm_w, p.eps = a.eps;
+    p.prologue = a.prologue, p.epilogue = a.epilogue;
+    p.residual = a.residual, p.ldres = a.ldres;
+    p.out = a.out, p.ldout = a.ldout;
+    p.kc = pl.kc, p.nstages = pl.nstages, p.prefetch = pl.prefetch;
+    p.status = status_ptr();
+    if (!p.status) return cudaErrorUnknown;
+
+    if (!pl.xres && a.prologue != PRO_NONE) {
+        // The activation block does not fit next to the ring: run the prologue
+        // as its own (tiny) kernel into the scratch rows, then stream those.
+        RowPrepArgs rp;
+        rp.x = a.x, rp.ldx = a.ldx;
+        rp.add = (a.prologue == PRO_ADD_RMSNORM) ? a.x_add : nullptr, rp.ldadd = a.ldadd;
+        rp.sum_out = (a.prologue == PRO_ADD_RMSNORM) ? a.x_sum_out : nullptr, rp.ldsum = a.ldsum;
+        rp.w = a.norm_w;
+        rp.y = a.xn_scratch, rp.ldy = a.K;
+        rp.rows = a.B, rp.dim = a.K, rp.eps = a.eps, rp.normalize = 1;
+        cudaError_t e = launch_row_prep(rp, stream);
+        if (e != cudaSuccess) return e;
+        p.x = a.xn_scratch, p.ldx = a.K;
+        p.prologue = PRO_NONE;
+    }
+
+    if (pl.xres) return pair ? dispatch_nt<true, true>(p, pl, stream) : dispatch_nt<true, false>(p, pl, stream);
+    return pair ? dispatch_nt<false, true>(p, pl, stream) : dispatch_nt<false, false>(p, pl, stream);
+}
+
+}  // namespace ezb

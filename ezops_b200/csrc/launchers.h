@@ -1,0 +1,104 @@
+// Host-side argument blocks and launch functions shared by the .cu files of
+// this library.  Launch functions validate nothing: the C-ABI layer (api.cu)
+// checks arguments before it fills these blocks.
+#pragma once
+
+#include "common.cuh"
+
+namespace ezb {
+
+// ------------------------------------------------------------------ GEMV ---
+enum GemvPrologue : int {
+    PRO_NONE = 0,         // x is used as given
+    PRO_RMSNORM = 1,      // x <- bf16(x * rsqrt(mean(x^2)+eps) [* w])
+    PRO_ADD_RMSNORM = 2,  // s = bf16(x + bf16(x_add)); CTA 0 stores s; x <- rmsnorm(s)
+};
+enum GemvEpilogue : int {
+    EPI_STORE = 0,      // out = bf16(acc)
+    EPI_RESIDUAL = 1,   // out = bf16(residual + bf16(acc))
+    EPI_SWIGLU = 2,     // out = bf16(bf16(silu(bf16(acc_gate))) * bf16(acc_up))
+    EPI_STORE_F32 = 3,  // out = acc (fp32)
+};
+
+struct GemvArgs {
+    const bf16* W0 = nullptr;  // [N, ldw]: row n produces output n (gate rows when W1 is set)
+    const bf16* W1 = nullptr;  // [N, ldw]: up rows (EPI_SWIGLU only)
+    long long ldw = 0;
+    int N = 0, K = 0, B = 0;
+    const bf16* x = nullptr;  // [B, ldx]
+    long long ldx = 0;
+    const float* x_add = nullptr;  // PRO_ADD_RMSNORM: [B, ldadd] fp32
+    long long ldadd = 0;
+    bf16* x_sum_out = nullptr;  // PRO_ADD_RMSNORM: [B, ldsum] bf16
+    long long ldsum = 0;
+    const bf16* norm_w = nullptr;  // optional [K]
+    float eps = 1e-6f;
+    int prologue = PRO_NONE;
+    int epilogue = EPI_STORE;
+    const bf16* residual = nullptr;  // EPI_RESIDUAL: [B, ldres]
+    long long ldres = 0;
+    void* out = nullptr;  // [B, ldout] bf16 (fp32 for EPI_STORE_F32)
+    long long ldout = 0;
+    bf16* xn_scratch = nullptr;  // [B, K] bf16: needed when the prologue cannot be fused (see gemv_needs_scratch)
+};
+
+// True when the activation block is too large to stay resident in shared memory
+// next to the weight ring, so a prologue has to run as a kernel of its own
+// writing to xn_scratch.
+bool gemv_needs_scratch(int B, int K);
+cudaError_t launch_gemv(const GemvArgs& a, cudaStream_t stream);
+
+// -------------------------------------------------------------- row prep ---
+// s = x (+ bf16(add));  optionally store s;  y = rmsnorm(s) [* w] or y = s.
+struct RowPrepArgs {
+    const bf16* x = nullptr;
+    long long ldx = 0;
+    const float* add = nullptr;  // optional fp32 [rows, ldadd]
+    long long ldadd = 0;
+    bf16* sum_out = nullptr;  // optional
+    long long ldsum = 0;
+    const bf16* w = nullptr;  // optional
+    bf16* y = nullptr;        // optional normalised output
+    long long ldy = 0;
+    int rows = 0, dim = 0;
+    float eps = 1e-6f;
+    int normalize = 1;
+};
+cudaError_t launch_row_prep(const RowPrepArgs& a, cudaStream_t stream);
+cudaError_t launch_rmsnorm_f32(const float* X, float* Out, int rows, int dim, float eps, cudaStream_t stream);
+
+struct RopeArgs {
+    const bf16 *q, *k, *v, *qw, *kw, *cos, *sin;
+    bf16 *K_cache, *V_cache, *q_out, *k_out;
+    int B, NQ, NKV, D, S, position;
+    const int* positions;
+    float eps;
+};
+cudaError_t launch_qk_norm_rope(const RopeArgs& a, cudaStream_t stream);
+
+// ------------------------------------------------------------- attention ---
+struct AttnArgs {
+    const bf16* Q = nullptr;  // query for (b, h) at Q + b*q_bstride + h*D
+    long long q_bstride = 0;
+    const bf16* K = nullptr;  // [B, NKV, S, D] contiguous
+    const bf16* V = nullptr;
+    bf16* Out = nullptr;  // output for (b, h) at Out + b*o_bstride + h*D
+    long long o_bstride = 0;
+    const int* seq_lens = nullptr;
+    int B = 0, H = 0, NKV = 0, S = 0, D = 0;
+    void* workspace = nullptr;
+    // decode-layer mode: q/k/v of the new token come from the fused projection
+    // output qkv[b] = [q heads | k heads | v heads]; q and k get a unit-weight
+    // RMSNorm over D; k and v are written to cache slot S-1 before it is read.
+    int fuse_new_token = 0;
+    const bf16* qkv = nullptr;
+    long long qkv_bstride = 0;
+    bf16* K_cache_w = nullptr;
+    bf16* V_cache_w = nullptr;
+    float eps = 1e-6f;
+};
+size_t attn_workspace_bytes(int B, int H, int NKV, int S, int D);
+int attn_chunk_keys(int B, int NKV, int S);  // keys per KV split chosen for this shape
+cudaError_t launch_attn_decode(const AttnArgs& a, cudaStream_t stream);
+
+}  // namespace ezb

@@ -1,0 +1,252 @@
+"""The sm_100a backends: one kernel class per operator of the decode path,
+registered as backend ``"cuda"``.  Each class validates what the operator
+contract asks of a constructor (``ValueError`` naming the rule), owns its
+workspace, and forwards to one entry point of ``libezb200.so`` on torch's
+current stream.  Calls enqueue work only (no synchronisation, no allocation
+after the first call), so they can be captured in a CUDA graph.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import _lib
+from ..registry import register_kernel
+from .base_kernel import BaseKernel
+
+_BF16 = torch.bfloat16
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _require(t: torch.Tensor, name: str, shape, dtype=_BF16) -> None:
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor")
+    if t.dtype != dtype:
+        raise ValueError(f"{name} must be {dtype}, got {t.dtype}")
+    if tuple(t.shape) != tuple(shape):
+        raise ValueError(f"{name} must have shape {tuple(shape)}, got {tuple(t.shape)}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+
+
+def _zeros_bytes(nbytes: int, device) -> torch.Tensor:
+    return torch.zeros(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+
+
+@register_kernel("gemv", "cuda")
+class GemvSm100Kernel(BaseKernel):
+    """C[N] = B[N,K] . A[K] (constructor contract: ezops/ops/gemv.py:21)."""
+
+    def __init__(self, N: int, K: int):
+        if K % 16:
+            raise ValueError(f"K ({K}) must be divisible by 16")
+        self.N, self.K = N, K
+        self._lib = _lib.load()
+
+    def __call__(self, A: torch.Tensor, B: torch.Tensor, C: torch.Tensor) -> None:
+        _require(A, "A", (self.K,))
+        _require(B, "B", (self.N, self.K))
+        _require(C, "C", (self.N,))
+        _lib.check(self._lib.ezb_gemv_bf16(A.data_ptr(), B.data_ptr(), C.data_ptr(), self.N, self.K, _stream()))
+
+
+@register_kernel("rmsnorm", "cuda")
+class RmsNormSm100Kernel(BaseKernel):
+    """fp32 rows without weight (ezops/ops/rmsnorm.py:22), or the bf16 variant
+    with optional weight when constructed with ``dtype=torch.bfloat16``."""
+
+    def __init__(self, batch_size: int, dim: int, eps: float = 1e-6, dtype=torch.float32, with_weight: bool = False):
+        if dtype == _BF16 and dim % 8:
+            raise ValueError(f"dim ({dim}) must be divisible by 8 for bf16 rows")
+        self.rows, self.dim, self.eps, self.dtype, self.with_weight = batch_size, dim, eps, dtype, with_weight
+        self._lib = _lib.load()
+
+    def __call__(self, X: torch.Tensor, *rest: torch.Tensor) -> None:
+        shape = (self.rows, self.dim)
+        if self.dtype == torch.float32:
+            (Out,) = rest
+            _require(X, "X", shape, torch.float32)
+            _require(Out, "Out", shape, torch.float32)
+            _lib.check(self._lib.ezb_rmsnorm_f32(X.data_ptr(), Out.data_ptr(), self.rows, self.dim, self.eps, _stream()))
+            return
+        if self.with_weight:
+            W, Out = rest
+            _require(W, "W", (self.dim,))
+        else:
+            (Out,), W = rest, None
+        _require(X, "X", shape)
+        _require(Out, "Out", shape)
+        _lib.check(
+            self._lib.ezb_rmsnorm_bf16(
+                X.data_ptr(), W.data_ptr() if W is not None else None, Out.data_ptr(), self.rows, self.dim, self.eps, _stream()
+            )
+        )
+
+
+@register_kernel("fused_qk_norm_rope", "cuda")
+class FusedQkNormRopeSm100Kernel(BaseKernel):
+    """Constructor contract: ezops/ops/fused_qk_norm_rope.py:85-92.  ``position``
+    may be a list with one entry per batch row (extension)."""
+
+    rms_eps = 1e-6
+
+    def __init__(self, batch, num_heads, head_dim, max_seq_len, position, num_kv_heads=None):
+        self.B, self.NQ, self.D, self.S = batch, num_heads, head_dim, max_seq_len
+        self.NKV = num_heads if num_kv_heads is None else num_kv_heads
+        if head_dim & (head_dim - 1) or not 8 <= head_dim <= 512:
+            raise ValueError(f"head_dim ({head_dim}) must be a power of two in [8, 512]")
+        if num_heads % self.NKV:
+            raise ValueError(f"num_heads ({num_heads}) must be divisible by num_kv_heads ({self.NKV})")
+        self.position = position
+        self._positions_dev = None
+        self._lib = _lib.load()
+
+    def __call__(self, q, k, v, q_norm_w, k_norm_w, cos, sin, K_cache, V_cache):
+        B, NQ, NKV, D, S = self.B, self.NQ, self.NKV, self.D, self.S
+        _require(q, "q", (B, NQ, D)); _require(k, "k", (B, NKV, D)); _require(v, "v", (B, NKV, D))
+        _require(q_norm_w, "q_norm_w", (D,)); _require(k_norm_w, "k_norm_w", (D,))
+        _require(cos, "cos", (S, D)); _require(sin, "sin", (S, D))
+        _require(K_cache, "K_cache", (B, NKV, S, D)); _require(V_cache, "V_cache", (B, NKV, S, D))
+        q_out, k_out = torch.empty_like(q), torch.empty_like(k)
+        if isinstance(self.position, int):
+            pos, pos_ptr = self.position, None
+        else:
+            if self._positions_dev is None or self._positions_dev.device != q.device:
+                self._positions_dev = torch.tensor(list(self.position), dtype=torch.int32, device=q.device)
+            pos, pos_ptr = 0, self._positions_dev.data_ptr()
+        _lib.check(
+            self._lib.ezb_qk_norm_rope(
+                q.data_ptr(), k.data_ptr(), v.data_ptr(), q_norm_w.data_ptr(), k_norm_w.data_ptr(), cos.data_ptr(),
+                sin.data_ptr(), K_cache.data_ptr(), V_cache.data_ptr(), q_out.data_ptr(), k_out.data_ptr(),
+                B, NQ, NKV, D, S, pos, pos_ptr, self.rms_eps, _stream(),
+            )
+        )
+        return q_out, k_out
+
+
+@register_kernel("attn_decode", "cuda")
+class AttnDecodeSm100Kernel(BaseKernel):
+    """Split-KV GQA flash decode (constructor contract: ezops/ops/attn_decode.py:42-51)."""
+
+    supports_gqa = True
+
+    def __init__(self, batch, num_heads, seq_len, head_dim, num_kv_heads=None, seq_lens=None):
+        self.B, self.H, self.S, self.D = batch, num_heads, seq_len, head_dim
+        self.NKV = num_heads if num_kv_heads is None else num_kv_heads
+        if head_dim not in (64, 128):
+            raise ValueError(f"head_dim ({head_dim}) must be 64 or 128")
+        if num_heads % self.NKV:
+            raise ValueError(f"num_heads ({num_heads}) must be divisible by num_kv_heads ({self.NKV})")
+        self.seq_lens = None if seq_lens is None else [int(x) for x in seq_lens]
+        self._lens_dev = None
+        self._ws = None
+        self._lib = _lib.load()
+
+    def _workspace(self, device):
+        need = self._lib.ezb_attn_decode_workspace_bytes(self.B, self.H, self.NKV, self.S, self.D)
+        if self._ws is None or self._ws.device != device or self._ws.numel() < need:
+            self._ws = _zeros_bytes(need, device)
+        return self._ws
+
+    def __call__(self, Q, K, V):
+        B, H, NKV, S, D = self.B, self.H, self.NKV, self.S, self.D
+        _require(Q, "Q", (B, H, 1, D)); _require(K, "K", (B, NKV, S, D)); _require(V, "V", (B, NKV, S, D))
+        out = torch.empty_like(Q)
+        ws = self._workspace(Q.device)
+        lens_ptr = None
+        if self.seq_lens is not None:
+            if self._lens_dev is None or self._lens_dev.device != Q.device:
+                self._lens_dev = torch.tensor(self.seq_lens, dtype=torch.int32, device=Q.device)
+            lens_ptr = self._lens_dev.data_ptr()
+        _lib.check(
+            self._lib.ezb_attn_decode(
+                Q.data_ptr(), K.data_ptr(), V.data_ptr(), out.data_ptr(), ws.data_ptr(), ws.numel(),
+                B, H, NKV, S, D, lens_ptr, _stream(),
+            )
+        )
+        return out
+
+
+@register_kernel("fused_o_proj_ffn", "cuda")
+class FusedOProjFfnSm100Kernel(BaseKernel):
+    """Constructor contract: ezops/ops/fused_o_proj_ffn.py:78."""
+
+    rms_eps = 1e-6
+
+    def __init__(self, batch, hidden_size, intermediate_size, num_heads, head_dim):
+        self.B, self.H, self.I, self.Q = batch, hidden_size, intermediate_size, num_heads * head_dim
+        for name, val in (("hidden_size", self.H), ("intermediate_size", self.I), ("num_heads * head_dim", self.Q)):
+            if val % 16:
+                raise ValueError(f"{name} ({val}) must be divisible by 16")
+        if not 1 <= batch <= 64:
+            raise ValueError(f"batch ({batch}) must be in [1, 64]")
+        self._ws = None
+        self._lib = _lib.load()
+
+    def __call__(self, attn, residual, Wo, post_norm_w, Wg, Wu, Wd):
+        B, H, I, Q = self.B, self.H, self.I, self.Q
+        _require(attn, "attn", (B, Q)); _require(residual, "residual", (B, H)); _require(Wo, "Wo", (H, Q))
+        _require(post_norm_w, "post_norm_w", (H,)); _require(Wg, "Wg", (I, H)); _require(Wu, "Wu", (I, H))
+        _require(Wd, "Wd", (H, I))
+        if self._ws is None or self._ws.device != attn.device:
+            self._ws = _zeros_bytes(self._lib.ezb_o_proj_ffn_workspace_bytes(B, H, I, Q), attn.device)
+        out = torch.empty_like(residual)
+        _lib.check(
+            self._lib.ezb_o_proj_ffn(
+                attn.data_ptr(), residual.data_ptr(), Wo.data_ptr(), post_norm_w.data_ptr(), Wg.data_ptr(), Wu.data_ptr(),
+                Wd.data_ptr(), out.data_ptr(), self._ws.data_ptr(), self._ws.numel(), B, H, I, Q, self.rms_eps, _stream(),
+            )
+        )
+        return out
+
+
+@register_kernel("qwen3_dense_decode", "cuda")
+class Qwen3DenseDecodeSm100Kernel(BaseKernel):
+    """The whole decode layer as a chain of five kernels linked by programmatic
+    dependent launch (constructor contract: ezops/ops/qwen3_dense_decode.py:100-108)."""
+
+    rms_eps = 1e-6
+
+    def __init__(self, batch, seq_len, hidden_size, intermediate_size, num_heads, head_dim, num_kv_heads=None):
+        self.B, self.S, self.H, self.I = batch, seq_len, hidden_size, intermediate_size
+        self.NH, self.D = num_heads, head_dim
+        self.NKV = num_heads if num_kv_heads is None else num_kv_heads
+        if num_heads % self.NKV:
+            raise ValueError(f"num_heads ({num_heads}) must be divisible by num_kv_heads ({self.NKV})")
+        if head_dim not in (64, 128):
+            raise ValueError(f"head_dim ({head_dim}) must be 64 or 128")
+        if num_heads // self.NKV > 16:
+            raise ValueError("at most 16 query heads per kv head")
+        for name, val in (("hidden_size", self.H), ("intermediate_size", self.I)):
+            if val % 16:
+                raise ValueError(f"{name} ({val}) must be divisible by 16")
+        if not 1 <= batch <= 64:
+            raise ValueError(f"batch ({batch}) must be in [1, 64]")
+        self._ws = None
+        self._lib = _lib.load()
+
+    def workspace(self, device):
+        if self._ws is None or self._ws.device != device:
+            need = self._lib.ezb_qwen3_decode_layer_workspace_bytes(self.B, self.S, self.H, self.I, self.NH, self.NKV, self.D)
+            self._ws = _zeros_bytes(need, device)
+        return self._ws
+
+    def __call__(self, hidden, K_cache, V_cache, Wqkv, Wo, Wgu, Wd, out=None):
+        B, S, H, I, NH, NKV, D = self.B, self.S, self.H, self.I, self.NH, self.NKV, self.D
+        _require(hidden, "hidden", (B, H))
+        _require(K_cache, "K_cache", (B, NKV, S, D)); _require(V_cache, "V_cache", (B, NKV, S, D))
+        _require(Wqkv, "Wqkv", ((NH + 2 * NKV) * D, H)); _require(Wo, "Wo", (H, NH * D))
+        _require(Wgu, "Wgu", (2 * I, H)); _require(Wd, "Wd", (H, I))
+        ws = self.workspace(hidden.device)
+        if out is None:
+            out = torch.empty_like(hidden)
+        _lib.check(
+            self._lib.ezb_qwen3_decode_layer(
+                hidden.data_ptr(), K_cache.data_ptr(), V_cache.data_ptr(), Wqkv.data_ptr(), Wo.data_ptr(), Wgu.data_ptr(),
+                Wd.data_ptr(), out.data_ptr(), ws.data_ptr(), ws.numel(), B, S, H, I, NH, NKV, D, self.rms_eps, _stream(),
+            )
+        )
+        return out

@@ -1,0 +1,123 @@
+"""Tensor-parallel form of the Qwen3 decode layer: one process per GPU, heads
+and FFN columns split across ranks, one sum over ranks after o_proj and one
+after down_proj (the reference is single-GPU and has no counterpart).
+
+Sharding (``tp`` ranks, rank ``r``):
+    Wqkv rows : q heads [r*NH/tp, (r+1)*NH/tp), the matching k heads and v heads
+    KV cache  : the rank's kv heads                    -> attention is rank-local
+    Wo        : the columns of the rank's q heads      -> partial [B, H], summed
+    Wgu rows  : gate rows and up rows [r*I/tp, (r+1)*I/tp)
+    Wd        : the same columns                       -> partial [B, H], summed
+Hidden states, residuals and norms are replicated.  Partials are exchanged in
+fp32 with ``torch.distributed.all_reduce`` (NCCL over NVLink on GPUs).
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+
+
+def shard_layer_weights(Wqkv, Wo, Wgu, Wd, num_heads: int, num_kv_heads: int, head_dim: int, tp: int, rank: int):
+    """Contiguous per-rank copies of one layer's weights (see module docstring)."""
+    if num_heads % tp or num_kv_heads % tp:
+        raise ValueError(f"tp ({tp}) must divide num_heads ({num_heads}) and num_kv_heads ({num_kv_heads})")
+    inter = Wgu.shape[0] // 2
+    if inter % tp or (inter // tp) % 16:
+        raise ValueError(f"intermediate_size / tp ({inter}/{tp}) must be a multiple of 16")
+    q_rows, kv_rows = num_heads * head_dim, num_kv_heads * head_dim
+    ql, kl, il = q_rows // tp, kv_rows // tp, inter // tp
+    Wqkv_r = torch.cat(
+        [
+            Wqkv[rank * ql : (rank + 1) * ql],
+            Wqkv[q_rows + rank * kl : q_rows + (rank + 1) * kl],
+            Wqkv[q_rows + kv_rows + rank * kl : q_rows + kv_rows + (rank + 1) * kl],
+        ]
+    ).contiguous()
+    Wo_r = Wo[:, rank * ql : (rank + 1) * ql].contiguous()
+    Wgu_r = torch.cat([Wgu[rank * il : (rank + 1) * il], Wgu[inter + rank * il : inter + (rank + 1) * il]]).contiguous()
+    Wd_r = Wd[:, rank * il : (rank + 1) * il].contiguous()
+    return Wqkv_r, Wo_r, Wgu_r, Wd_r
+
+
+def shard_kv_cache(cache: torch.Tensor, tp: int, rank: int) -> torch.Tensor:
+    nkv = cache.shape[1]
+    if nkv % tp:
+        raise ValueError(f"tp ({tp}) must divide num_kv_heads ({nkv})")
+    n = nkv // tp
+    return cache[:, rank * n : (rank + 1) * n].contiguous()
+
+
+class TensorParallelDecodeLayer:
+    """Per-rank executor.  ``__call__(hidden, K_local, V_local, Wqkv_l, Wo_l, Wgu_l, Wd_l)``
+    returns the full [B, H] layer output (identical on every rank)."""
+
+    rms_eps = 1e-6
+
+    def __init__(self, batch, seq_len, hidden_size, intermediate_size, num_heads, head_dim, num_kv_heads, group=None):
+        self.group = group
+        self.tp = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        tp = self.tp
+        if num_heads % tp or num_kv_heads % tp or intermediate_size % tp:
+            raise ValueError(f"tp ({tp}) must divide num_heads, num_kv_heads and intermediate_size")
+        self.B, self.S, self.H, self.D = batch, seq_len, hidden_size, head_dim
+        self.NH_l, self.NKV_l, self.I_l = num_heads // tp, num_kv_heads // tp, intermediate_size // tp
+        if self.I_l % 16 or hidden_size % 16:
+            raise ValueError("hidden_size and intermediate_size / tp must be divisible by 16")
+        self._bufs = None
+
+    # -- buffers ------------------------------------------------------------
+    def _buffers(self, device):
+        if self._bufs is None or self._bufs["partial_o"].device != device:
+            lib = _lib.load()
+            ws1 = lib.ezb_qwen3_decode_layer_workspace_bytes(self.B, self.S, self.H, self.I_l, self.NH_l, self.NKV_l, self.D)
+            ws2 = lib.ezb_o_proj_ffn_workspace_bytes(self.B, self.H, self.I_l, 16)
+            self._bufs = dict(
+                ws1=torch.zeros(max(ws1, 256), dtype=torch.uint8, device=device),
+                ws2=torch.zeros(max(ws2, 256), dtype=torch.uint8, device=device),
+                partial_o=torch.empty(self.B, self.H, dtype=torch.float32, device=device),
+                partial_d=torch.empty(self.B, self.H, dtype=torch.float32, device=device),
+                x2=torch.empty(self.B, self.H, dtype=torch.bfloat16, device=device),
+            )
+        return self._bufs
+
+    # -- the three local parts (C ABI) and the exchange in between ------------
+    def _part_attn(self, hidden, K_l, V_l, Wqkv_l, Wo_l, bufs):
+        lib = _lib.load()
+        s = torch.cuda.current_stream().cuda_stream
+        _lib.check(lib.ezb_qwen3_decode_layer_tp_attn(
+            hidden.data_ptr(), K_l.data_ptr(), V_l.data_ptr(), Wqkv_l.data_ptr(), Wo_l.data_ptr(),
+            bufs["partial_o"].data_ptr(), bufs["ws1"].data_ptr(), bufs["ws1"].numel(),
+            self.B, self.S, self.H, self.NH_l, self.NKV_l, self.D, self.rms_eps, s))
+
+    def _part_ffn(self, hidden, Wgu_l, Wd_l, bufs):
+        lib = _lib.load()
+        s = torch.cuda.current_stream().cuda_stream
+        _lib.check(lib.ezb_qwen3_decode_layer_tp_ffn(
+            hidden.data_ptr(), bufs["partial_o"].data_ptr(), Wgu_l.data_ptr(), Wd_l.data_ptr(), bufs["x2"].data_ptr(),
+            bufs["partial_d"].data_ptr(), bufs["ws2"].data_ptr(), bufs["ws2"].numel(),
+            self.B, self.H, self.I_l, self.rms_eps, s))
+
+    def _part_out(self, out, bufs):
+        lib = _lib.load()
+        s = torch.cuda.current_stream().cuda_stream
+        _lib.check(lib.ezb_residual_add_f32(bufs["x2"].data_ptr(), bufs["partial_d"].data_ptr(), out.data_ptr(),
+                                            self.B, self.H, s))
+
+    def _sum_over_ranks(self, t: torch.Tensor) -> None:
+        if self.tp > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+
+    def __call__(self, hidden, K_local, V_local, Wqkv_l, Wo_l, Wgu_l, Wd_l, out=None):
+        bufs = self._buffers(hidden.device)
+        if out is None:
+            out = torch.empty_like(hidden)
+        self._part_attn(hidden, K_local, V_local, Wqkv_l, Wo_l, bufs)
+        self._sum_over_ranks(bufs["partial_o"])
+        self._part_ffn(hidden, Wgu_l, Wd_l, bufs)
+        self._sum_over_ranks(bufs["partial_d"])
+        self._part_out(out, bufs)
+        return out

@@ -1,0 +1,166 @@
+/*
+ * ezb200 -- C ABI of the B200 (sm_100a) kernels for the Qwen3 dense-decode
+ * path of ez-ops.  One entry point per operator of that path; each comment
+ * names the reference interface the entry point stands in for (file:line,
+ * paths relative to the ez-ops project root).
+ *
+ * Conventions
+ *   - All pointers are device pointers unless the name ends in _host.
+ *   - "bf16" buffers are passed as void* / const void* (2 bytes per element).
+ *   - The library never allocates or frees device memory.  Operators that need
+ *     scratch take a workspace pointer and size; the matching
+ *     *_workspace_bytes() query gives the size.  A workspace must be zero-filled
+ *     once before its first use; every call leaves it ready for the next one.
+ *     One workspace serves one stream at a time.
+ *   - Work is enqueued on `stream` and the call returns without synchronising,
+ *     so calls can be captured into a CUDA graph.  The kernels of one call, and
+ *     consecutive calls on one stream, are chained with programmatic dependent
+ *     launch; ordering against other work on the stream is the usual one.
+ *   - Return value: EZB_OK or a negative EZB_ERR_* code.  ezb_strerror() names
+ *     the code, ezb_last_error_message() gives the detail of the last failure
+ *     on the calling thread.  Arguments are validated before anything is
+ *     launched; a rejected call has no effect.
+ *   - Device-side waits are bounded.  A kernel that gives up on a wait records
+ *     a code in a per-device status word, finishes without hanging, and leaves
+ *     its outputs unspecified; ezb_device_status() reads the word.
+ */
+#ifndef EZB200_H
+#define EZB200_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* ezb_stream_t; /* same type as cudaStream_t */
+
+#define EZB_OK 0
+#define EZB_ERR_INVALID_ARGUMENT (-1) /* null / misaligned pointer, non-positive size */
+#define EZB_ERR_UNSUPPORTED_SHAPE (-2) /* shape outside what the kernels cover          */
+#define EZB_ERR_CUDA (-3)              /* a CUDA runtime call failed                    */
+#define EZB_ERR_WORKSPACE (-4)         /* workspace missing or too small                */
+#define EZB_ERR_DEVICE_FAULT (-5)      /* ezb_device_status() found a recorded fault    */
+
+/* Tuning knobs for ezb_set_tuning / ezb_get_tuning (process-wide, read at launch). */
+#define EZB_TUNE_PDL 0              /* 1: chain kernels with programmatic dependent launch (default 1) */
+#define EZB_TUNE_GEMV_SMEM_KB 1     /* shared-memory budget per CTA of the weight-streaming kernel      */
+#define EZB_TUNE_GEMV_PREFETCH 2    /* weight stages requested before the dependency wait (0 = all)     */
+#define EZB_TUNE_GEMV_CTAS_PER_SM 3 /* persistent CTAs per SM of the weight-streaming kernel            */
+#define EZB_TUNE_ATTN_MIN_CHUNK 4   /* smallest KV split, in keys (multiple of 64)                      */
+#define EZB_TUNE_ATTN_WAVES 5       /* target number of KV splits per SM                                */
+#define EZB_TUNE_GEMV_KC 6          /* k-chunk length of a weight stage (0 = automatic)                 */
+#define EZB_TUNE_COUNT 7
+
+int ezb_version(void);
+const char* ezb_strerror(int code);
+const char* ezb_last_error_message(void);
+int ezb_set_tuning(int key, int value);
+int ezb_get_tuning(int key);
+
+/* Reads (and with clear != 0 resets) the status word of the current device.
+ * Synchronises the device.  *status_out == 0 means no kernel gave up a wait. */
+int ezb_device_status(unsigned int* status_out_host, int clear);
+
+/* y[N] = W[N,K] . x[K], bf16 in, fp32 accumulate, bf16 out.
+ * Replaces the host entries gemv_cu(A,B,C) (ezops/kernels/gemv/gemv_cu.cu:71)
+ * and gemv_ws_cu(A,B,C) (ezops/kernels/gemv/gemv_ws_cu.cu:211) behind
+ * GemvOp.forward (ezops/ops/gemv.py:26-27).  K % 16 == 0. */
+int ezb_gemv_bf16(const void* x, const void* W, void* y, int N, int K, ezb_stream_t stream);
+
+/* Batched form of the same kernel: Y[b, :] = W[N,K] . X[b, :] for b < B <= 64,
+ * X [B,K], Y [B,N]; the weight is still streamed once for the whole batch.
+ * (The reference op is batch 1 only; its fused ops hold the batched
+ * projections, e.g. ezops/ops/qwen3_dense_decode.py:157.)  `workspace` is only
+ * touched when B > 8 or B*K is large; it needs ezb_gemv_workspace_bytes(). */
+size_t ezb_gemv_workspace_bytes(int B, int K);
+int ezb_gemv_batched_bf16(const void* X, const void* W, void* Y, void* workspace, size_t workspace_bytes, int B, int N,
+                          int K, ezb_stream_t stream);
+
+/* Out = X * rsqrt(mean(X^2) + eps), fp32 rows, no weight.
+ * Replaces rmsnorm_cu(X,Out,eps) (ezops/kernels/rmsnorm/rmsnorm_cu.cu:51)
+ * behind RmsNormOp.forward (ezops/ops/rmsnorm.py:26-27). */
+int ezb_rmsnorm_f32(const float* X, float* Out, int rows, int dim, float eps, ezb_stream_t stream);
+
+/* bf16 rows with optional bf16 weight (null = unit weight): fp32 statistics,
+ * (x * rsqrt(var+eps) * w) in fp32, one rounding.  The norm that the reference
+ * has only inside its fused ops (ezops/ops/fused_o_proj_ffn.py:107-110,
+ * ezops/ops/qwen3_dense_decode.py:137-140), exposed as an operator. dim % 8 == 0. */
+int ezb_rmsnorm_bf16(const void* X, const void* w_or_null, void* Out, int rows, int dim, float eps,
+                     ezb_stream_t stream);
+
+/* Per-head RMSNorm(w) + rotate-half RoPE of q and k, and the KV-cache write
+ * K_cache[b,:,pos]=k_out, V_cache[b,:,pos]=v.  Replaces the kernel objects
+ * behind FusedQkNormRopeOp.forward (ezops/ops/fused_qk_norm_rope.py:95-107;
+ * the reference has Triton/TileLang backends only,
+ * ezops/kernels/fused_qk_norm_rope/fused_qk_norm_rope_triton.py:53-102).
+ * q,q_out [B,NQ,D]; k,v,k_out [B,NKV,D]; qw,kw [D]; cos,sin [S,D];
+ * K_cache,V_cache [B,NKV,S,D].  positions_or_null: int32[B] device array with
+ * one slot per batch row; when null every row uses `position`.  D is a power of
+ * two in [8, 512]. */
+int ezb_qk_norm_rope(const void* q, const void* k, const void* v, const void* qw, const void* kw, const void* cos,
+                     const void* sin, void* K_cache, void* V_cache, void* q_out, void* k_out, int B, int NQ, int NKV,
+                     int D, int S, int position, const int* positions_or_null, float eps, ezb_stream_t stream);
+
+/* Single-query GQA attention, split over the KV length with a log-sum-exp
+ * combine.  Replaces attn_decode_cu(Q,K,V,Out)
+ * (ezops/kernels/attn_decode/attn_decode_cu.cu:140, MHA only) and the
+ * flash_decode_tilelang_gqa* kernels (ezops/kernels/attn_decode/attn_decode_tl.py:25-657)
+ * behind AttnDecodeOp.forward (ezops/ops/attn_decode.py:55-56).
+ * Q,Out [B,H,1,D]; K,V [B,NKV,S,D]; seq_lens_or_null int32[B] (1 <= len <= S).
+ * D in {64, 128}; H % NKV == 0. */
+size_t ezb_attn_decode_workspace_bytes(int B, int H, int NKV, int S, int D);
+int ezb_attn_decode(const void* Q, const void* K, const void* V, void* Out, void* workspace, size_t workspace_bytes,
+                    int B, int H, int NKV, int S, int D, const int* seq_lens_or_null, ezb_stream_t stream);
+
+/* x2 = residual + attn Wo^T ; out = x2 + (silu(xn Wg^T) * (xn Wu^T)) Wd^T with
+ * xn = rmsnorm(x2) * post_norm_w.  Replaces the kernel objects behind
+ * FusedOProjFfnOp.forward (ezops/ops/fused_o_proj_ffn.py:84-94; reference
+ * backends ezops/kernels/fused_o_proj_ffn/fused_o_proj_ffn_triton.py:31-231).
+ * attn [B,Q]; residual,out [B,H]; Wo [H,Q]; post_norm_w [H]; Wg,Wu [I,H];
+ * Wd [H,I].  Q, H, I multiples of 16; B in [1, 64]. */
+size_t ezb_o_proj_ffn_workspace_bytes(int B, int H, int I, int Q);
+int ezb_o_proj_ffn(const void* attn, const void* residual, const void* Wo, const void* post_norm_w, const void* Wg,
+                   const void* Wu, const void* Wd, void* out, void* workspace, size_t workspace_bytes, int B, int H,
+                   int I, int Q, float eps, ezb_stream_t stream);
+
+/* One decode step of a Qwen3 dense layer (no RoPE, unit-weight norms), new
+ * k / v written to cache slot S-1.  Replaces the kernel objects behind
+ * Qwen3DenseDecodeOp.forward (ezops/ops/qwen3_dense_decode.py:110-120;
+ * reference backends under ezops/kernels/qwen3_dense_decode/).
+ * hidden,out [B,H]; K_cache,V_cache [B,NKV,S,D]; Wqkv [(NH+2NKV)D,H];
+ * Wo [H,NH*D]; Wgu [2I,H] (gate rows then up rows); Wd [H,I].
+ * D in {64,128}; NH/NKV <= 16; H, I multiples of 16; B in [1, 64]. */
+size_t ezb_qwen3_decode_layer_workspace_bytes(int B, int S, int H, int I, int NH, int NKV, int D);
+int ezb_qwen3_decode_layer(const void* hidden, void* K_cache, void* V_cache, const void* Wqkv, const void* Wo,
+                           const void* Wgu, const void* Wd, void* out, void* workspace, size_t workspace_bytes, int B,
+                           int S, int H, int I, int NH, int NKV, int D, float eps, ezb_stream_t stream);
+
+/* Tensor-parallel form of the same layer for one rank holding NH_local query
+ * heads, NKV_local kv heads and I_local FFN columns (no counterpart in the
+ * reference, which is single-GPU; the split follows the usual row/column
+ * scheme: Wqkv_local [(NH_local+2NKV_local)D,H], Wo_local [H,NH_local*D],
+ * Wgu_local [2*I_local,H], Wd_local [H,I_local]).  The layer is cut at its two
+ * exchange points; the caller sums the fp32 partials over ranks in between
+ * (NCCL all-reduce):
+ *   part 1: rmsnorm, QKV, attention, o_proj         -> partial_o   [B,H] fp32
+ *   part 2: x2 = hidden + sum(partial_o), rmsnorm, gate/up, SwiGLU, down
+ *                                                   -> x2 [B,H] bf16, partial_d [B,H] fp32
+ *   part 3: out = x2 + sum(partial_d)               -> out [B,H] bf16
+ * Part 1 takes a workspace of ezb_qwen3_decode_layer_workspace_bytes() for the
+ * local sizes; part 2 takes a separate one of
+ * ezb_o_proj_ffn_workspace_bytes(B, H, I_local, 16).  Neither may be shared
+ * with the other part. */
+int ezb_qwen3_decode_layer_tp_attn(const void* hidden, void* K_cache, void* V_cache, const void* Wqkv_local,
+                                   const void* Wo_local, float* partial_o, void* workspace, size_t workspace_bytes,
+                                   int B, int S, int H, int NH_local, int NKV_local, int D, float eps,
+                                   ezb_stream_t stream);
+int ezb_qwen3_decode_layer_tp_ffn(const void* hidden, const float* summed_o, const void* Wgu_local,
+                                  const void* Wd_local, void* x2, float* partial_d, void* workspace,
+                                  size_t workspace_bytes, int B, int H, int I_local, float eps, ezb_stream_t stream);
+int ezb_residual_add_f32(const void* x2, const float* summed_d, void* out, int B, int H, ezb_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EZB200_H */

@@ -1,0 +1,468 @@
+"""Parity of the sm_100a kernels (called through the operator API, which calls
+the C ABI) against the CPU oracle and the golden fixtures.
+
+Tolerances (floating point, bf16 storage):
+  * element-wise ops / attention / GEMV: torch.allclose(atol=1e-2, rtol=1e-2),
+    the reference's own acceptance (ezops/ops/gemv.py:12-13 etc.);
+  * GEMV also: relative error <= 1e-3 against the fp32-accumulated oracle
+    rounded to bf16 once;
+  * fused layer ops: relative Frobenius error < 1e-2 (the reference's check) and
+    max-abs <= 2e-2 on O(1) outputs where that is meaningful for bf16;
+  * fp32 RMSNorm: 1e-5.
+Integer / copy semantics are exact: V-cache writes bit-equal, every cache slot
+other than the written one untouched, two calls byte-identical.
+"""
+
+import pytest
+import torch
+
+from helpers import frac_within_one_ulp, load_golden, max_abs, rel_fro
+from oracle import ezops_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ez(cuda_device):
+    import ezops_b200
+
+    return ezops_b200
+
+
+@pytest.fixture(autouse=True)
+def _device_healthy(cuda_device):
+    yield
+    from ezops_b200 import _lib
+
+    assert _lib.device_status() == 0, "a kernel recorded a device-side fault"
+
+
+def dev(*ts):
+    return tuple(t.cuda() for t in ts)
+
+
+# ------------------------------------------------------------------ GEMV ---
+@pytest.mark.parametrize("N,K", [(192, 320), (100, 64), (1, 16), (4096, 4096), (6144, 4096), (4096, 12288), (5120, 25600)])
+def test_gemv_vs_oracle(ez, N, K):
+    from ezops_b200 import workloads as wl
+    from ezops_b200.ops.utils import check_determinism, check_input_readonly
+
+    x, W, y = wl.gemv_inputs(N, K, seed=7)
+    op = ez.GemvOp(N, K, backend="cuda")
+    xd, Wd, yd = dev(x, W, y)
+    op(xd, Wd, yd)
+    ref = orc.gemv_ref(x, W)
+    assert op.check(yd.cpu(), ref)
+    once = orc.gemv_fp32(x, W).to(torch.bfloat16)
+    assert rel_fro(yd, once) <= 1e-3
+    assert frac_within_one_ulp(yd, once) > 0.999
+    assert check_determinism(op, (xd, Wd), yd)
+    assert check_input_readonly(op, (xd, Wd), yd)
+
+
+def test_gemv_golden(ez):
+    g = load_golden("gemv")
+    N, K = g["W"].shape
+    y = torch.empty(N, dtype=torch.bfloat16, device="cuda")
+    ez.GemvOp(N, K, backend="cuda")(g["x"].cuda(), g["W"].cuda(), y)
+    assert torch.allclose(y.cpu(), g["y"], atol=1e-2, rtol=1e-2)
+    assert rel_fro(y, g["y"]) < 2e-3
+
+
+def test_gemv_reference_distribution(ez):
+    # the reference draws W ~ N(0,1) (ezops/ops/gemv.py:31-33)
+    torch.manual_seed(42)
+    N = K = 2048
+    A, B = torch.randn(K).bfloat16(), torch.randn(N, K).bfloat16()
+    C = torch.empty(N, dtype=torch.bfloat16, device="cuda")
+    op = ez.GemvOp(N, K, backend="cuda")
+    op(A.cuda(), B.cuda(), C)
+    assert op.check(C.cpu(), orc.gemv_ref(A, B))
+
+
+@pytest.mark.parametrize("B,N,K", [(2, 256, 512), (5, 100, 320), (8, 4096, 4096), (8, 512, 12288), (16, 1024, 2048),
+                                   (33, 300, 1024), (64, 2048, 4096)])
+def test_gemv_batched(ez, B, N, K):
+    from ezops_b200 import _lib
+
+    g = torch.Generator().manual_seed(B * 1000 + N)
+    X = torch.randn(B, K, generator=g).bfloat16()
+    W = (torch.randn(N, K, generator=g) * 0.05).bfloat16()
+    Y = torch.full((B, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    Xd, Wd = dev(X, W)
+    ws = torch.zeros(256, dtype=torch.uint8, device="cuda")
+    lib = _lib.load()
+    _lib.check(lib.ezb_gemv_batched_bf16(Xd.data_ptr(), Wd.data_ptr(), Y.data_ptr(), ws.data_ptr(), ws.numel(), B, N, K,
+                                         torch.cuda.current_stream().cuda_stream))
+    ref = (X.float() @ W.float().T).to(torch.bfloat16)
+    assert rel_fro(Y, ref) <= 1e-3
+    assert torch.allclose(Y.cpu().float(), ref.float(), atol=1e-2, rtol=1e-2)
+
+
+def test_gemv_rejects_bad_k(ez):
+    with pytest.raises(ValueError, match="divisible"):
+        ez.GemvOp(64, 100, backend="cuda")
+
+
+# --------------------------------------------------------------- RMSNorm ---
+@pytest.mark.parametrize("batch,dim", [(1, 64), (128, 1024), (3, 100), (7, 4097), (4096, 4096), (5, 1025), (2, 20000)])
+def test_rmsnorm_f32(ez, batch, dim):
+    from ezops_b200.ops.utils import check_determinism, check_input_readonly
+
+    g = torch.Generator().manual_seed(42)
+    X = torch.randn(batch, dim, generator=g)
+    op = ez.RmsNormOp(batch, dim, backend="cuda")
+    Xd = X.cuda()
+    Out = torch.empty_like(Xd)
+    op(Xd, Out)
+    ref = orc.rmsnorm_f32_ref(X)
+    assert op.check(Out.cpu(), ref), max_abs(Out, ref)
+    assert check_determinism(op, (Xd,), Out)
+    assert check_input_readonly(op, (Xd,), Out)
+
+
+def test_rmsnorm_f32_golden_and_eps(ez):
+    g = load_golden("rmsnorm_f32")
+    X = g["X"].cuda()
+    Out = torch.empty_like(X)
+    ez.RmsNormOp(*g["X"].shape, backend="cuda", eps=g["eps"])(X, Out)
+    assert torch.allclose(Out.cpu(), g["Out"], atol=1e-5, rtol=1e-5)
+    X2 = torch.randn(64, 1024, generator=torch.Generator().manual_seed(1))
+    Out2 = torch.empty(64, 1024, device="cuda")
+    ez.RmsNormOp(64, 1024, backend="cuda", eps=1e-5)(X2.cuda(), Out2)
+    assert torch.allclose(Out2.cpu(), orc.rmsnorm_f32_ref(X2, 1e-5), atol=1e-5, rtol=1e-5)
+
+
+@pytest.mark.parametrize("rows,dim,weighted", [(32, 4096, True), (1, 4096, False), (3, 5120, True), (64, 128, True)])
+def test_rmsnorm_bf16(ez, rows, dim, weighted):
+    from ezops_b200 import workloads as wl
+
+    X, w = wl.rmsnorm_inputs(rows, dim)
+    op = ez.RmsNormOp(rows, dim, backend="cuda", dtype=torch.bfloat16, with_weight=weighted)
+    Out = torch.empty(rows, dim, dtype=torch.bfloat16, device="cuda")
+    if weighted:
+        op(X.cuda(), w.cuda(), Out)
+    else:
+        op(X.cuda(), Out)
+    ref = orc.rmsnorm_bf16_ref(X, w if weighted else None)
+    assert torch.allclose(Out.cpu().float(), ref.float(), atol=1e-2, rtol=1e-2)
+    assert frac_within_one_ulp(Out, ref) > 0.999
+
+
+# -------------------------------------------------------- QK-norm + RoPE ---
+def _run_rope(ez, tensors, position, B, NQ, NKV, D, S):
+    q, k, v, qw, kw, cos, sin, K0, V0 = tensors
+    Kr, Vr = K0.clone(), V0.clone()
+    q_ref, k_ref = orc.qk_norm_rope_ref(q, k, v, qw, kw, cos, sin, Kr, Vr, position)
+    op = ez.FusedQkNormRopeOp(B, NQ, D, S, position, backend="cuda", num_kv_heads=NKV)
+    args = dev(q, k, v, qw, kw, cos, sin, K0.clone(), V0.clone())
+    q_out, k_out = op(*args)
+    Kc, Vc = args[7].cpu(), args[8].cpu()
+    assert op.check((q_out.cpu(), k_out.cpu()), (q_ref, k_ref))
+    assert frac_within_one_ulp(q_out, q_ref) > 0.999 and frac_within_one_ulp(k_out, k_ref) > 0.999
+    pos = [position] * B if isinstance(position, int) else position
+    for b, p in enumerate(pos):
+        assert torch.allclose(Kc[b, :, p].float(), Kr[b, :, p].float(), atol=1e-2, rtol=1e-2)
+        assert torch.equal(Kc[b, :, p], k_out[b].cpu())  # cache holds exactly what was returned
+        assert torch.equal(Vc[b, :, p], Vr[b, :, p])  # raw copy: bit exact
+        mask = torch.ones(S, dtype=torch.bool)
+        mask[p] = False
+        assert torch.equal(Kc[b][:, mask], K0[b][:, mask]) and torch.equal(Vc[b][:, mask], V0[b][:, mask])
+    for a, t in zip(args[:7], tensors[:7]):
+        assert torch.equal(a.cpu(), t)  # inputs untouched
+
+
+@pytest.mark.parametrize("batch,S,position,NKV", [(1, 128, 0, 8), (1, 1024, 512, 8), (2, 1025, 1024, 8), (1, 4096, 1, 4),
+                                                  (1, 100, 50, 16), (1, 33, 17, 2)])
+def test_qk_norm_rope_reference_cases(ez, batch, S, position, NKV):
+    # the cases of the reference's tests/test_fused_qk_norm_rope.py:52-62, with its N(0,1) norm weights
+    NQ, D = 16, 128
+    g = torch.Generator().manual_seed(42)
+    r = lambda *s: torch.randn(*s, generator=g).bfloat16()
+    cos, sin = orc.rope_tables(S, D)
+    tensors = (r(batch, NQ, D), r(batch, NKV, D), r(batch, NKV, D), r(D), r(D), cos, sin, r(batch, NKV, S, D), r(batch, NKV, S, D))
+    _run_rope(ez, tensors, position, batch, NQ, NKV, D, S)
+
+
+def test_qk_norm_rope_golden(ez):
+    for tag in "ab":
+        g = load_golden(f"qk_norm_rope_{tag}")
+        B, NQ, D = g["q"].shape
+        NKV, S = g["k"].shape[1], g["cos"].shape[0]
+        op = ez.FusedQkNormRopeOp(B, NQ, D, S, g["position"], backend="cuda", num_kv_heads=NKV)
+        Kc, Vc = g["K0"].cuda(), g["V0"].cuda()
+        q_out, k_out = op(*dev(g["q"], g["k"], g["v"], g["qw"], g["kw"], g["cos"], g["sin"]), Kc, Vc)
+        assert torch.allclose(q_out.cpu().float(), g["q_out"].float(), atol=1e-2, rtol=1e-2)
+        assert torch.allclose(k_out.cpu().float(), g["k_out"].float(), atol=1e-2, rtol=1e-2)
+        assert torch.equal(Vc.cpu(), g["V1"])
+        assert torch.allclose(Kc.cpu().float(), g["K1"].float(), atol=1e-2, rtol=1e-2)
+
+
+def test_qk_norm_rope_qwen3_8b_per_row_positions(ez):
+    from ezops_b200 import workloads as wl
+
+    tensors, positions = wl.qk_norm_rope_inputs(batch=32, max_seq_len=8192)
+    _run_rope(ez, tensors, positions, 32, 32, 8, 128, 8192)
+
+
+def test_qk_norm_rope_constructor_checks(ez):
+    with pytest.raises(ValueError, match="power of two"):
+        ez.FusedQkNormRopeOp(1, num_heads=16, head_dim=100, max_seq_len=128, position=0, backend="cuda")
+    with pytest.raises(ValueError, match="position"):
+        ez.FusedQkNormRopeOp(1, num_heads=16, head_dim=128, max_seq_len=128, position=128, backend="cuda")
+    with pytest.raises(ValueError, match="divisible"):
+        ez.FusedQkNormRopeOp(1, num_heads=16, head_dim=128, max_seq_len=128, position=0, num_kv_heads=6, backend="cuda")
+
+
+# ------------------------------------------------------------- attention ---
+def _attn_case(ez, B, H, NKV, S, D, seq_lens=None, seed=0):
+    g = torch.Generator().manual_seed(seed + S)
+    r = lambda *s: torch.randn(*s, generator=g).bfloat16()
+    Q, K, V = r(B, H, 1, D), r(B, NKV, S, D), r(B, NKV, S, D)
+    op = ez.AttnDecodeOp(B, H, S, D, backend="cuda", num_kv_heads=NKV, seq_lens=seq_lens)
+    Qd, Kd, Vd = dev(Q, K, V)
+    out = op(Qd, Kd, Vd)
+    ref = orc.attn_decode_ref(Q, K, V, seq_lens)
+    assert out.shape == ref.shape
+    assert op.check(out.cpu(), ref), (max_abs(out, ref), rel_fro(out, ref))
+    f64 = orc.attn_decode_fp64(Q, K, V, seq_lens)
+    assert rel_fro(out, f64) < 6e-3
+    out2 = op(Qd, Kd, Vd)
+    assert torch.equal(out, out2)  # deterministic
+    assert torch.equal(Kd.cpu(), K) and torch.equal(Vd.cpu(), V) and torch.equal(Qd.cpu(), Q)
+
+
+@pytest.mark.parametrize("B,H,NKV,S,D", [
+    (1, 32, 8, 4096, 128), (1, 16, 8, 1000, 128), (2, 16, 8, 1025, 128), (1, 16, 4, 4096, 128), (1, 16, 8, 1, 128),
+    (3, 8, 8, 33, 128), (1, 16, 1, 300, 128), (2, 64, 8, 777, 128), (2, 8, 2, 77, 64), (1, 4, 4, 64, 64), (1, 4, 2, 65, 64),
+    (4, 32, 8, 8192, 128), (1, 64, 2, 200, 64),
+])
+def test_attn_decode(ez, B, H, NKV, S, D):
+    _attn_case(ez, B, H, NKV, S, D)
+
+
+def test_attn_decode_golden(ez):
+    g = load_golden("attn_decode")
+    B, H, _, D = g["Q"].shape
+    NKV, S = g["K"].shape[1], g["K"].shape[2]
+    out = ez.AttnDecodeOp(B, H, S, D, backend="cuda", num_kv_heads=NKV)(*dev(g["Q"], g["K"], g["V"]))
+    assert torch.allclose(out.cpu().float(), g["out"].float(), atol=1e-2, rtol=1e-2)
+
+
+def test_attn_decode_ragged_lengths(ez):
+    _attn_case(ez, 5, 16, 4, 1500, 128, seq_lens=[1, 64, 65, 1499, 1500])
+    _attn_case(ez, 3, 8, 2, 300, 64, seq_lens=[7, 300, 129])
+
+
+def test_attn_decode_qwen3_8b_batch32_ragged(ez):
+    from ezops_b200 import workloads as wl
+
+    (Q, K, V), lens = wl.attn_decode_inputs()
+    op = ez.AttnDecodeOp(32, 32, 8192, 128, backend="cuda", num_kv_heads=8, seq_lens=lens)
+    out = op(*dev(Q, K, V))
+    ref = orc.attn_decode_ref(Q, K, V, lens)
+    assert op.check(out.cpu(), ref), (max_abs(out, ref), rel_fro(out, ref))
+    assert max_abs(out, ref) <= 2e-2
+
+
+def test_attn_decode_many_small_splits(ez):
+    from ezops_b200 import _lib
+
+    old = _lib.get_tuning("attn_min_chunk")
+    try:
+        _lib.set_tuning(attn_min_chunk=64)
+        _attn_case(ez, 1, 16, 8, 1000, 128, seed=5)
+        _attn_case(ez, 2, 8, 2, 4096, 128, seq_lens=[100, 4096], seed=6)
+    finally:
+        _lib.set_tuning(attn_min_chunk=old)
+
+
+# ----------------------------------------------------------- o_proj + FFN ---
+@pytest.mark.parametrize("batch,shape", [(1, "2b"), (1, "0.6b"), (2, "2b"), (4, "2b"), (8, "2b"), (16, "0.6b"), (1, "8b")])
+def test_fused_o_proj_ffn(ez, batch, shape):
+    from ezops_b200 import workloads as wl
+
+    sh = {"2b": wl.QWEN3_VL_2B, "0.6b": wl.QWEN3_0_6B, "8b": wl.QWEN3_8B}[shape]
+    torch.manual_seed(42)
+    H, I, Q = sh.hidden, sh.inter, sh.q_rows
+    r = lambda *s: torch.randn(*s).bfloat16()
+    # the reference's gen_data scaling (ezops/ops/fused_o_proj_ffn.py:96-105)
+    args = (r(batch, Q), r(batch, H), r(H, Q) * Q**-0.5, r(H), r(I, H) * H**-0.5, r(I, H) * H**-0.5, r(H, I) * I**-0.5)
+    op = ez.FusedOProjFfnOp(batch, H, I, sh.num_heads, sh.head_dim, backend="cuda")
+    dargs = dev(*args)
+    out = op(*dargs)
+    ref = orc.o_proj_ffn_ref(*args)
+    assert op.check(out.cpu(), ref), rel_fro(out, ref)
+    assert rel_fro(out, orc.o_proj_ffn_fp64(*args)) < 1e-2
+    assert torch.equal(op(*dargs), out)
+    for a, t in zip(dargs, args):
+        assert torch.equal(a.cpu(), t)
+
+
+def test_fused_o_proj_ffn_golden(ez):
+    for tag in "ab":
+        g = load_golden(f"o_proj_ffn_{tag}")
+        B, Q = g["attn"].shape
+        H, I = g["Wd"].shape
+        op = ez.FusedOProjFfnOp(B, H, I, Q // 32, 32, backend="cuda")
+        out = op(*dev(*[g[k] for k in ("attn", "residual", "Wo", "post_norm_w", "Wg", "Wu", "Wd")]))
+        assert rel_fro(out, g["out"]) < 1e-2
+
+
+def test_fused_o_proj_ffn_divisibility(ez):
+    with pytest.raises(ValueError, match="divisible"):
+        ez.FusedOProjFfnOp(1, hidden_size=2048, intermediate_size=6200, num_heads=16, head_dim=128, backend="cuda")
+
+
+# ------------------------------------------------------------ decode layer ---
+def _layer_case(ez, batch, seq_len, shape, num_kv_heads=None, std=None, max_abs_bound=None):
+    from ezops_b200 import workloads as wl
+
+    sh = shape if num_kv_heads is None else wl.LayerShape(shape.name, shape.hidden, shape.inter, shape.num_heads,
+                                                          num_kv_heads, shape.head_dim)
+    if std is None:  # the reference's fan-in scaling (ezops/ops/qwen3_dense_decode.py:131-134)
+        torch.manual_seed(42)
+        r = lambda *s: torch.randn(*s).bfloat16()
+        H, I = sh.hidden, sh.inter
+        data = (r(batch, H), r(batch, sh.num_kv_heads, seq_len, sh.head_dim), r(batch, sh.num_kv_heads, seq_len, sh.head_dim),
+                r(sh.q_rows + 2 * sh.kv_rows, H) * H**-0.5, r(H, sh.q_rows) * sh.q_rows**-0.5, r(2 * I, H) * H**-0.5,
+                r(H, I) * I**-0.5)
+    else:
+        data = wl.decode_layer_inputs(sh, batch, seq_len)
+    hidden, K0, V0, Wqkv, Wo, Wgu, Wd = data
+    heads = (sh.num_heads, sh.num_kv_heads, sh.head_dim)
+    Kr, Vr = K0.clone(), V0.clone()
+    ref = orc.qwen3_dense_decode_ref(hidden, Kr, Vr, Wqkv, Wo, Wgu, Wd, *heads)
+
+    op = ez.Qwen3DenseDecodeOp(batch, seq_len, sh.hidden, sh.inter, sh.num_heads, sh.head_dim, backend="cuda",
+                               num_kv_heads=sh.num_kv_heads)
+    dargs = dev(hidden, K0, V0, Wqkv, Wo, Wgu, Wd)
+    out = op(*dargs)
+    Kc, Vc = dargs[1].cpu(), dargs[2].cpu()
+    assert out.shape == ref.shape
+    assert op.check(out.cpu(), ref), rel_fro(out, ref)
+    if max_abs_bound is not None:
+        # max-abs is meaningful only in units of the output's own bf16 spacing
+        assert frac_within_one_ulp(out, ref) > 0.97, frac_within_one_ulp(out, ref)
+    assert torch.allclose(Kc[:, :, -1].float(), Kr[:, :, -1].float(), atol=1e-2, rtol=1e-2)
+    assert torch.allclose(Vc[:, :, -1].float(), Vr[:, :, -1].float(), atol=1e-2, rtol=1e-2)
+    assert torch.equal(Kc[:, :, :-1], K0[:, :, :-1]) and torch.equal(Vc[:, :, :-1], V0[:, :, :-1])
+    f64 = orc.qwen3_dense_decode_fp64(hidden, K0, V0, Wqkv, Wo, Wgu, Wd, *heads)
+    assert rel_fro(out, f64) < 1e-2
+    # second call on the already-updated cache: idempotent and deterministic
+    out2 = op(*dargs)
+    assert torch.equal(out2, out)
+    for a, t in zip((dargs[0],) + dargs[3:], (hidden, Wqkv, Wo, Wgu, Wd)):
+        assert torch.equal(a.cpu(), t)
+    return out, ref
+
+
+@pytest.mark.parametrize("batch,seq_len,num_kv_heads", [(1, 128, 8), (1, 1000, 8), (2, 1025, 8), (1, 4096, 4), (1, 1, 8)])
+def test_decode_layer_reference_cases(ez, batch, seq_len, num_kv_heads):
+    from ezops_b200 import workloads as wl
+
+    _layer_case(ez, batch, seq_len, wl.QWEN3_VL_2B, num_kv_heads)
+
+
+@pytest.mark.parametrize("batch", [1, 8, 32, 64])
+def test_decode_layer_qwen3_8b(ez, batch):
+    from ezops_b200 import workloads as wl
+
+    _layer_case(ez, batch, 4096, wl.QWEN3_8B, std=0.02, max_abs_bound=2e-2)
+
+
+def test_decode_layer_qwen3_32b_small_batch(ez):
+    from ezops_b200 import workloads as wl
+
+    _layer_case(ez, 2, 512, wl.QWEN3_32B, std=0.02)
+
+
+def test_decode_layer_constructor_checks(ez):
+    with pytest.raises(ValueError, match="divisible"):
+        ez.Qwen3DenseDecodeOp(1, 128, num_heads=16, head_dim=128, hidden_size=2048, intermediate_size=6144,
+                              num_kv_heads=6, backend="cuda")
+    with pytest.raises(ValueError, match="head_dim"):
+        ez.Qwen3DenseDecodeOp(1, 128, num_heads=4, head_dim=32, hidden_size=128, intermediate_size=256, backend="cuda")
+    with pytest.raises(ValueError, match="seq_len"):
+        ez.Qwen3DenseDecodeOp(1, 0, num_heads=16, head_dim=128, hidden_size=2048, intermediate_size=6144, backend="cuda")
+
+
+def test_decode_layer_under_cuda_graph(ez):
+    from ezops_b200 import workloads as wl
+
+    sh = wl.QWEN3_VL_2B
+    data = wl.decode_layer_inputs(sh, 1, 512)
+    op = ez.Qwen3DenseDecodeOp(1, 512, sh.hidden, sh.inter, sh.num_heads, sh.head_dim, backend="cuda", num_kv_heads=sh.num_kv_heads)
+    dargs = dev(*data)
+    eager = op(*dargs)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    static = tuple(t.clone() for t in dargs)
+    with torch.cuda.graph(g):
+        captured = op(*static)
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(captured, eager)
+
+
+def test_decode_layer_without_pdl_matches(ez):
+    from ezops_b200 import _lib
+    from ezops_b200 import workloads as wl
+
+    sh = wl.QWEN3_VL_2B
+    data = wl.decode_layer_inputs(sh, 2, 300)
+    op = ez.Qwen3DenseDecodeOp(2, 300, sh.hidden, sh.inter, sh.num_heads, sh.head_dim, backend="cuda", num_kv_heads=sh.num_kv_heads)
+    a = op(*dev(*data))
+    try:
+        _lib.set_tuning(pdl=0)
+        b = op(*dev(*data))
+    finally:
+        _lib.set_tuning(pdl=1)
+    assert torch.equal(a, b)
+
+
+# ----------------------------------------- tensor-parallel parts on one GPU ---
+@pytest.mark.parametrize("tp,batch", [(2, 1), (4, 3), (8, 16)])
+def test_tp_parts_sum_to_the_layer(ez, tp, batch):
+    """All ranks' local parts run one after the other on this GPU, the two sums
+    over ranks done with torch: checks the sharded kernels (fp32 partial
+    epilogue, add + norm prologue) without needing several GPUs."""
+    from ezops_b200 import tp as tpm
+    from ezops_b200 import workloads as wl
+
+    sh = wl.QWEN3_VL_2B if tp < 8 else wl.QWEN3_8B
+    S = 700
+    hidden, K0, V0, Wqkv, Wo, Wgu, Wd = wl.decode_layer_inputs(sh, batch, S)
+    heads = (sh.num_heads, sh.num_kv_heads, sh.head_dim)
+    Kr, Vr = K0.clone(), V0.clone()
+    ref = orc.qwen3_dense_decode_ref(hidden, Kr, Vr, Wqkv, Wo, Wgu, Wd, *heads)
+
+    hid = hidden.cuda()
+    layers, shards, caches = [], [], []
+    for r in range(tp):
+        lay = tpm.TensorParallelDecodeLayer.__new__(tpm.TensorParallelDecodeLayer)
+        lay.group, lay.tp, lay.rank = None, 1, 0  # no process group: sums are done below
+        lay.B, lay.S, lay.H, lay.D = batch, S, sh.hidden, sh.head_dim
+        lay.NH_l, lay.NKV_l, lay.I_l = sh.num_heads // tp, sh.num_kv_heads // tp, sh.inter // tp
+        lay._bufs = None
+        layers.append(lay)
+        shards.append(dev(*tpm.shard_layer_weights(Wqkv, Wo, Wgu, Wd, *heads, tp, r)))
+        caches.append(dev(tpm.shard_kv_cache(K0, tp, r), tpm.shard_kv_cache(V0, tp, r)))
+    bufs = [lay._buffers(hid.device) for lay in layers]
+    for r, lay in enumerate(layers):
+        lay._part_attn(hid, caches[r][0], caches[r][1], shards[r][0], shards[r][1], bufs[r])
+    total_o = sum(b["partial_o"] for b in bufs)
+    for b in bufs:
+        b["partial_o"].copy_(total_o)
+    for r, lay in enumerate(layers):
+        lay._part_ffn(hid, shards[r][2], shards[r][3], bufs[r])
+    total_d = sum(b["partial_d"] for b in bufs)
+    out = torch.empty_like(hid)
+    bufs[0]["partial_d"].copy_(total_d)
+    layers[0]._part_out(out, bufs[0])
+    assert rel_fro(out, ref) < 1e-2, rel_fro(out, ref)
+    n = sh.num_kv_heads // tp
+    for r in range(tp):
+        assert torch.allclose(caches[r][0][:, :, -1].cpu().float(), Kr[:, r * n:(r + 1) * n, -1].float(), atol=1e-2, rtol=1e-2)
+        assert torch.equal(caches[r][0][:, :, :-1].cpu(), K0[:, r * n:(r + 1) * n, :-1])
