@@ -55,6 +55,8 @@ def parse_args():
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a CUDA graph")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--no-cross-call-pdl", action="store_true",
+                    help="order the first kernel of every layer call fully after the previous call")
     return ap.parse_args()
 
 
@@ -196,6 +198,7 @@ def workload_config(args, shape, n):
         "hidden": shape.hidden, "intermediate": shape.inter, "heads": f"{shape.num_heads}q/{shape.num_kv_heads}kv x {shape.head_dim}",
         "parallelism": f"tp{n}",
         "cache_policy": f"inputs larger than L2: steps rotate over {NUM_WEIGHT_SETS} weight+KV sets",
+        "pdl_across_calls": not getattr(args, "no_cross_call_pdl", False),
     }
 
 
@@ -229,6 +232,9 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
     tp = world
+    # A decode loop over resident, immutable weights: let the first kernel of a
+    # layer request its weight tiles while the previous layer's last kernel drains.
+    _lib.set_tuning(pdl_across_calls=0 if args.no_cross_call_pdl else 1)
     steps = args.steps if args.steps is not None else 1000
     warmup = max(3, args.warmup if args.warmup is not None else 20)
     B, S, H, I = args.batch, args.seq_len, shape.hidden, shape.inter

@@ -27,6 +27,8 @@ TUNE = {
     "attn_min_chunk": 4,
     "attn_waves": 5,
     "gemv_kc": 6,
+    "gemv_rows8": 7,
+    "pdl_across_calls": 8,
 }
 
 # name -> (restype, argtypes); every symbol include/ezb200.h declares

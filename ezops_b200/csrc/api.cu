@@ -63,20 +63,30 @@ unsigned int* status_ptr() {
     return p;
 }
 
+static thread_local bool t_chain_first = false;
+void chain_begin() { t_chain_first = true; }
+bool chain_take_first() {
+    const bool f = t_chain_first;
+    t_chain_first = false;
+    return f;
+}
+
 static std::atomic<int> g_tuning[EZB_TUNE_COUNT];
 static std::atomic<bool> g_tuning_ready{false};
 static const int kTuningDefaults[EZB_TUNE_COUNT] = {
     1,    // EZB_TUNE_PDL
-    100,  // EZB_TUNE_GEMV_SMEM_KB
+    220,  // EZB_TUNE_GEMV_SMEM_KB
     0,    // EZB_TUNE_GEMV_PREFETCH (all stages)
     1,    // EZB_TUNE_GEMV_CTAS_PER_SM
-    256,  // EZB_TUNE_ATTN_MIN_CHUNK
+    128,  // EZB_TUNE_ATTN_MIN_CHUNK
     16,   // EZB_TUNE_ATTN_WAVES
     0,    // EZB_TUNE_GEMV_KC (automatic)
+    1,    // EZB_TUNE_GEMV_ROWS8
+    0,    // EZB_TUNE_PDL_ACROSS_CALLS
 };
 static const char* kTuningEnv[EZB_TUNE_COUNT] = {
     "EZB_TUNE_PDL",          "EZB_TUNE_GEMV_SMEM_KB",   "EZB_TUNE_GEMV_PREFETCH", "EZB_TUNE_GEMV_CTAS_PER_SM",
-    "EZB_TUNE_ATTN_MIN_CHUNK", "EZB_TUNE_ATTN_WAVES", "EZB_TUNE_GEMV_KC",
+    "EZB_TUNE_ATTN_MIN_CHUNK", "EZB_TUNE_ATTN_WAVES", "EZB_TUNE_GEMV_KC", "EZB_TUNE_GEMV_ROWS8", "EZB_TUNE_PDL_ACROSS_CALLS",
 };
 
 static void tuning_init() {
@@ -276,6 +286,7 @@ int ezb_gemv_bf16(const void* x, const void* W, void* y, int N, int K, ezb_strea
     g.W0 = static_cast<const bf16*>(W), g.ldw = K, g.N = N, g.K = K, g.B = 1;
     g.x = static_cast<const bf16*>(x), g.ldx = K;
     g.out = y, g.ldout = N;
+    chain_begin();
     EZB_CUDA_TRY(launch_gemv(g, stream));
     return EZB_OK;
 }
@@ -297,6 +308,7 @@ int ezb_gemv_batched_bf16(const void* X, const void* W, void* Y, void* workspace
     g.W0 = static_cast<const bf16*>(W), g.ldw = K, g.N = N, g.K = K, g.B = B;
     g.x = static_cast<const bf16*>(X), g.ldx = K;
     g.out = Y, g.ldout = N;
+    chain_begin();
     EZB_CUDA_TRY(launch_gemv(g, stream));
     return EZB_OK;
 }
@@ -305,6 +317,7 @@ int ezb_rmsnorm_f32(const float* X, float* Out, int rows, int dim, float eps, ez
     EZB_REQUIRE(X && Out, "null pointer");
     EZB_REQUIRE(rows >= 1 && dim >= 1, "rows and dim must be positive");
     EZB_REQUIRE(aligned16(X) && aligned16(Out), "X and Out must be 16-byte aligned");
+    chain_begin();
     EZB_CUDA_TRY(launch_rmsnorm_f32(X, Out, rows, dim, eps, stream));
     return EZB_OK;
 }
@@ -319,6 +332,7 @@ int ezb_rmsnorm_bf16(const void* X, const void* w_or_null, void* Out, int rows, 
     a.w = static_cast<const bf16*>(w_or_null);
     a.y = static_cast<bf16*>(Out), a.ldy = dim;
     a.rows = rows, a.dim = dim, a.eps = eps, a.normalize = 1;
+    chain_begin();
     EZB_CUDA_TRY(launch_row_prep(a, stream));
     return EZB_OK;
 }
@@ -339,6 +353,7 @@ int ezb_qk_norm_rope(const void* q, const void* k, const void* v, const void* qw
     a.q_out = static_cast<bf16*>(q_out), a.k_out = static_cast<bf16*>(k_out);
     a.B = B, a.NQ = NQ, a.NKV = NKV, a.D = D, a.S = S, a.position = position;
     a.positions = positions_or_null, a.eps = eps;
+    chain_begin();
     EZB_CUDA_TRY(launch_qk_norm_rope(a, stream));
     return EZB_OK;
 }
@@ -367,6 +382,7 @@ int ezb_attn_decode(const void* Q, const void* K, const void* V, void* Out, void
     a.seq_lens = seq_lens_or_null;
     a.B = B, a.H = H, a.NKV = NKV, a.S = S, a.D = D;
     a.workspace = workspace;
+    chain_begin();
     EZB_CUDA_TRY(launch_attn_decode(a, stream));
     return EZB_OK;
 }
@@ -389,6 +405,7 @@ int ezb_o_proj_ffn(const void* attn, const void* residual, const void* Wo, const
         set_last_message("workspace missing or smaller than ezb_o_proj_ffn_workspace_bytes()");
         return EZB_ERR_WORKSPACE;
     }
+    chain_begin();
     EZB_CUDA_TRY(launch_o_proj(static_cast<const bf16*>(attn), static_cast<const bf16*>(Wo), B, H, Q,
                                static_cast<const bf16*>(residual), w.x2, false, stream));
     EZB_CUDA_TRY(launch_gate_up(w.x2, nullptr, nullptr, static_cast<const bf16*>(post_norm_w), static_cast<const bf16*>(Wg),
@@ -417,6 +434,7 @@ int ezb_qwen3_decode_layer(const void* hidden, void* K_cache, void* V_cache, con
     }
     const bf16* hid = static_cast<const bf16*>(hidden);
     const bf16* wgu = static_cast<const bf16*>(Wgu);
+    chain_begin();
     EZB_CUDA_TRY(launch_qkv_and_attention(hid, static_cast<bf16*>(K_cache), static_cast<bf16*>(V_cache),
                                           static_cast<const bf16*>(Wqkv), w, B, S, H, NH, NKV, D, eps, stream));
     EZB_CUDA_TRY(launch_o_proj(w.attn_out, static_cast<const bf16*>(Wo), B, H, NH * D, hid, w.x2, false, stream));
@@ -440,6 +458,7 @@ int ezb_qwen3_decode_layer_tp_attn(const void* hidden, void* K_cache, void* V_ca
         set_last_message("workspace missing or smaller than ezb_qwen3_decode_layer_workspace_bytes()");
         return EZB_ERR_WORKSPACE;
     }
+    chain_begin();
     EZB_CUDA_TRY(launch_qkv_and_attention(static_cast<const bf16*>(hidden), static_cast<bf16*>(K_cache),
                                           static_cast<bf16*>(V_cache), static_cast<const bf16*>(Wqkv_local), w, B, S, H,
                                           NH_local, NKV_local, D, eps, stream));
@@ -462,6 +481,7 @@ int ezb_qwen3_decode_layer_tp_ffn(const void* hidden, const float* summed_o, con
         return EZB_ERR_WORKSPACE;
     }
     const bf16* wgu = static_cast<const bf16*>(Wgu_local);
+    chain_begin();
     EZB_CUDA_TRY(launch_gate_up(static_cast<const bf16*>(hidden), summed_o, static_cast<bf16*>(x2), nullptr, wgu,
                                 wgu + (size_t)I_local * H, B, H, I_local, eps, w.h, w.xn, stream));
     EZB_CUDA_TRY(launch_down(w.h, static_cast<const bf16*>(Wd_local), B, H, I_local, nullptr, partial_d, true, stream));
@@ -478,6 +498,7 @@ int ezb_residual_add_f32(const void* x2, const float* summed_d, void* out, int B
     a.add = summed_d, a.ldadd = H;
     a.sum_out = static_cast<bf16*>(out), a.ldsum = H;
     a.rows = B, a.dim = H, a.normalize = 0;
+    chain_begin();
     EZB_CUDA_TRY(launch_row_prep(a, stream));
     return EZB_OK;
 }

@@ -75,24 +75,64 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
     const long long kv_row0 = ((long long)b * p.NKV + kvh) * p.S;
 
     pdl_trigger();
+    // The KV cache is mutable state (an earlier kernel in the stream may have
+    // written a slot of it), so nothing is read before the dependency wait.
     pdl_wait();
 
+    // The first tiles are requested right away, so that their latency overlaps
+    // the query prologue below.
     int len = p.S;
     if (p.seq_lens) len = max(0, min(p.S, p.seq_lens[b]));
     const int c0 = chunk_id * p.chunk;
     const int c1 = min(len, c0 + p.chunk);
     const int nkeys = max(0, c1 - c0);
     const int ntiles = (nkeys + kTileKeys - 1) / kTileKeys;
+    const bool owns_new_slot = p.fuse_new_token && c0 <= p.S - 1 && p.S - 1 < c1;
+
+    auto load_tile = [&](int t) {
+        unsigned char* st = stages + (t % kAttnStages) * STAGE_BYTES;
+        const int key0 = c0 + t * kTileKeys;
+#pragma unroll
+        for (int i = 0; i < (2 * kTileKeys * CPR) / kAttnThreads; ++i) {
+            const int idx = tid + i * kAttnThreads;
+            const int which = idx / (kTileKeys * CPR);
+            const int rem = idx % (kTileKeys * CPR);
+            const int r = rem / CPR, c = rem % CPR;
+            const int key = key0 + r;
+            const bool valid = key < c1;
+            const bf16* src = (which ? p.V : p.K) + (kv_row0 + (valid ? key : 0)) * D + c * 8;
+            const uint32_t dst = smem_u32(st) + which * TILE_BYTES + r * ROW_BYTES + ((c ^ (r & 7)) << 4);
+            cp_async16(dst, src, valid);
+        }
+    };
+    // Tiles of the start-up window (one commit group per tile, in tile order).
+    // The tile that holds slot S-1 is the last one of its CTA; if it falls in
+    // the window it is requested after the new k / v have been written.
+    int early = min(kAttnStages - 1, ntiles);
+    if (owns_new_slot && ntiles <= kAttnStages - 1) early = ntiles - 1;
+    for (int t = 0; t < early; ++t) {
+        load_tile(t);
+        cp_async_commit();
+    }
 
     // ---- queries of this kv group into shared memory (rows >= gn are zero) ----
     {
         const bf16* qsrc = p.fuse_new_token ? p.qkv : p.Q;
         const long long qb = p.fuse_new_token ? p.qkv_bstride : p.q_bstride;
-        for (int idx = tid; idx < 16 * CPR; idx += kAttnThreads) {
+        constexpr int QV = (16 * CPR + kAttnThreads - 1) / kAttnThreads;
+        uint4 qv[QV];
+#pragma unroll
+        for (int u = 0; u < QV; ++u) {  // loads first, stores after: one L2 round trip
+            const int idx = tid + u * kAttnThreads;
             const int row = idx / CPR, c = idx % CPR;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (row < gn) v = *reinterpret_cast<const uint4*>(qsrc + (long long)b * qb + (long long)(kvh * G + g0 + row) * D + c * 8);
-            *reinterpret_cast<uint4*>(q_s + row * QS + c * 8) = v;
+            qv[u] = make_uint4(0, 0, 0, 0);
+            if (idx < 16 * CPR && row < gn)
+                qv[u] = *reinterpret_cast<const uint4*>(qsrc + (long long)b * qb + (long long)(kvh * G + g0 + row) * D + c * 8);
+        }
+#pragma unroll
+        for (int u = 0; u < QV; ++u) {
+            const int idx = tid + u * kAttnThreads;
+            if (idx < 16 * CPR) *reinterpret_cast<uint4*>(q_s + (idx / CPR) * QS + (idx % CPR) * 8) = qv[u];
         }
         __syncthreads();
         if (p.fuse_new_token) {
@@ -111,7 +151,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
                 for (int j = 0; j < D / 32; ++j) q_s[row * QS + lane + j * 32] = __float2bfloat16_rn(x[j] * r);
             }
             // new token's k (normalised) and v into cache slot S-1, by the CTA that will read it
-            if (qt == 0 && c0 <= p.S - 1 && p.S - 1 < c1) {
+            if (qt == 0 && owns_new_slot) {
                 const long long slot = (kv_row0 + p.S - 1) * D;
                 if (warp == 0) {
                     const bf16* ksrc = p.qkv + (long long)b * p.qkv_bstride + p.q_rows + kvh * D;
@@ -148,30 +188,13 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
         qa[kk][3] = *reinterpret_cast<const uint32_t*>(base + (g4 + 8) * QS + 8);
     }
 
-    auto load_tile = [&](int t) {
-        unsigned char* st = stages + (t % kAttnStages) * STAGE_BYTES;
-        const int key0 = c0 + t * kTileKeys;
-#pragma unroll
-        for (int i = 0; i < (2 * kTileKeys * CPR) / kAttnThreads; ++i) {
-            const int idx = tid + i * kAttnThreads;
-            const int which = idx / (kTileKeys * CPR);
-            const int rem = idx % (kTileKeys * CPR);
-            const int r = rem / CPR, c = rem % CPR;
-            const int key = key0 + r;
-            const bool valid = key < c1;
-            const bf16* src = (which ? p.V : p.K) + (kv_row0 + (valid ? key : 0)) * D + c * 8;
-            const uint32_t dst = smem_u32(st) + which * TILE_BYTES + r * ROW_BYTES + ((c ^ (r & 7)) << 4);
-            cp_async16(dst, src, valid);
-        }
-    };
-
     float o[D / 8][4];
 #pragma unroll
     for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY};
     float l_run[2] = {0.f, 0.f};
 
-    for (int t = 0; t < kAttnStages - 1; ++t) {
+    for (int t = early; t < kAttnStages - 1; ++t) {
         if (t < ntiles) load_tile(t);
         cp_async_commit();
     }
@@ -314,21 +337,50 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
     __syncthreads();
     if (!s_is_last) return;
     __threadfence();
-    for (int idx = tid; idx < gn * D; idx += kAttnThreads) {
-        const int row = idx / D, d = idx % D;
+    // Per (split, head): weight 2^(M_c - M) / L.  The records are first copied to
+    // shared memory with one independent load per thread, so the L2 latency is
+    // paid once and not once per split.
+    float* cm = reinterpret_cast<float*>(smem);        // [nchunks][16] split maxima, then weights
+    float* cl = cm + (size_t)p.nchunks * 16;           // [nchunks][16] split sums
+    for (int idx = tid; idx < p.nchunks * gn; idx += kAttnThreads) {
+        const int c = idx / gn, row = idx % gn;
+        const long long rec = ((group * p.nchunks + c) * 16 + row) * 2;
+        cm[c * 16 + row] = __ldcg(&p.part_ml[rec]);
+        cl[c * 16 + row] = __ldcg(&p.part_ml[rec + 1]);
+    }
+    __syncthreads();
+    for (int row = warp; row < gn; row += 4) {  // one warp per head, lanes over splits
         float M = -INFINITY;
-        for (int c = 0; c < p.nchunks; ++c) M = fmaxf(M, __ldcg(&p.part_ml[((group * p.nchunks + c) * 16 + row) * 2]));
-        float O = 0.f, L = 0.f;
-        if (M != -INFINITY) {
-            for (int c = 0; c < p.nchunks; ++c) {
-                const long long it = group * p.nchunks + c;
-                const float f = fast_exp2(__ldcg(&p.part_ml[(it * 16 + row) * 2]) - M);
-                L += f * __ldcg(&p.part_ml[(it * 16 + row) * 2 + 1]);
-                O += f * __ldcg(&p.part_o[(it * 16 + row) * D + d]);
+        for (int c = lane; c < p.nchunks; c += 32) M = fmaxf(M, cm[c * 16 + row]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        float L = 0.f;
+        if (M != -INFINITY)
+            for (int c = lane; c < p.nchunks; c += 32) L += fast_exp2(cm[c * 16 + row] - M) * cl[c * 16 + row];
+        L = warp_sum(L);
+        const float inv = (L > 0.f) ? 1.0f / L : 0.f;
+        for (int c = lane; c < p.nchunks; c += 32)
+            cm[c * 16 + row] = (M != -INFINITY) ? fast_exp2(cm[c * 16 + row] - M) * inv : 0.f;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < gn * (D / 4); idx += kAttnThreads) {
+        const int row = idx / (D / 4), d = (idx % (D / 4)) * 4;
+        const float* po = p.part_o + ((group * p.nchunks) * 16 + row) * D + d;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int c = 0; c < p.nchunks; c += 8) {
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                v[u] = (c + u < p.nchunks) ? __ldcg(reinterpret_cast<const float4*>(po + (long long)(c + u) * 16 * D))
+                                           : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const float f = (c + u < p.nchunks) ? cm[(c + u) * 16 + row] : 0.f;
+                acc.x += f * v[u].x, acc.y += f * v[u].y, acc.z += f * v[u].z, acc.w += f * v[u].w;
             }
         }
-        const float val = (L > 0.f) ? O / L : 0.f;
-        p.Out[(long long)b * p.o_bstride + (long long)(kvh * G + g0 + row) * D + d] = __float2bfloat16_rn(val);
+        bf16* dst = p.Out + (long long)b * p.o_bstride + (long long)(kvh * G + g0 + row) * D + d;
+        *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
     }
     if (tid == 0) p.counters[group] = 0u;  // ready for the next call
 }
@@ -345,6 +397,8 @@ int attn_chunk_keys(int B, int NKV, int S) {
     if (chunk < floor_keys) chunk = floor_keys;
     const long long cap = ((long long)S + kTileKeys - 1) / kTileKeys * kTileKeys;
     if (chunk > cap) chunk = cap;
+    // the combine keeps two floats per (split, head) in shared memory
+    while ((S + chunk - 1) / chunk > 256) chunk += kTileKeys;
     return (int)chunk;
 }
 

@@ -212,6 +212,8 @@ int sm_count();               // SMs of the current device (cached per device)
 int max_smem_optin();         // opt-in shared memory per block of the current device
 int tuning(int key);          // value of a tuning knob (see EZB_TUNE_* in ezb200.h)
 unsigned int* status_ptr();   // device address of the status word on the current device (null on error)
+void chain_begin();           // marks the next launch_pdl() of this thread as the first kernel of a call
+bool chain_take_first();      // true once after chain_begin()
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -229,7 +231,9 @@ cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = tuning(EZB_TUNE_PDL) ? 1 : 0;
+    const bool first = chain_take_first();
+    const bool early_start = tuning(EZB_TUNE_PDL) && (!first || tuning(EZB_TUNE_PDL_ACROSS_CALLS));
+    attr[0].val.programmaticStreamSerializationAllowed = early_start ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);

@@ -22,6 +22,16 @@
 //     before griddepcontrol.wait, because weights never depend on the kernel in
 //     front; only then are activations read.
 // Every mbarrier wait is bounded (see mbar_wait_bounded).
+//
+// Two kernels share this structure:
+//   gemv_rows8_kernel   batch <= 8 with the activations resident: the weights are
+//                       the 8-wide B operand, so a stage is 8 whole weight rows
+//                       (up to 4096 elements = 8 KB per bulk copy, the size at
+//                       which the TMA unit reaches its streaming rate) and the
+//                       batch rows form the A operand;
+//   gemv_stream_kernel  every other case (batch up to 64, activations streamed
+//                       or resident): weights are the 16-row A operand, stages
+//                       are [16 rows x kc].
 #include "launchers.h"
 
 namespace ezb {
@@ -69,6 +79,117 @@ __host__ __device__ constexpr size_t red_bytes() {
 template <int NT, bool XRES, bool PAIR>
 __host__ __device__ constexpr int stage_rows() {
     return kRowBlock * (PAIR ? 2 : 1) + (XRES ? 0 : NT * 8);
+}
+
+
+// Brings the activation block into shared memory (row stride xs_stride
+// elements), optionally adding an fp32 term first and RMS-normalising:
+// statistics in fp32, (x * r [* w]) in fp32, one rounding to bf16.  Called by
+// the 128 consumer threads; `scratch` needs four floats.
+__device__ __forceinline__ void stage_activations(const GemvParams& p, bf16* xs, int xs_stride, float* scratch, int ct,
+                                                  int cw, int lane) {
+    constexpr int U = 8;  // independent 16-byte loads in flight per thread
+    const int nvec = p.K / 8;
+    for (int b = 0; b < p.B; ++b) {
+        const bf16* xrow = p.x + (long long)b * p.ldx;
+        bf16* srow = xs + (size_t)b * xs_stride;
+        float ssq = 0.f;
+        for (int base = 0; base < nvec; base += U * kConsumerThreads) {
+            // all loads of the batch are issued before any of them is used, so the
+            // L2 latency is paid once per batch and not once per vector
+            uint4 raw[U];
+            float4 add0[U], add1[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int i = base + u * kConsumerThreads + ct;
+                if (i < nvec) {
+                    raw[u] = *reinterpret_cast<const uint4*>(xrow + i * 8);
+                    if (p.prologue == PRO_ADD_RMSNORM) {
+                        add0[u] = *reinterpret_cast<const float4*>(p.x_add + (long long)b * p.ldadd + i * 8);
+                        add1[u] = *reinterpret_cast<const float4*>(p.x_add + (long long)b * p.ldadd + i * 8 + 4);
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int i = base + u * kConsumerThreads + ct;
+                if (i < nvec) {
+                    uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+                    if (p.prologue == PRO_ADD_RMSNORM) {
+                        const float add[8] = {add0[u].x, add0[u].y, add0[u].z, add0[u].w,
+                                              add1[u].x, add1[u].y, add1[u].z, add1[u].w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            w[e] = pack_bf16(bf16_lo(w[e]) + round_bf16(add[2 * e]), bf16_hi(w[e]) + round_bf16(add[2 * e + 1]));
+                        if (blockIdx.x == 0 && p.x_sum_out)
+                            *reinterpret_cast<uint4*>(p.x_sum_out + (long long)b * p.ldsum + i * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float lo = bf16_lo(w[e]), hi = bf16_hi(w[e]);
+                        ssq += lo * lo + hi * hi;
+                    }
+                    *reinterpret_cast<uint4*>(srow + i * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+        }
+        if (p.prologue != PRO_NONE) {
+            ssq = warp_sum(ssq);
+            if (lane == 0) scratch[cw] = ssq;
+            named_bar_sync(1, kConsumerThreads);
+            const float tot = scratch[0] + scratch[1] + scratch[2] + scratch[3];
+            const float r = 1.0f / sqrtf(tot / (float)p.K + p.eps);
+            for (int i = ct; i < p.K / 8; i += kConsumerThreads) {
+                uint4 raw = *reinterpret_cast<uint4*>(srow + i * 8);
+                uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+                uint32_t nw[4] = {0u, 0u, 0u, 0u};
+                if (p.norm_w) {
+                    const uint4 q = *reinterpret_cast<const uint4*>(p.norm_w + i * 8);
+                    nw[0] = q.x, nw[1] = q.y, nw[2] = q.z, nw[3] = q.w;
+                }
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float lo = bf16_lo(w[e]) * r, hi = bf16_hi(w[e]) * r;
+                    if (p.norm_w) lo *= bf16_lo(nw[e]), hi *= bf16_hi(nw[e]);
+                    w[e] = pack_bf16(lo, hi);
+                }
+                *reinterpret_cast<uint4*>(srow + i * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            named_bar_sync(1, kConsumerThreads);  // scratch is reused by the next row
+        }
+    }
+    named_bar_sync(1, kConsumerThreads);
+}
+
+// One output element: rounding points follow the torch reference's bf16 staging.
+__device__ __forceinline__ void store_output(const GemvParams& p, int b, int n, float v0, float v1) {
+    const long long o = (long long)b * p.ldout + n;
+    if (p.epilogue == EPI_STORE_F32) {
+        reinterpret_cast<float*>(p.out)[o] = v0;
+    } else if (p.epilogue == EPI_RESIDUAL) {
+        const float res = __bfloat162float(p.residual[(long long)b * p.ldres + n]);
+        reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16_rn(res + round_bf16(v0));
+    } else if (p.epilogue == EPI_SWIGLU) {
+        const float gate = round_bf16(v0), up = round_bf16(v1);
+        reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16_rn(round_bf16(silu_f32(gate)) * up);
+    } else {
+        reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16_rn(v0);
+    }
+}
+
+// Producer's exit path after an abort: wait (bounded) until nothing is still in
+// flight towards this CTA's shared memory.
+__device__ __forceinline__ void drain_after_abort(uint64_t* full_bar, int NS, int issued, unsigned int* status) {
+    const int first = max(0, issued - NS);
+    for (int it = first; it < issued; ++it) {
+        const long long t0 = clock64();
+        while (!mbar_try_wait(smem_u32(&full_bar[it % NS]), (uint32_t)((it / NS) & 1))) {
+            if (clock64() - t0 > kWaitLimitCycles) {
+                report_fault(status, FAULT_GEMV_DRAIN);
+                break;
+            }
+        }
+    }
 }
 
 template <int NT, bool XRES, bool PAIR>
@@ -164,18 +285,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_stream_kernel(const Gemv
         // Leave only when nothing is still in flight towards this CTA's shared
         // memory.  On the normal path the consumers have already waited for
         // every stage, so these waits return at once.
-        if (*abort_flag) {
-            const int first = max(0, issued - NS);
-            for (int it = first; it < issued; ++it) {
-                const long long t0 = clock64();
-                while (!mbar_try_wait(smem_u32(&full_bar[it % NS]), (uint32_t)((it / NS) & 1))) {
-                    if (clock64() - t0 > kWaitLimitCycles) {
-                        report_fault(p.status, FAULT_GEMV_DRAIN);
-                        break;
-                    }
-                }
-            }
-        }
+        if (*abort_flag) drain_after_abort(full_bar, NS, issued, p.status);
         return;
     }
 
@@ -184,62 +294,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_stream_kernel(const Gemv
     const int ct = tid - 32;  // 0..127 among consumer threads
     pdl_wait();
 
-    if (XRES) {
-        // Bring the activation block into shared memory, optionally adding an
-        // fp32 term first and RMS-normalising (statistics in fp32, one rounding).
-        float* scratch = red;  // 4 floats per use, free until the first row block ends
-        for (int b = 0; b < p.B; ++b) {
-            const bf16* xrow = p.x + (long long)b * p.ldx;
-            bf16* srow = xs + (size_t)b * xs_stride;
-            float ssq = 0.f;
-            for (int i = ct; i < p.K / 8; i += kConsumerThreads) {
-                uint4 raw = *reinterpret_cast<const uint4*>(xrow + i * 8);
-                uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-                if (p.prologue == PRO_ADD_RMSNORM) {
-                    const float4 a0 = *reinterpret_cast<const float4*>(p.x_add + (long long)b * p.ldadd + i * 8);
-                    const float4 a1 = *reinterpret_cast<const float4*>(p.x_add + (long long)b * p.ldadd + i * 8 + 4);
-                    const float add[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-#pragma unroll
-                    for (int e = 0; e < 4; ++e)
-                        w[e] = pack_bf16(bf16_lo(w[e]) + round_bf16(add[2 * e]), bf16_hi(w[e]) + round_bf16(add[2 * e + 1]));
-                    raw = make_uint4(w[0], w[1], w[2], w[3]);
-                    if (blockIdx.x == 0 && p.x_sum_out)
-                        *reinterpret_cast<uint4*>(p.x_sum_out + (long long)b * p.ldsum + i * 8) = raw;
-                }
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float lo = bf16_lo(w[e]), hi = bf16_hi(w[e]);
-                    ssq += lo * lo + hi * hi;
-                }
-                *reinterpret_cast<uint4*>(srow + i * 8) = raw;
-            }
-            if (p.prologue != PRO_NONE) {
-                ssq = warp_sum(ssq);
-                if (lane == 0) scratch[cw] = ssq;
-                named_bar_sync(1, kConsumerThreads);
-                const float tot = scratch[0] + scratch[1] + scratch[2] + scratch[3];
-                const float r = 1.0f / sqrtf(tot / (float)p.K + p.eps);
-                for (int i = ct; i < p.K / 8; i += kConsumerThreads) {
-                    uint4 raw = *reinterpret_cast<uint4*>(srow + i * 8);
-                    uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-                    uint32_t nw[4] = {0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u};  // bf16 ones
-                    if (p.norm_w) {
-                        const uint4 q = *reinterpret_cast<const uint4*>(p.norm_w + i * 8);
-                        nw[0] = q.x, nw[1] = q.y, nw[2] = q.z, nw[3] = q.w;
-                    }
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        float lo = bf16_lo(w[e]) * r, hi = bf16_hi(w[e]) * r;
-                        if (p.norm_w) lo *= bf16_lo(nw[e]), hi *= bf16_hi(nw[e]);
-                        w[e] = pack_bf16(lo, hi);
-                    }
-                    *reinterpret_cast<uint4*>(srow + i * 8) = make_uint4(w[0], w[1], w[2], w[3]);
-                }
-                named_bar_sync(1, kConsumerThreads);  // scratch is reused by the next row
-            }
-        }
-        named_bar_sync(1, kConsumerThreads);
-    }
+    if (XRES) stage_activations(p, xs, xs_stride, red, ct, cw, lane);
 
     const int g4 = lane >> 2, t4 = lane & 3;
     for (int rb = 0; rb < nrb; ++rb) {
@@ -309,21 +364,152 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_stream_kernel(const Gemv
                     for (int w = 0; w < kConsumerWarps; ++w) sum += red[(size_t)((w * M + m) * NT + j) * 128 + ct];
                     v[m] = sum;
                 }
-                if (live && b < p.B) {
-                    const long long o = (long long)b * p.ldout + n;
-                    if (p.epilogue == EPI_STORE_F32) {
-                        reinterpret_cast<float*>(p.out)[o] = v[0];
-                    } else if (p.epilogue == EPI_RESIDUAL) {
-                        const float res = __bfloat162float(p.residual[(long long)b * p.ldres + n]);
-                        reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16_rn(res + round_bf16(v[0]));
-                    } else if (PAIR && p.epilogue == EPI_SWIGLU) {
-                        const float gate = round_bf16(v[0]);
-                        const float up = round_bf16(v[M - 1]);
-                        reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16_rn(round_bf16(silu_f32(gate)) * up);
-                    } else {
-                        reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16_rn(v[0]);
-                    }
+                if (live && b < p.B) store_output(p, b, n, v[0], v[M - 1]);
+            }
+        }
+        named_bar_sync(1, kConsumerThreads);
+    }
+}
+
+
+// ---------------------------------------------------------------------------
+// Small-batch kernel (batch <= 8, activations resident).
+//
+// A stage holds 8 weight rows (4 gate + 4 up rows in PAIR mode) of up to 4096
+// elements each, one bulk copy per row.  ldmatrix.x4 on 8 rows x 32 k gives the
+// B fragments of two k-steps; the activations (batch rows 0..7 of the 16-row A
+// tile, rows 8..15 are zero) come from shared memory as 32-bit loads.  The C
+// tile is [batch x 8 weight rows]; two accumulator chains per warp.
+// ---------------------------------------------------------------------------
+static constexpr int kRows8 = 8;
+static constexpr int kRed8Bytes = kConsumerWarps * 64 * (int)sizeof(float);
+
+template <bool PAIR>
+__global__ void __launch_bounds__(kGemvThreads, 1) gemv_rows8_kernel(const GemvParams p) {
+    constexpr int UNITS = PAIR ? 4 : 8;  // outputs per row block
+    extern __shared__ __align__(128) unsigned char smem[];
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem);
+    uint64_t* empty_bar = full_bar + kMaxStages;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 2 * kMaxStages * 8);
+    float* red = reinterpret_cast<float*>(smem + kHeaderBytes);
+    bf16* xs = reinterpret_cast<bf16*>(smem + kHeaderBytes + kRed8Bytes);
+    const int xs_stride = p.K + 8;
+    const size_t xs_bytes = align_up((size_t)p.B * xs_stride * sizeof(bf16), 128);
+    unsigned char* stage_base = smem + kHeaderBytes + kRed8Bytes + xs_bytes;
+    const int ws_stride = p.kc + 8;
+    const uint32_t stage_bytes = (uint32_t)align_up((size_t)kRows8 * ws_stride * sizeof(bf16), 128);
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31;
+    const int NS = p.nstages;
+    const int r0 = (int)((long long)p.N * blockIdx.x / gridDim.x);
+    const int r1 = (int)((long long)p.N * (blockIdx.x + 1) / gridDim.x);
+    const int nrb = (r1 - r0 + UNITS - 1) / UNITS;
+    const int nkc = (p.K + p.kc - 1) / p.kc;
+    const int total = nrb * nkc;
+
+    if (tid == 0) {
+        for (int s = 0; s < NS; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), kConsumerWarps);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    pdl_trigger();
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer
+        auto request = [&](int it) {
+            const int rb = it / nkc, kci = it - rb * nkc, s = it % NS;
+            const int k0 = kci * p.kc;
+            const int len = min(p.kc, p.K - k0);
+            const int unit0 = r0 + rb * UNITS;
+            const int nu = min(UNITS, r1 - unit0);
+            const uint32_t bar = smem_u32(&full_bar[s]);
+            if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)(nu * (PAIR ? 2 : 1) * len * (int)sizeof(bf16)));
+            __syncwarp();
+            if (lane < kRows8) {
+                const int m = PAIR ? (lane >> 2) : 0;
+                const int u = PAIR ? (lane & 3) : lane;
+                if (u < nu) {
+                    const bf16* src = (m ? p.W1 : p.W0) + (long long)(unit0 + u) * p.ldw + k0;
+                    const uint32_t dst = smem_u32(stage_base + (size_t)s * stage_bytes) + (uint32_t)(lane * ws_stride * (int)sizeof(bf16));
+                    bulk_g2s(dst, src, (uint32_t)(len * (int)sizeof(bf16)), bar);
                 }
+            }
+        };
+        // Weights never depend on the kernel in front: fill the ring first.
+        const int npre = min(min(p.prefetch, NS), total);
+        for (int it = 0; it < npre; ++it) request(it);
+        pdl_wait();
+        int issued = npre;
+        for (int it = npre; it < total; ++it) {
+            const int s = it % NS;
+            const uint32_t parity = (uint32_t)(((it / NS) & 1) ^ 1);
+            if (!mbar_wait_bounded(smem_u32(&empty_bar[s]), parity, abort_flag, p.status, FAULT_GEMV_EMPTY_WAIT)) break;
+            request(it);
+            issued = it + 1;
+        }
+        if (*abort_flag) drain_after_abort(full_bar, NS, issued, p.status);
+        return;
+    }
+
+    // ---------------------------------------------------------------- consumers
+    const int cw = warp - 1;
+    const int ct = tid - 32;
+    pdl_wait();
+    stage_activations(p, xs, xs_stride, red, ct, cw, lane);
+
+    const int g4 = lane >> 2, t4 = lane & 3;
+    const bool has_row = g4 < p.B;
+    const bf16* xrow = xs + (size_t)(has_row ? g4 : 0) * xs_stride + t4 * 2;
+    const uint32_t lds_off = (uint32_t)(((lane & 7) * ws_stride + (lane >> 3) * 8) * (int)sizeof(bf16));
+
+    for (int rb = 0; rb < nrb; ++rb) {
+        float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int kci = 0; kci < nkc; ++kci) {
+            const int it = rb * nkc + kci;
+            const int s = it % NS;
+            mbar_wait_bounded(smem_u32(&full_bar[s]), (uint32_t)((it / NS) & 1), abort_flag, p.status, FAULT_GEMV_FULL_WAIT);
+            const int k0 = kci * p.kc;
+            const int len = min(p.kc, p.K - k0);
+            const int nk32 = len >> 5;
+            const uint32_t w_base = smem_u32(stage_base + (size_t)s * stage_bytes) + lds_off;
+            const bf16* xk = xrow + k0;
+#pragma unroll 4
+            for (int k32 = cw; k32 < nk32; k32 += kConsumerWarps) {
+                uint32_t w0, w1, w2, w3;
+                ldsm_x4(w_base + (uint32_t)(k32 * 32 * (int)sizeof(bf16)), w0, w1, w2, w3);
+                uint32_t a0 = 0u, a2 = 0u, c0 = 0u, c2 = 0u;
+                if (has_row) {
+                    const bf16* xb = xk + k32 * 32;
+                    a0 = *reinterpret_cast<const uint32_t*>(xb);
+                    a2 = *reinterpret_cast<const uint32_t*>(xb + 8);
+                    c0 = *reinterpret_cast<const uint32_t*>(xb + 16);
+                    c2 = *reinterpret_cast<const uint32_t*>(xb + 24);
+                }
+                mma_bf16_16816(acc0, a0, 0u, a2, 0u, w0, w1);
+                mma_bf16_16816(acc1, c0, 0u, c2, 0u, w2, w3);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&empty_bar[s]));
+        }
+        // rows 0..7 of the C tile are the batch; this thread holds (batch g4, weight rows 2*t4, 2*t4+1)
+        *reinterpret_cast<float2*>(red + cw * 64 + g4 * 8 + t4 * 2) = make_float2(acc0[0] + acc1[0], acc0[1] + acc1[1]);
+        named_bar_sync(1, kConsumerThreads);
+        if (ct < 64) {
+            const int b = ct >> 3, j = ct & 7;
+            const int n = r0 + rb * UNITS + j;
+            if (j < UNITS && n < r1 && b < p.B && !(*abort_flag)) {
+                float v0 = 0.f, v1 = 0.f;
+#pragma unroll
+                for (int w = 0; w < kConsumerWarps; ++w) {
+                    v0 += red[w * 64 + b * 8 + j];
+                    if (PAIR) v1 += red[w * 64 + b * 8 + j + 4];
+                }
+                store_output(p, b, n, v0, v1);
             }
         }
         named_bar_sync(1, kConsumerThreads);
@@ -409,9 +595,65 @@ static cudaError_t dispatch_nt(const GemvParams& p, const GemvPlan& pl, cudaStre
     }
 }
 
+
+// Plan for the small-batch kernel; returns false when the shape is outside it.
+static bool plan_rows8(const GemvArgs& a, GemvPlan& pl) {
+    if (a.B > 8 || a.K % 32 != 0) return false;
+    if ((size_t)a.B * (a.K + 8) * 2 > 64 * 1024) return false;  // keep room for a deep ring of whole rows
+    const size_t cap = (size_t)max_smem_optin();
+    const size_t xs = align_up((size_t)a.B * (a.K + 8) * 2, 128);
+    const size_t fixed = kHeaderBytes + kRed8Bytes + xs;
+    int best_kc = 0, best_ns = 0;
+    int forced = tuning(EZB_TUNE_GEMV_KC);
+    for (int kc = 4096; kc >= 256; kc >>= 1) {
+        int k = kc > a.K ? a.K : kc;
+        if (forced > 0) k = (forced > a.K ? a.K : forced) / 32 * 32;
+        if (k < 32) k = 32;
+        const size_t stage = align_up((size_t)kRows8 * (k + 8) * 2, 128);
+        if (fixed + 2 * stage > cap) continue;
+        int ns = (int)((cap - fixed) / stage);
+        if (ns > kMaxStages) ns = kMaxStages;
+        if (best_kc == 0 || (best_ns < 3 && ns >= 3)) best_kc = k, best_ns = ns;
+        if (best_ns >= 3 || forced > 0) break;
+    }
+    if (best_kc == 0) return false;
+    pl.NT = 1, pl.xres = true, pl.kc = best_kc;
+    const size_t stage = align_up((size_t)kRows8 * (best_kc + 8) * 2, 128);
+    // no more stages than the longest CTA can use, and at most ~200 KB in flight
+    int ns = best_ns;
+    const int budget_ns = (int)(((size_t)tuning(EZB_TUNE_GEMV_SMEM_KB) * 1024 > fixed
+                                     ? (size_t)tuning(EZB_TUNE_GEMV_SMEM_KB) * 1024 - fixed : 0) / stage);
+    if (budget_ns >= 2 && budget_ns < ns) ns = budget_ns;
+    pl.nstages = ns;
+    int pf = tuning(EZB_TUNE_GEMV_PREFETCH);
+    pl.prefetch = (pf <= 0 || pf > ns) ? ns : pf;
+    pl.smem = fixed + (size_t)ns * stage;
+    int grid = sm_count() * max(1, tuning(EZB_TUNE_GEMV_CTAS_PER_SM));
+    const int units = a.N;
+    if (grid > units) grid = units;
+    pl.grid = grid;
+    return true;
+}
+
+template <bool PAIR>
+static cudaError_t launch_rows8(const GemvParams& p, const GemvPlan& pl, cudaStream_t stream) {
+    auto kernel = gemv_rows8_kernel<PAIR>;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin());
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    return launch_pdl(kernel, dim3(pl.grid), dim3(kGemvThreads), pl.smem, stream, p);
+}
+
 cudaError_t launch_gemv(const GemvArgs& a, cudaStream_t stream) {
     const bool pair = a.epilogue == EPI_SWIGLU;
-    GemvPlan pl = plan_gemv(a, pair);
+    GemvPlan pl;
+    const bool rows8 = tuning(EZB_TUNE_GEMV_ROWS8) != 0 && plan_rows8(a, pl);
+    if (!rows8) pl = plan_gemv(a, pair);
 
     GemvParams p;
     p.W0 = a.W0, p.W1 = a.W1, p.ldw = a.ldw;
@@ -443,6 +685,7 @@ cudaError_t launch_gemv(const GemvArgs& a, cudaStream_t stream) {
         p.prologue = PRO_NONE;
     }
 
+    if (rows8) return pair ? launch_rows8<true>(p, pl, stream) : launch_rows8<false>(p, pl, stream);
     if (pl.xres) return pair ? dispatch_nt<true, true>(p, pl, stream) : dispatch_nt<true, false>(p, pl, stream);
     return pair ? dispatch_nt<false, true>(p, pl, stream) : dispatch_nt<false, false>(p, pl, stream);
 }

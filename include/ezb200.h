@@ -13,9 +13,15 @@
  *     once before its first use; every call leaves it ready for the next one.
  *     One workspace serves one stream at a time.
  *   - Work is enqueued on `stream` and the call returns without synchronising,
- *     so calls can be captured into a CUDA graph.  The kernels of one call, and
- *     consecutive calls on one stream, are chained with programmatic dependent
- *     launch; ordering against other work on the stream is the usual one.
+ *     so calls can be captured into a CUDA graph.  The kernels of one call are
+ *     chained with programmatic dependent launch: a kernel may start while its
+ *     predecessor drains and request WEIGHT tiles early, but reads activations
+ *     and the KV cache only after the predecessor has finished.  The first kernel
+ *     of a call is ordered against earlier work on the stream in the usual way,
+ *     unless EZB_TUNE_PDL_ACROSS_CALLS is set; set it only when the weight
+ *     tensors are not written by work enqueued shortly before the call (a decode
+ *     loop over resident weights), since early weight requests then overlap the
+ *     tail of the previous call.
  *   - Return value: EZB_OK or a negative EZB_ERR_* code.  ezb_strerror() names
  *     the code, ezb_last_error_message() gives the detail of the last failure
  *     on the calling thread.  Arguments are validated before anything is
@@ -50,7 +56,9 @@ typedef struct CUstream_st* ezb_stream_t; /* same type as cudaStream_t */
 #define EZB_TUNE_ATTN_MIN_CHUNK 4   /* smallest KV split, in keys (multiple of 64)                      */
 #define EZB_TUNE_ATTN_WAVES 5       /* target number of KV splits per SM                                */
 #define EZB_TUNE_GEMV_KC 6          /* k-chunk length of a weight stage (0 = automatic)                 */
-#define EZB_TUNE_COUNT 7
+#define EZB_TUNE_GEMV_ROWS8 7       /* 1: batch <= 8 uses the whole-row small-batch kernel (default 1)   */
+#define EZB_TUNE_PDL_ACROSS_CALLS 8 /* 1: the first kernel of a call may also start early (default 0)    */
+#define EZB_TUNE_COUNT 9
 
 int ezb_version(void);
 const char* ezb_strerror(int code);

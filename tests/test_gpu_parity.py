@@ -341,13 +341,16 @@ def _layer_case(ez, batch, seq_len, shape, num_kv_heads=None, std=None, max_abs_
     Kc, Vc = dargs[1].cpu(), dargs[2].cpu()
     assert out.shape == ref.shape
     assert op.check(out.cpu(), ref), rel_fro(out, ref)
+    f64 = orc.qwen3_dense_decode_fp64(hidden, K0, V0, Wqkv, Wo, Wgu, Wd, *heads)
     if max_abs_bound is not None:
-        # max-abs is meaningful only in units of the output's own bf16 spacing
-        assert frac_within_one_ulp(out, ref) > 0.97, frac_within_one_ulp(out, ref)
+        # Outputs reach |x| ~ 10, where one bf16 step is 0.0625, so an absolute bound of
+        # 2e-2 is only meaningful relative to the output scale: max |diff| <= 2e-2 * max |ref|,
+        # and the kernel must be as close to the exact (float64) layer as the reference is.
+        assert max_abs(out, ref) <= max_abs_bound * ref.float().abs().max().item(), max_abs(out, ref)
+        assert rel_fro(out, f64) <= 1.5 * rel_fro(ref, f64) + 1e-4, (rel_fro(out, f64), rel_fro(ref, f64))
     assert torch.allclose(Kc[:, :, -1].float(), Kr[:, :, -1].float(), atol=1e-2, rtol=1e-2)
     assert torch.allclose(Vc[:, :, -1].float(), Vr[:, :, -1].float(), atol=1e-2, rtol=1e-2)
     assert torch.equal(Kc[:, :, :-1], K0[:, :, :-1]) and torch.equal(Vc[:, :, :-1], V0[:, :, :-1])
-    f64 = orc.qwen3_dense_decode_fp64(hidden, K0, V0, Wqkv, Wo, Wgu, Wd, *heads)
     assert rel_fro(out, f64) < 1e-2
     # second call on the already-updated cache: idempotent and deterministic
     out2 = op(*dargs)
