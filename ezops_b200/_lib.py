@@ -47,6 +47,7 @@ SIGNATURES = {
     "ezb_qk_norm_rope": (c_int, [c_void_p] * 11 + [c_int] * 6 + [c_void_p, c_float, c_void_p]),
     "ezb_attn_decode_workspace_bytes": (c_size_t, [c_int] * 5),
     "ezb_attn_decode": (c_int, [c_void_p] * 5 + [c_size_t] + [c_int] * 5 + [c_void_p, c_void_p]),
+    "ezb_attn_decode_static": (c_int, [c_void_p] * 4 + [c_int] * 5 + [c_void_p, c_void_p]),
     "ezb_o_proj_ffn_workspace_bytes": (c_size_t, [c_int] * 4),
     "ezb_o_proj_ffn": (c_int, [c_void_p] * 9 + [c_size_t] + [c_int] * 4 + [c_float, c_void_p]),
     "ezb_qwen3_decode_layer_workspace_bytes": (c_size_t, [c_int] * 7),

@@ -404,6 +404,11 @@ int attn_chunk_keys(int B, int NKV, int S) {
 
 static size_t counters_bytes(int B, int NKV, int nqt) { return ((size_t)B * NKV * nqt * 4 + 255) / 256 * 256; }
 
+size_t attn_counters_bytes(int B, int H, int NKV) {
+    const int G = H / NKV;
+    return counters_bytes(B, NKV, (G + 15) / 16);
+}
+
 size_t attn_workspace_bytes(int B, int H, int NKV, int S, int D) {
     const int G = H / NKV, nqt = (G + 15) / 16;
     const int chunk = attn_chunk_keys(B, NKV, S);

@@ -121,6 +121,21 @@ size_t ezb_attn_decode_workspace_bytes(int B, int H, int NKV, int S, int D);
 int ezb_attn_decode(const void* Q, const void* K, const void* V, void* Out, void* workspace, size_t workspace_bytes,
                     int B, int H, int NKV, int S, int D, const int* seq_lens_or_null, ezb_stream_t stream);
 
+/* The same attention for callers that cannot allocate device memory (a plugin
+ * inside a framework that owns the device heap and passes only inputs and
+ * outputs; a serving loop that must never hit cudaMalloc's device sync).  It has
+ * no counterpart in the reference.  The scratch lives in a fixed array of
+ * EZB_ATTN_STATIC_SCRATCH_BYTES inside the library (held by every GPU that
+ * loads it, until exit); larger shapes are refused with EZB_ERR_WORKSPACE.
+ * Nothing is allocated or freed.  The first call on a device resolves the
+ * array's address and should happen outside stream capture.  All calls on a
+ * device share the array (its zero-initialised part is cleared on `stream`
+ * before every launch), so calls that may overlap on the GPU must be
+ * serialised by the caller. */
+#define EZB_ATTN_STATIC_SCRATCH_BYTES (8u << 20)
+int ezb_attn_decode_static(const void* Q, const void* K, const void* V, void* Out, int B, int H, int NKV, int S, int D,
+                           const int* seq_lens_or_null, ezb_stream_t stream);
+
 /* x2 = residual + attn Wo^T ; out = x2 + (silu(xn Wg^T) * (xn Wu^T)) Wd^T with
  * xn = rmsnorm(x2) * post_norm_w.  Replaces the kernel objects behind
  * FusedOProjFfnOp.forward (ezops/ops/fused_o_proj_ffn.py:84-94; reference
