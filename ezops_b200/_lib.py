@@ -10,7 +10,10 @@ import ctypes
 from ctypes import c_char_p, c_float, c_int, c_size_t, c_uint, c_void_p, POINTER
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "libezb200.so"
+import os
+
+# EZB200_LIBRARY points at an alternative build of the same library (used to A/B kernel variants).
+LIB_PATH = Path(os.environ.get("EZB200_LIBRARY") or Path(__file__).resolve().parent / "libezb200.so")
 
 EZB_OK = 0
 EZB_ERR_INVALID_ARGUMENT = -1
@@ -29,6 +32,10 @@ TUNE = {
     "gemv_kc": 6,
     "gemv_rows8": 7,
     "pdl_across_calls": 8,
+    "l2_prefetch": 9,
+    "l2_prefetch_kb": 10,
+    "gemv_window": 11,
+    "l2_prefetch_attn_kb": 12,
 }
 
 # name -> (restype, argtypes); every symbol include/ezb200.h declares
@@ -39,6 +46,7 @@ SIGNATURES = {
     "ezb_set_tuning": (c_int, [c_int, c_int]),
     "ezb_get_tuning": (c_int, [c_int]),
     "ezb_device_status": (c_int, [POINTER(c_uint), c_int]),
+    "ezb_trace_enable": (c_int, [c_void_p, c_void_p, c_uint]),
     "ezb_gemv_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "ezb_gemv_workspace_bytes": (c_size_t, [c_int, c_int]),
     "ezb_gemv_batched_bf16": (c_int, [c_void_p] * 4 + [c_size_t] + [c_int] * 3 + [c_void_p]),

@@ -63,6 +63,10 @@ unsigned int* status_ptr() {
     return p;
 }
 
+// Timeline tracing: buffers are supplied by the caller (ezb_trace_enable), one set per process.
+static Trace g_trace = {nullptr, nullptr, 0};
+Trace trace_handle() { return g_trace; }
+
 static thread_local bool t_chain_first = false;
 void chain_begin() { t_chain_first = true; }
 bool chain_take_first() {
@@ -83,10 +87,14 @@ static const int kTuningDefaults[EZB_TUNE_COUNT] = {
     0,    // EZB_TUNE_GEMV_KC (automatic)
     1,    // EZB_TUNE_GEMV_ROWS8
     0,    // EZB_TUNE_PDL_ACROSS_CALLS
+    1,    // EZB_TUNE_L2_PREFETCH
+    192,  // EZB_TUNE_L2_PREFETCH_KB
+    0,    // EZB_TUNE_GEMV_WINDOW
+    0,    // EZB_TUNE_L2_PREFETCH_ATTN_KB
 };
 static const char* kTuningEnv[EZB_TUNE_COUNT] = {
     "EZB_TUNE_PDL",          "EZB_TUNE_GEMV_SMEM_KB",   "EZB_TUNE_GEMV_PREFETCH", "EZB_TUNE_GEMV_CTAS_PER_SM",
-    "EZB_TUNE_ATTN_MIN_CHUNK", "EZB_TUNE_ATTN_WAVES", "EZB_TUNE_GEMV_KC", "EZB_TUNE_GEMV_ROWS8", "EZB_TUNE_PDL_ACROSS_CALLS",
+    "EZB_TUNE_ATTN_MIN_CHUNK", "EZB_TUNE_ATTN_WAVES", "EZB_TUNE_GEMV_KC", "EZB_TUNE_GEMV_ROWS8", "EZB_TUNE_PDL_ACROSS_CALLS", "EZB_TUNE_L2_PREFETCH", "EZB_TUNE_L2_PREFETCH_KB", "EZB_TUNE_GEMV_WINDOW", "EZB_TUNE_L2_PREFETCH_ATTN_KB",
 };
 
 static void tuning_init() {
@@ -163,9 +171,30 @@ static int check_common_layer_dims(int B, int H, int I, int Q) {
     return EZB_OK;
 }
 
+static const PrefetchList kNoPrefetch = {};
+
+// Rows [skip_kb, skip_kb + kb) (in KB per CTA) of a following GEMV's weight(s).
+static PrefetchPlan next_rows(const bf16* W0, const bf16* W1, int N, int K, int kb, int skip_kb = 0) {
+    const long long row_bytes = (long long)K * 2 * (W1 ? 2 : 1);
+    long long cap = (long long)kb * 1024 / row_bytes;
+    if (cap < 1) cap = 1;
+    const long long skip = (long long)skip_kb * 1024 / row_bytes;
+    return prefetch_plan_rows(W0, W1, N, K, (int)cap, (int)skip);
+}
+static PrefetchList one_plan(const PrefetchPlan& a) {
+    PrefetchList l = {};
+    l.plan[0] = a;
+    return l;
+}
+static PrefetchList two_plans(const PrefetchPlan& a, const PrefetchPlan& b) {
+    PrefetchList l = {};
+    l.plan[0] = a, l.plan[1] = b;
+    return l;
+}
+
 // o_proj (+residual or fp32 partial), gate/up + SwiGLU, down (+residual or fp32 partial)
 static cudaError_t launch_o_proj(const bf16* attn, const bf16* Wo, int B, int H, int Q, const bf16* residual, void* out,
-                                 bool f32_partial, cudaStream_t stream) {
+                                 bool f32_partial, cudaStream_t stream, const PrefetchList& next = kNoPrefetch) {
     GemvArgs g;
     g.W0 = Wo, g.ldw = Q, g.N = H, g.K = Q, g.B = B;
     g.x = attn, g.ldx = Q;
@@ -173,12 +202,14 @@ static cudaError_t launch_o_proj(const bf16* attn, const bf16* Wo, int B, int H,
     g.epilogue = f32_partial ? EPI_STORE_F32 : EPI_RESIDUAL;
     g.residual = residual, g.ldres = H;
     g.out = out, g.ldout = H;
+    g.next = next;
+    g.trace_id = 3;
     return launch_gemv(g, stream);
 }
 
 static cudaError_t launch_gate_up(const bf16* x, const float* x_add, bf16* x_sum_out, const bf16* norm_w, const bf16* Wg,
                                   const bf16* Wu, int B, int H, int I, float eps, bf16* h, bf16* xn_scratch,
-                                  cudaStream_t stream) {
+                                  cudaStream_t stream, const PrefetchList& next = kNoPrefetch) {
     GemvArgs g;
     g.W0 = Wg, g.W1 = Wu, g.ldw = H, g.N = I, g.K = H, g.B = B;
     g.x = x, g.ldx = H;
@@ -188,11 +219,13 @@ static cudaError_t launch_gate_up(const bf16* x, const float* x_add, bf16* x_sum
     g.epilogue = EPI_SWIGLU;
     g.out = h, g.ldout = I;
     g.xn_scratch = xn_scratch;
+    g.next = next;
+    g.trace_id = 4;
     return launch_gemv(g, stream);
 }
 
 static cudaError_t launch_down(const bf16* h, const bf16* Wd, int B, int H, int I, const bf16* residual, void* out,
-                               bool f32_partial, cudaStream_t stream) {
+                               bool f32_partial, cudaStream_t stream, const PrefetchList& next = kNoPrefetch) {
     GemvArgs g;
     g.W0 = Wd, g.ldw = I, g.N = H, g.K = I, g.B = B;
     g.x = h, g.ldx = I;
@@ -200,11 +233,14 @@ static cudaError_t launch_down(const bf16* h, const bf16* Wd, int B, int H, int 
     g.epilogue = f32_partial ? EPI_STORE_F32 : EPI_RESIDUAL;
     g.residual = residual, g.ldres = H;
     g.out = out, g.ldout = H;
+    g.trace_id = 5;
+    g.next = next;
     return launch_gemv(g, stream);
 }
 
 static cudaError_t launch_qkv_and_attention(const bf16* hidden, bf16* Kc, bf16* Vc, const bf16* Wqkv, const LayerWorkspace& w,
-                                            int B, int S, int H, int NH, int NKV, int D, float eps, cudaStream_t stream) {
+                                            int B, int S, int H, int NH, int NKV, int D, float eps, cudaStream_t stream,
+                                            const bf16* Wo, const PrefetchPlan* after_wo = nullptr) {
     const int rows = (NH + 2 * NKV) * D;
     GemvArgs g;
     g.W0 = Wqkv, g.ldw = H, g.N = rows, g.K = H, g.B = B;
@@ -212,6 +248,10 @@ static cudaError_t launch_qkv_and_attention(const bf16* hidden, bf16* Kc, bf16* 
     g.eps = eps, g.prologue = PRO_RMSNORM, g.epilogue = EPI_STORE;
     g.out = w.qkv, g.ldout = rows;
     g.xn_scratch = w.xn;
+    g.trace_id = 1;
+    // while the projection drains, start pulling the KV cache (if it is small enough to sit in L2)
+    const size_t kv_bytes = (size_t)B * NKV * S * D * 2;
+    if (2 * kv_bytes <= ((size_t)48 << 20)) g.next = one_plan(prefetch_plan_flat(Kc, Vc, kv_bytes));
     cudaError_t e = launch_gemv(g, stream);
     if (e != cudaSuccess) return e;
 
@@ -224,6 +264,11 @@ static cudaError_t launch_qkv_and_attention(const bf16* hidden, bf16* Kc, bf16* 
     a.qkv = w.qkv, a.qkv_bstride = rows;
     a.K_cache_w = Kc, a.V_cache_w = Vc;
     a.eps = eps;
+    // attention is latency-bound at small batch: let HBM stream the output projection meanwhile
+    if ((size_t)H * NH * D * 2 <= ((size_t)64 << 20)) {
+        a.next = one_plan(next_rows(Wo, nullptr, H, NH * D, 1 << 20));
+        if (after_wo) a.next.plan[1] = *after_wo;
+    }
     return launch_attn_decode(a, stream);
 }
 
@@ -265,6 +310,14 @@ int ezb_set_tuning(int key, int value) {
 }
 
 int ezb_get_tuning(int key) { return tuning(key); }
+
+int ezb_trace_enable(void* records, unsigned int* cursor, unsigned int capacity) {
+    g_trace.buf = static_cast<unsigned long long*>(records);
+    g_trace.cursor = cursor;
+    g_trace.capacity = (records && cursor) ? capacity : 0;
+    if (!g_trace.capacity) g_trace.buf = nullptr;
+    return EZB_OK;
+}
 
 int ezb_device_status(unsigned int* status_out_host, int clear) {
     EZB_REQUIRE(status_out_host != nullptr, "status_out_host is null");
@@ -406,10 +459,13 @@ int ezb_o_proj_ffn(const void* attn, const void* residual, const void* Wo, const
         return EZB_ERR_WORKSPACE;
     }
     chain_begin();
+    const int pf_kb = tuning(EZB_TUNE_L2_PREFETCH_KB);
     EZB_CUDA_TRY(launch_o_proj(static_cast<const bf16*>(attn), static_cast<const bf16*>(Wo), B, H, Q,
-                               static_cast<const bf16*>(residual), w.x2, false, stream));
+                               static_cast<const bf16*>(residual), w.x2, false, stream,
+                               one_plan(next_rows(static_cast<const bf16*>(Wg), static_cast<const bf16*>(Wu), I, H, pf_kb))));
     EZB_CUDA_TRY(launch_gate_up(w.x2, nullptr, nullptr, static_cast<const bf16*>(post_norm_w), static_cast<const bf16*>(Wg),
-                                static_cast<const bf16*>(Wu), B, H, I, eps, w.h, w.xn, stream));
+                                static_cast<const bf16*>(Wu), B, H, I, eps, w.h, w.xn, stream,
+                                one_plan(next_rows(static_cast<const bf16*>(Wd), nullptr, H, I, pf_kb))));
     EZB_CUDA_TRY(launch_down(w.h, static_cast<const bf16*>(Wd), B, H, I, w.x2, out, false, stream));
     return EZB_OK;
 }
@@ -435,10 +491,17 @@ int ezb_qwen3_decode_layer(const void* hidden, void* K_cache, void* V_cache, con
     const bf16* hid = static_cast<const bf16*>(hidden);
     const bf16* wgu = static_cast<const bf16*>(Wgu);
     chain_begin();
+    const int pf_kb = tuning(EZB_TUNE_L2_PREFETCH_KB);
+    const int pf_attn_kb = tuning(EZB_TUNE_L2_PREFETCH_ATTN_KB);
+    // attention is latency-bound: besides Wo it pulls the head of the gate/up rows; o_proj then pulls the rows after those
+    const PrefetchPlan gu_head = next_rows(wgu, wgu + (size_t)I * H, I, H, pf_attn_kb);
     EZB_CUDA_TRY(launch_qkv_and_attention(hid, static_cast<bf16*>(K_cache), static_cast<bf16*>(V_cache),
-                                          static_cast<const bf16*>(Wqkv), w, B, S, H, NH, NKV, D, eps, stream));
-    EZB_CUDA_TRY(launch_o_proj(w.attn_out, static_cast<const bf16*>(Wo), B, H, NH * D, hid, w.x2, false, stream));
-    EZB_CUDA_TRY(launch_gate_up(w.x2, nullptr, nullptr, nullptr, wgu, wgu + (size_t)I * H, B, H, I, eps, w.h, w.xn, stream));
+                                          static_cast<const bf16*>(Wqkv), w, B, S, H, NH, NKV, D, eps, stream,
+                                          static_cast<const bf16*>(Wo), pf_attn_kb > 0 ? &gu_head : nullptr));
+    EZB_CUDA_TRY(launch_o_proj(w.attn_out, static_cast<const bf16*>(Wo), B, H, NH * D, hid, w.x2, false, stream,
+                               one_plan(next_rows(wgu, wgu + (size_t)I * H, I, H, pf_kb, pf_attn_kb > 0 ? pf_attn_kb : 0))));
+    EZB_CUDA_TRY(launch_gate_up(w.x2, nullptr, nullptr, nullptr, wgu, wgu + (size_t)I * H, B, H, I, eps, w.h, w.xn, stream,
+                                one_plan(next_rows(static_cast<const bf16*>(Wd), nullptr, H, I, pf_kb))));
     EZB_CUDA_TRY(launch_down(w.h, static_cast<const bf16*>(Wd), B, H, I, w.x2, out, false, stream));
     return EZB_OK;
 }
@@ -461,7 +524,7 @@ int ezb_qwen3_decode_layer_tp_attn(const void* hidden, void* K_cache, void* V_ca
     chain_begin();
     EZB_CUDA_TRY(launch_qkv_and_attention(static_cast<const bf16*>(hidden), static_cast<bf16*>(K_cache),
                                           static_cast<bf16*>(V_cache), static_cast<const bf16*>(Wqkv_local), w, B, S, H,
-                                          NH_local, NKV_local, D, eps, stream));
+                                          NH_local, NKV_local, D, eps, stream, static_cast<const bf16*>(Wo_local)));
     EZB_CUDA_TRY(launch_o_proj(w.attn_out, static_cast<const bf16*>(Wo_local), B, H, NH_local * D, nullptr, partial_o, true,
                                stream));
     return EZB_OK;
@@ -483,7 +546,8 @@ int ezb_qwen3_decode_layer_tp_ffn(const void* hidden, const float* summed_o, con
     const bf16* wgu = static_cast<const bf16*>(Wgu_local);
     chain_begin();
     EZB_CUDA_TRY(launch_gate_up(static_cast<const bf16*>(hidden), summed_o, static_cast<bf16*>(x2), nullptr, wgu,
-                                wgu + (size_t)I_local * H, B, H, I_local, eps, w.h, w.xn, stream));
+                                wgu + (size_t)I_local * H, B, H, I_local, eps, w.h, w.xn, stream,
+                                one_plan(next_rows(static_cast<const bf16*>(Wd_local), nullptr, H, I_local, tuning(EZB_TUNE_L2_PREFETCH_KB)))));
     EZB_CUDA_TRY(launch_down(w.h, static_cast<const bf16*>(Wd_local), B, H, I_local, nullptr, partial_d, true, stream));
     return EZB_OK;
 }

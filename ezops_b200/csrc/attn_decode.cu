@@ -47,6 +47,8 @@ struct AttnParams {
     bf16* K_cache_w;
     bf16* V_cache_w;
     float eps;
+    PrefetchList next;
+    Trace trace;
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -65,6 +67,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned char* stages = smem;
     bf16* q_s = reinterpret_cast<bf16*>(smem + kAttnStages * STAGE_BYTES);
+    bf16* kv_new_s = q_s + 16 * QS;  // [2][D]: the new token's k (normalised) and v, decode-layer mode
     __shared__ int s_is_last;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -74,10 +77,16 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
     const int G = p.G, g0 = qt * 16, gn = min(16, G - g0);
     const long long kv_row0 = ((long long)b * p.NKV + kvh) * p.S;
 
+    unsigned long long* trec = (tid == 0) ? trace_open(p.trace, 9u, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) : nullptr;
     pdl_trigger();
+    // This kernel is latency-bound at small batch; meanwhile HBM can already pull
+    // the next kernel's weights (immutable, so safe before the dependency wait).
+    if (warp == 3) prefetch_next_operands(p.next, lane, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x,
+                                         gridDim.x * gridDim.y * gridDim.z);
     // The KV cache is mutable state (an earlier kernel in the stream may have
     // written a slot of it), so nothing is read before the dependency wait.
     pdl_wait();
+    trace_mark(trec, 3);
 
     // The first tiles are requested right away, so that their latency overlaps
     // the query prologue below.
@@ -106,10 +115,10 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
         }
     };
     // Tiles of the start-up window (one commit group per tile, in tile order).
-    // The tile that holds slot S-1 is the last one of its CTA; if it falls in
-    // the window it is requested after the new k / v have been written.
-    int early = min(kAttnStages - 1, ntiles);
-    if (owns_new_slot && ntiles <= kAttnStages - 1) early = ntiles - 1;
+    // In decode-layer mode slot S-1 still holds stale data when its tile is
+    // requested; the CTA that owns it overwrites that row in shared memory once
+    // the tile has landed (see the loop below), so it needs no global round trip.
+    const int early = min(kAttnStages - 1, ntiles);
     for (int t = 0; t < early; ++t) {
         load_tile(t);
         cp_async_commit();
@@ -150,8 +159,9 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
 #pragma unroll
                 for (int j = 0; j < D / 32; ++j) q_s[row * QS + lane + j * 32] = __float2bfloat16_rn(x[j] * r);
             }
-            // new token's k (normalised) and v into cache slot S-1, by the CTA that will read it
-            if (qt == 0 && owns_new_slot) {
+            // new token's k (normalised) and v: kept in shared memory for the patch below and
+            // written to cache slot S-1 (nobody reads that slot from memory in this kernel)
+            if (owns_new_slot) {
                 const long long slot = (kv_row0 + p.S - 1) * D;
                 if (warp == 0) {
                     const bf16* ksrc = p.qkv + (long long)b * p.qkv_bstride + p.q_rows + kvh * D;
@@ -165,13 +175,20 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
                     ssq = warp_sum(ssq);
                     const float r = 1.0f / sqrtf(ssq / (float)D + p.eps);
 #pragma unroll
-                    for (int j = 0; j < D / 32; ++j) p.K_cache_w[slot + lane + j * 32] = __float2bfloat16_rn(x[j] * r);
+                    for (int j = 0; j < D / 32; ++j) {
+                        const bf16 kn = __float2bfloat16_rn(x[j] * r);
+                        kv_new_s[lane + j * 32] = kn;
+                        if (qt == 0) p.K_cache_w[slot + lane + j * 32] = kn;
+                    }
                 } else if (warp == 1) {
                     const bf16* vsrc = p.qkv + (long long)b * p.qkv_bstride + p.q_rows + p.kv_rows + kvh * D;
 #pragma unroll
-                    for (int j = 0; j < D / 32; ++j) p.V_cache_w[slot + lane + j * 32] = vsrc[lane + j * 32];
+                    for (int j = 0; j < D / 32; ++j) {
+                        const bf16 vn = vsrc[lane + j * 32];
+                        kv_new_s[D + lane + j * 32] = vn;
+                        if (qt == 0) p.V_cache_w[slot + lane + j * 32] = vn;
+                    }
                 }
-                __threadfence();
             }
             __syncthreads();
         }
@@ -201,8 +218,19 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
     for (int t = 0; t < ntiles; ++t) {
         cp_async_wait<kAttnStages - 2>();
         __syncthreads();
+        if (t == 0) trace_mark(trec, 4);
         if (t + kAttnStages - 1 < ntiles) load_tile(t + kAttnStages - 1);
         cp_async_commit();
+        if (owns_new_slot && t == ntiles - 1) {
+            // overwrite the stale row of slot S-1 in this tile with the new token's k and v
+            const int r = p.S - 1 - (c0 + t * kTileKeys);
+            if (tid < 2 * CPR) {
+                const int which = tid / CPR, c = tid % CPR;
+                unsigned char* dst = stages + (t % kAttnStages) * STAGE_BYTES + which * TILE_BYTES + r * ROW_BYTES + ((c ^ (r & 7)) << 4);
+                *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(kv_new_s + which * D + c * 8);
+            }
+            __syncthreads();
+        }
 
         const unsigned char* st = stages + (t % kAttnStages) * STAGE_BYTES;
         const uint32_t k_s = smem_u32(st), v_s = k_s + TILE_BYTES;
@@ -325,64 +353,119 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
             }
         }
     }
-    if (p.nchunks == 1) return;
+    if (p.nchunks == 1) {
+        trace_mark(trec, 5);
+        return;
+    }
 
     // ---- the last CTA of this (row, kv head, q tile) folds the splits together ----
-    __threadfence();
+    // One acq_rel atomic after the barrier both publishes this CTA's records (the
+    // barrier orders the other threads' stores before it) and, for the CTA that
+    // draws the last ticket, makes every other CTA's records visible.
     __syncthreads();
     if (tid == 0) {
-        const unsigned int prev = atomicAdd(&p.counters[group], 1u);
+        unsigned int prev;
+        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(prev) : "l"(p.counters + group) : "memory");
         s_is_last = (prev == (unsigned int)(p.nchunks - 1));
     }
     __syncthreads();
-    if (!s_is_last) return;
-    __threadfence();
-    // Per (split, head): weight 2^(M_c - M) / L.  The records are first copied to
-    // shared memory with one independent load per thread, so the L2 latency is
-    // paid once and not once per split.
-    float* cm = reinterpret_cast<float*>(smem);        // [nchunks][16] split maxima, then weights
-    float* cl = cm + (size_t)p.nchunks * 16;           // [nchunks][16] split sums
-    for (int idx = tid; idx < p.nchunks * gn; idx += kAttnThreads) {
-        const int c = idx / gn, row = idx % gn;
-        const long long rec = ((group * p.nchunks + c) * 16 + row) * 2;
-        cm[c * 16 + row] = __ldcg(&p.part_ml[rec]);
-        cl[c * 16 + row] = __ldcg(&p.part_ml[rec + 1]);
+    if (!s_is_last) {
+        trace_mark(trec, 5);
+        return;
     }
-    __syncthreads();
-    for (int row = warp; row < gn; row += 4) {  // one warp per head, lanes over splits
-        float M = -INFINITY;
-        for (int c = lane; c < p.nchunks; c += 32) M = fmaxf(M, cm[c * 16 + row]);
+    if (p.nchunks <= 32) {
+        // Fast path: every thread owns four output dims of one head and issues all
+        // its loads up front (32 split records + the first 16 partial vectors), so
+        // the whole fold costs two L2 round trips.
+        for (int idx = tid; idx < gn * (D / 4); idx += kAttnThreads) {
+            const int row = idx / (D / 4), d = (idx % (D / 4)) * 4;
+            const float* pm = p.part_ml + ((group * p.nchunks) * 16 + row) * 2;
+            const float* po = p.part_o + ((group * p.nchunks) * 16 + row) * D + d;
+            float2 ml[32];
+            float4 v[16];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-        float L = 0.f;
-        if (M != -INFINITY)
-            for (int c = lane; c < p.nchunks; c += 32) L += fast_exp2(cm[c * 16 + row] - M) * cl[c * 16 + row];
-        L = warp_sum(L);
-        const float inv = (L > 0.f) ? 1.0f / L : 0.f;
-        for (int c = lane; c < p.nchunks; c += 32)
-            cm[c * 16 + row] = (M != -INFINITY) ? fast_exp2(cm[c * 16 + row] - M) * inv : 0.f;
-    }
-    __syncthreads();
-    for (int idx = tid; idx < gn * (D / 4); idx += kAttnThreads) {
-        const int row = idx / (D / 4), d = (idx % (D / 4)) * 4;
-        const float* po = p.part_o + ((group * p.nchunks) * 16 + row) * D + d;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int c = 0; c < p.nchunks; c += 8) {
-            float4 v[8];
+            for (int c = 0; c < 32; ++c)
+                ml[c] = (c < p.nchunks) ? __ldcg(reinterpret_cast<const float2*>(pm + (long long)c * 32)) : make_float2(-INFINITY, 0.f);
 #pragma unroll
-            for (int u = 0; u < 8; ++u)
-                v[u] = (c + u < p.nchunks) ? __ldcg(reinterpret_cast<const float4*>(po + (long long)(c + u) * 16 * D))
-                                           : make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int c = 0; c < 16; ++c)
+                v[c] = (c < p.nchunks) ? __ldcg(reinterpret_cast<const float4*>(po + (long long)c * 16 * D)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            float M = -INFINITY;
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const float f = (c + u < p.nchunks) ? cm[(c + u) * 16 + row] : 0.f;
-                acc.x += f * v[u].x, acc.y += f * v[u].y, acc.z += f * v[u].z, acc.w += f * v[u].w;
+            for (int c = 0; c < 32; ++c) M = fmaxf(M, ml[c].x);
+            float L = 0.f;
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+                ml[c].x = (M != -INFINITY) ? fast_exp2(ml[c].x - M) : 0.f;
+                L += ml[c].x * ml[c].y;
             }
+            const float inv = (L > 0.f) ? 1.0f / L : 0.f;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                const float f = ml[c].x;
+                acc.x += f * v[c].x, acc.y += f * v[c].y, acc.z += f * v[c].z, acc.w += f * v[c].w;
+            }
+            if (p.nchunks > 16) {
+#pragma unroll
+                for (int c = 0; c < 16; ++c)
+                    v[c] = (c + 16 < p.nchunks) ? __ldcg(reinterpret_cast<const float4*>(po + (long long)(c + 16) * 16 * D))
+                                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int c = 0; c < 16; ++c) {
+                    const float f = ml[c + 16].x;
+                    acc.x += f * v[c].x, acc.y += f * v[c].y, acc.z += f * v[c].z, acc.w += f * v[c].w;
+                }
+            }
+            bf16* dst = p.Out + (long long)b * p.o_bstride + (long long)(kvh * G + g0 + row) * D + d;
+            *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
         }
-        bf16* dst = p.Out + (long long)b * p.o_bstride + (long long)(kvh * G + g0 + row) * D + d;
-        *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
+    } else {
+        // General path: split weights through shared memory.
+        float* cm = reinterpret_cast<float*>(smem);        // [nchunks][16] split maxima, then weights
+        float* cl = cm + (size_t)p.nchunks * 16;           // [nchunks][16] split sums
+        for (int idx = tid; idx < p.nchunks * gn; idx += kAttnThreads) {
+            const int c = idx / gn, row = idx % gn;
+            const long long rec = ((group * p.nchunks + c) * 16 + row) * 2;
+            cm[c * 16 + row] = __ldcg(&p.part_ml[rec]);
+            cl[c * 16 + row] = __ldcg(&p.part_ml[rec + 1]);
+        }
+        __syncthreads();
+        for (int row = warp; row < gn; row += 4) {  // one warp per head, lanes over splits
+            float M = -INFINITY;
+            for (int c = lane; c < p.nchunks; c += 32) M = fmaxf(M, cm[c * 16 + row]);
+#pragma unroll
+            for (int o2 = 16; o2 > 0; o2 >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o2));
+            float L = 0.f;
+            if (M != -INFINITY)
+                for (int c = lane; c < p.nchunks; c += 32) L += fast_exp2(cm[c * 16 + row] - M) * cl[c * 16 + row];
+            L = warp_sum(L);
+            const float inv = (L > 0.f) ? 1.0f / L : 0.f;
+            for (int c = lane; c < p.nchunks; c += 32)
+                cm[c * 16 + row] = (M != -INFINITY) ? fast_exp2(cm[c * 16 + row] - M) * inv : 0.f;
+        }
+        __syncthreads();
+        for (int idx = tid; idx < gn * (D / 4); idx += kAttnThreads) {
+            const int row = idx / (D / 4), d = (idx % (D / 4)) * 4;
+            const float* po = p.part_o + ((group * p.nchunks) * 16 + row) * D + d;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int c = 0; c < p.nchunks; c += 16) {
+                float4 v[16];
+#pragma unroll
+                for (int u = 0; u < 16; ++u)
+                    v[u] = (c + u < p.nchunks) ? __ldcg(reinterpret_cast<const float4*>(po + (long long)(c + u) * 16 * D))
+                                               : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int u = 0; u < 16; ++u) {
+                    const float f = (c + u < p.nchunks) ? cm[(c + u) * 16 + row] : 0.f;
+                    acc.x += f * v[u].x, acc.y += f * v[u].y, acc.z += f * v[u].z, acc.w += f * v[u].w;
+                }
+            }
+            bf16* dst = p.Out + (long long)b * p.o_bstride + (long long)(kvh * G + g0 + row) * D + d;
+            *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
+        }
     }
     if (tid == 0) p.counters[group] = 0u;  // ready for the next call
+    trace_mark(trec, 5);
 }
 
 // ---------------------------------------------------------------------------
@@ -420,7 +503,7 @@ size_t attn_workspace_bytes(int B, int H, int NKV, int S, int D) {
 template <int D>
 static cudaError_t launch_attn_instance(const AttnParams& p, cudaStream_t stream) {
     auto kernel = attn_decode_kernel<D>;
-    constexpr size_t smem = (size_t)kAttnStages * 2 * kTileKeys * D * 2 + 16 * (D + 8) * 2;
+    constexpr size_t smem = (size_t)kAttnStages * 2 * kTileKeys * D * 2 + 16 * (D + 8) * 2 + 2 * D * 2;
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -451,6 +534,9 @@ cudaError_t launch_attn_decode(const AttnArgs& a, cudaStream_t stream) {
     p.q_rows = a.H * a.D, p.kv_rows = a.NKV * a.D;
     p.K_cache_w = a.K_cache_w, p.V_cache_w = a.V_cache_w;
     p.eps = a.eps;
+    p.next = a.next;
+    if (!tuning(EZB_TUNE_L2_PREFETCH)) p.next.plan[0].units = p.next.plan[1].units = 0;
+    p.trace = trace_handle();
     if (a.D == 128) return launch_attn_instance<128>(p, stream);
     return launch_attn_instance<64>(p, stream);
 }

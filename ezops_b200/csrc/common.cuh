@@ -38,6 +38,35 @@ __device__ __forceinline__ void report_fault(unsigned int* status, unsigned int 
 static constexpr long long kWaitLimitCycles = 2000000000LL;
 
 // ---------------------------------------------------------------------------
+// Optional timeline tracing (off unless ezb_trace_enable() was called): thread 0
+// of every CTA records %globaltimer at entry, after the dependency wait, when
+// its first data arrived and at exit.  One record = 6 x u64:
+// {kernel id, block index, t_entry, t_dep, t_data, t_exit} in nanoseconds.
+// ---------------------------------------------------------------------------
+struct Trace {
+    unsigned long long* buf;
+    unsigned int* cursor;
+    unsigned int capacity;
+};
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ unsigned long long* trace_open(const Trace& tr, unsigned int kernel_id, unsigned int block) {
+    if (!tr.buf) return nullptr;
+    const unsigned int slot = atomicAdd(tr.cursor, 1u);
+    if (slot >= tr.capacity) return nullptr;
+    unsigned long long* r = tr.buf + (size_t)slot * 6;
+    r[0] = kernel_id, r[1] = block, r[2] = global_ns(), r[3] = 0, r[4] = 0, r[5] = 0;
+    return r;
+}
+__device__ __forceinline__ void trace_mark(unsigned long long* rec, int field) {
+    if (rec) rec[field] = global_ns();
+}
+
+// ---------------------------------------------------------------------------
 // Address helpers
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -101,6 +130,58 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uin
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
         "l"(src), "r"(bytes), "r"(bar)
         : "memory");
+}
+
+// ---------------------------------------------------------------------------
+// L2 prefetch of what the NEXT kernel of a chain will stream first.  A kernel
+// whose own requests are all issued (or that is latency-bound anyway) asks the
+// memory system to pull the successor's leading weight bytes into L2, so HBM
+// keeps working across the kernel boundary and the successor's ring fills from
+// L2.  `units` contiguous units of `unit_bytes` are split over `next_grid` CTAs
+// the way the successor splits its rows; each share is capped at `cap_units`.
+// ---------------------------------------------------------------------------
+struct PrefetchPlan {
+    const void* base[2];
+    long long unit_bytes;
+    int units;
+    int next_grid;
+    int cap_units;
+    int skip_units;  // leading units of every share that an earlier kernel already pulled
+};
+struct PrefetchList {
+    PrefetchPlan plan[2];
+};
+
+__device__ __forceinline__ void prefetch_l2_bulk(const void* ptr, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr), "r"(bytes) : "memory");
+}
+
+// Called by one warp; CTA `cta` of `grid` takes the shares cta, cta+grid, ...
+__device__ __forceinline__ void prefetch_next_operand(const PrefetchPlan& pf, int lane, int cta, int grid) {
+    if (pf.units <= 0 || pf.next_grid <= 0) return;
+    constexpr long long kPiece = 16384;
+    for (int c = cta; c < pf.next_grid; c += grid) {
+        const long long u0 = (long long)pf.units * c / pf.next_grid + pf.skip_units;
+        const long long u1 = (long long)pf.units * (c + 1) / pf.next_grid;
+        long long n = u1 - u0;
+        if (n <= 0) continue;
+        if (n > pf.cap_units) n = pf.cap_units;
+        const long long bytes = n * pf.unit_bytes;
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+            if (!pf.base[m]) continue;
+            const char* b = static_cast<const char*>(pf.base[m]) + u0 * pf.unit_bytes;
+            for (long long off = (long long)lane * kPiece; off < bytes; off += 32 * kPiece) {
+                const long long left = bytes - off;
+                prefetch_l2_bulk(b + off, (uint32_t)(left < kPiece ? left : kPiece));
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void prefetch_next_operands(const PrefetchList& l, int lane, int cta, int grid) {
+    prefetch_next_operand(l.plan[0], lane, cta, grid);
+    prefetch_next_operand(l.plan[1], lane, cta, grid);
 }
 
 // ---------------------------------------------------------------------------
@@ -212,6 +293,7 @@ int sm_count();               // SMs of the current device (cached per device)
 int max_smem_optin();         // opt-in shared memory per block of the current device
 int tuning(int key);          // value of a tuning knob (see EZB_TUNE_* in ezb200.h)
 unsigned int* status_ptr();   // device address of the status word on the current device (null on error)
+Trace trace_handle();         // tracing buffers of the current device (buf == null when disabled)
 void chain_begin();           // marks the next launch_pdl() of this thread as the first kernel of a call
 bool chain_take_first();      // true once after chain_begin()
 

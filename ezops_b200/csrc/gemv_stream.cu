@@ -36,7 +36,10 @@
 
 namespace ezb {
 
-static constexpr int kConsumerWarps = 4;
+#ifndef EZB_CONSUMER_WARPS
+#define EZB_CONSUMER_WARPS 8
+#endif
+static constexpr int kConsumerWarps = EZB_CONSUMER_WARPS;
 static constexpr int kConsumerThreads = kConsumerWarps * 32;
 static constexpr int kGemvThreads = 32 + kConsumerThreads;
 static constexpr int kMaxStages = 8;
@@ -64,7 +67,11 @@ struct GemvParams {
     int kc;        // k elements per stage (multiple of 16)
     int nstages;   // ring depth
     int prefetch;  // stages requested before the dependency wait
+    int window;    // at most this many stages requested but not yet landed (0 = no limit)
     unsigned int* status;
+    PrefetchList next;
+    Trace trace;
+    int trace_id;
 };
 
 __host__ __device__ constexpr size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -86,6 +93,35 @@ __host__ __device__ constexpr int stage_rows() {
 // elements), optionally adding an fp32 term first and RMS-normalising:
 // statistics in fp32, (x * r [* w]) in fp32, one rounding to bf16.  Called by
 // the 128 consumer threads; `scratch` needs four floats.
+// With PERMUTE32 every group of 32 elements is stored as four 16-byte blocks,
+// block t holding the element pairs (j*8 + 2t, j*8 + 2t + 1), j = 0..3: exactly
+// the four words that lane t of a quad feeds to two consecutive k-steps as its
+// A fragments, so the rows8 kernel fetches them with one 128-bit load.
+template <bool PERMUTE32>
+__device__ __forceinline__ void store_x8(bf16* srow, int i, const uint32_t (&w)[4]) {
+    if (!PERMUTE32) {
+        *reinterpret_cast<uint4*>(srow + i * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+    } else {
+        uint32_t* base = reinterpret_cast<uint32_t*>(srow + (i >> 2) * 32);  // start of the 32-element group
+        const int j = i & 3;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) base[t * 4 + j] = w[t];
+    }
+}
+template <bool PERMUTE32>
+__device__ __forceinline__ void load_x8(const bf16* srow, int i, uint32_t (&w)[4]) {
+    if (!PERMUTE32) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(srow + i * 8);
+        w[0] = raw.x, w[1] = raw.y, w[2] = raw.z, w[3] = raw.w;
+    } else {
+        const uint32_t* base = reinterpret_cast<const uint32_t*>(srow + (i >> 2) * 32);
+        const int j = i & 3;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) w[t] = base[t * 4 + j];
+    }
+}
+
+template <bool PERMUTE32>
 __device__ __forceinline__ void stage_activations(const GemvParams& p, bf16* xs, int xs_stride, float* scratch, int ct,
                                                   int cw, int lane) {
     constexpr int U = 8;  // independent 16-byte loads in flight per thread
@@ -129,7 +165,7 @@ __device__ __forceinline__ void stage_activations(const GemvParams& p, bf16* xs,
                         const float lo = bf16_lo(w[e]), hi = bf16_hi(w[e]);
                         ssq += lo * lo + hi * hi;
                     }
-                    *reinterpret_cast<uint4*>(srow + i * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                    store_x8<PERMUTE32>(srow, i, w);
                 }
             }
         }
@@ -137,11 +173,13 @@ __device__ __forceinline__ void stage_activations(const GemvParams& p, bf16* xs,
             ssq = warp_sum(ssq);
             if (lane == 0) scratch[cw] = ssq;
             named_bar_sync(1, kConsumerThreads);
-            const float tot = scratch[0] + scratch[1] + scratch[2] + scratch[3];
+            float tot = 0.f;
+#pragma unroll
+            for (int w = 0; w < kConsumerWarps; ++w) tot += scratch[w];
             const float r = 1.0f / sqrtf(tot / (float)p.K + p.eps);
             for (int i = ct; i < p.K / 8; i += kConsumerThreads) {
-                uint4 raw = *reinterpret_cast<uint4*>(srow + i * 8);
-                uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+                uint32_t w[4];
+                load_x8<PERMUTE32>(srow, i, w);
                 uint32_t nw[4] = {0u, 0u, 0u, 0u};
                 if (p.norm_w) {
                     const uint4 q = *reinterpret_cast<const uint4*>(p.norm_w + i * 8);
@@ -153,7 +191,7 @@ __device__ __forceinline__ void stage_activations(const GemvParams& p, bf16* xs,
                     if (p.norm_w) lo *= bf16_lo(nw[e]), hi *= bf16_hi(nw[e]);
                     w[e] = pack_bf16(lo, hi);
                 }
-                *reinterpret_cast<uint4*>(srow + i * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                store_x8<PERMUTE32>(srow, i, w);
             }
             named_bar_sync(1, kConsumerThreads);  // scratch is reused by the next row
         }
@@ -286,6 +324,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_stream_kernel(const Gemv
         // memory.  On the normal path the consumers have already waited for
         // every stage, so these waits return at once.
         if (*abort_flag) drain_after_abort(full_bar, NS, issued, p.status);
+        else prefetch_next_operands(p.next, lane, blockIdx.x, gridDim.x);
         return;
     }
 
@@ -294,7 +333,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_stream_kernel(const Gemv
     const int ct = tid - 32;  // 0..127 among consumer threads
     pdl_wait();
 
-    if (XRES) stage_activations(p, xs, xs_stride, red, ct, cw, lane);
+    if (XRES) stage_activations<false>(p, xs, xs_stride, red, ct, cw, lane);
 
     const int g4 = lane >> 2, t4 = lane & 3;
     for (int rb = 0; rb < nrb; ++rb) {
@@ -347,7 +386,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_stream_kernel(const Gemv
                 *reinterpret_cast<float4*>(red + ((size_t)((cw * M + m) * NT + j) * 32 + lane) * 4) =
                     make_float4(acc[m][j][0], acc[m][j][1], acc[m][j][2], acc[m][j][3]);
         named_bar_sync(1, kConsumerThreads);
-        {
+        if (ct < 128) {
             const int fl = ct >> 2, e = ct & 3;
             const int row = (fl >> 2) + ((e >= 2) ? 8 : 0);
             const int col = (fl & 3) * 2 + (e & 1);
@@ -382,7 +421,9 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_stream_kernel(const Gemv
 // tile is [batch x 8 weight rows]; two accumulator chains per warp.
 // ---------------------------------------------------------------------------
 static constexpr int kRows8 = 8;
-static constexpr int kRed8Bytes = kConsumerWarps * 64 * (int)sizeof(float);
+static constexpr int kXsPad8 = 32;  // activation rows 64 bytes apart in bank space: 128-bit loads of a quarter warp never collide
+static constexpr int kRed8Bytes = 2 * kConsumerWarps * 64 * (int)sizeof(float);  // double buffered
+static constexpr int kResidualSlots = 1024;  // residual values (batch x rows of this CTA) kept in shared memory
 
 template <bool PAIR>
 __global__ void __launch_bounds__(kGemvThreads, 1) gemv_rows8_kernel(const GemvParams p) {
@@ -392,10 +433,11 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_rows8_kernel(const GemvP
     uint64_t* empty_bar = full_bar + kMaxStages;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 2 * kMaxStages * 8);
     float* red = reinterpret_cast<float*>(smem + kHeaderBytes);
-    bf16* xs = reinterpret_cast<bf16*>(smem + kHeaderBytes + kRed8Bytes);
-    const int xs_stride = p.K + 8;
+    float* res_s = reinterpret_cast<float*>(smem + kHeaderBytes + kRed8Bytes);
+    bf16* xs = reinterpret_cast<bf16*>(smem + kHeaderBytes + kRed8Bytes + kResidualSlots * sizeof(float));
+    const int xs_stride = p.K + kXsPad8;
     const size_t xs_bytes = align_up((size_t)p.B * xs_stride * sizeof(bf16), 128);
-    unsigned char* stage_base = smem + kHeaderBytes + kRed8Bytes + xs_bytes;
+    unsigned char* stage_base = reinterpret_cast<unsigned char*>(xs) + xs_bytes;
     const int ws_stride = p.kc + 8;
     const uint32_t stage_bytes = (uint32_t)align_up((size_t)kRows8 * ws_stride * sizeof(bf16), 128);
 
@@ -416,6 +458,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_rows8_kernel(const GemvP
         *abort_flag = 0;
         mbar_fence_init();
     }
+    unsigned long long* trec = (tid == 32) ? trace_open(p.trace, (unsigned)p.trace_id, blockIdx.x) : nullptr;
     __syncthreads();
     pdl_trigger();
 
@@ -440,19 +483,32 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_rows8_kernel(const GemvP
                 }
             }
         };
+        // `window` (0 = off) bounds how many stages may be requested but not yet
+        // landed: requests that are outstanding together complete together.
+        auto landed = [&](int it) {
+            return mbar_wait_bounded(smem_u32(&full_bar[it % NS]), (uint32_t)((it / NS) & 1), abort_flag, p.status,
+                                     FAULT_GEMV_FULL_WAIT);
+        };
+        const int W = p.window;
         // Weights never depend on the kernel in front: fill the ring first.
         const int npre = min(min(p.prefetch, NS), total);
-        for (int it = 0; it < npre; ++it) request(it);
+        bool ok = true;
+        for (int it = 0; it < npre && ok; ++it) {
+            if (W > 0 && it >= W) ok = landed(it - W);
+            if (ok) request(it);
+        }
         pdl_wait();
-        int issued = npre;
-        for (int it = npre; it < total; ++it) {
+        int issued = ok ? npre : 0;
+        for (int it = npre; it < total && ok; ++it) {
             const int s = it % NS;
             const uint32_t parity = (uint32_t)(((it / NS) & 1) ^ 1);
             if (!mbar_wait_bounded(smem_u32(&empty_bar[s]), parity, abort_flag, p.status, FAULT_GEMV_EMPTY_WAIT)) break;
+            if (W > 0 && it >= W && !landed(it - W)) break;
             request(it);
             issued = it + 1;
         }
         if (*abort_flag) drain_after_abort(full_bar, NS, issued, p.status);
+        else prefetch_next_operands(p.next, lane, blockIdx.x, gridDim.x);
         return;
     }
 
@@ -460,11 +516,21 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_rows8_kernel(const GemvP
     const int cw = warp - 1;
     const int ct = tid - 32;
     pdl_wait();
-    stage_activations(p, xs, xs_stride, red, ct, cw, lane);
+    trace_mark(trec, 3);
+    // The residual values this CTA will add are fetched now, together with the
+    // activations, so that no epilogue waits on a global load.
+    const int rows_here = r1 - r0;
+    const bool res_in_smem = p.epilogue == EPI_RESIDUAL && p.B * rows_here <= kResidualSlots;
+    if (res_in_smem)
+        for (int i = ct; i < p.B * rows_here; i += kConsumerThreads) {
+            const int b = i / rows_here, r = i - b * rows_here;
+            res_s[i] = __bfloat162float(p.residual[(long long)b * p.ldres + r0 + r]);
+        }
+    stage_activations<true>(p, xs, xs_stride, red, ct, cw, lane);  // ends with a barrier among the consumers
 
     const int g4 = lane >> 2, t4 = lane & 3;
     const bool has_row = g4 < p.B;
-    const bf16* xrow = xs + (size_t)(has_row ? g4 : 0) * xs_stride + t4 * 2;
+    const bf16* xrow = xs + (size_t)(has_row ? g4 : 0) * xs_stride + t4 * 8;  // permuted layout, see store_x8
     const uint32_t lds_off = (uint32_t)(((lane & 7) * ws_stride + (lane >> 3) * 8) * (int)sizeof(bf16));
 
     for (int rb = 0; rb < nrb; ++rb) {
@@ -473,31 +539,30 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_rows8_kernel(const GemvP
             const int it = rb * nkc + kci;
             const int s = it % NS;
             mbar_wait_bounded(smem_u32(&full_bar[s]), (uint32_t)((it / NS) & 1), abort_flag, p.status, FAULT_GEMV_FULL_WAIT);
+            if (it == 0) trace_mark(trec, 4);
             const int k0 = kci * p.kc;
             const int len = min(p.kc, p.K - k0);
             const int nk32 = len >> 5;
             const uint32_t w_base = smem_u32(stage_base + (size_t)s * stage_bytes) + lds_off;
             const bf16* xk = xrow + k0;
+            // The eight warps run eight independent mma chains; unrolling lets the
+            // loads of later iterations overlap the chain of the current one.
 #pragma unroll 4
             for (int k32 = cw; k32 < nk32; k32 += kConsumerWarps) {
                 uint32_t w0, w1, w2, w3;
                 ldsm_x4(w_base + (uint32_t)(k32 * 32 * (int)sizeof(bf16)), w0, w1, w2, w3);
-                uint32_t a0 = 0u, a2 = 0u, c0 = 0u, c2 = 0u;
-                if (has_row) {
-                    const bf16* xb = xk + k32 * 32;
-                    a0 = *reinterpret_cast<const uint32_t*>(xb);
-                    a2 = *reinterpret_cast<const uint32_t*>(xb + 8);
-                    c0 = *reinterpret_cast<const uint32_t*>(xb + 16);
-                    c2 = *reinterpret_cast<const uint32_t*>(xb + 24);
-                }
-                mma_bf16_16816(acc0, a0, 0u, a2, 0u, w0, w1);
-                mma_bf16_16816(acc1, c0, 0u, c2, 0u, w2, w3);
+                uint4 a = make_uint4(0u, 0u, 0u, 0u);
+                if (has_row) a = *reinterpret_cast<const uint4*>(xk + k32 * 32);
+                mma_bf16_16816(acc0, a.x, 0u, a.y, 0u, w0, w1);
+                mma_bf16_16816(acc1, a.z, 0u, a.w, 0u, w2, w3);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&empty_bar[s]));
         }
-        // rows 0..7 of the C tile are the batch; this thread holds (batch g4, weight rows 2*t4, 2*t4+1)
-        *reinterpret_cast<float2*>(red + cw * 64 + g4 * 8 + t4 * 2) = make_float2(acc0[0] + acc1[0], acc0[1] + acc1[1]);
+        // rows 0..7 of the C tile are the batch; this thread holds (batch g4, weight rows 2*t4, 2*t4+1).
+        // The reduction buffer alternates between row blocks, so one barrier per block is enough.
+        float* redb = red + (rb & 1) * (kConsumerWarps * 64);
+        *reinterpret_cast<float2*>(redb + cw * 64 + g4 * 8 + t4 * 2) = make_float2(acc0[0] + acc1[0], acc0[1] + acc1[1]);
         named_bar_sync(1, kConsumerThreads);
         if (ct < 64) {
             const int b = ct >> 3, j = ct & 7;
@@ -506,14 +571,19 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_rows8_kernel(const GemvP
                 float v0 = 0.f, v1 = 0.f;
 #pragma unroll
                 for (int w = 0; w < kConsumerWarps; ++w) {
-                    v0 += red[w * 64 + b * 8 + j];
-                    if (PAIR) v1 += red[w * 64 + b * 8 + j + 4];
+                    v0 += redb[w * 64 + b * 8 + j];
+                    if (PAIR) v1 += redb[w * 64 + b * 8 + j + 4];
                 }
-                store_output(p, b, n, v0, v1);
+                if (res_in_smem) {
+                    const float res = res_s[b * rows_here + (n - r0)];
+                    reinterpret_cast<bf16*>(p.out)[(long long)b * p.ldout + n] = __float2bfloat16_rn(res + round_bf16(v0));
+                } else {
+                    store_output(p, b, n, v0, v1);
+                }
             }
         }
-        named_bar_sync(1, kConsumerThreads);
     }
+    trace_mark(trec, 5);
 }
 
 // ---------------------------------------------------------------------------
@@ -532,6 +602,28 @@ static int pick_nt(int B) { return B <= 8 ? 1 : (B <= 16 ? 2 : (B <= 32 ? 4 : 8)
 static bool x_fits_resident(int B, int K) { return (size_t)B * (K + 8) * 2 <= 72 * 1024 && B <= 8; }
 
 bool gemv_needs_scratch(int B, int K) { return !x_fits_resident(B, K); }
+
+PrefetchPlan prefetch_plan_rows(const bf16* W0, const bf16* W1, int N, int K, int cap_rows, int skip_rows) {
+    PrefetchPlan pf;
+    pf.skip_units = skip_rows;
+    pf.base[0] = W0, pf.base[1] = W1;
+    pf.unit_bytes = (long long)K * 2;
+    pf.units = N;
+    pf.next_grid = sm_count() < N ? sm_count() : N;
+    pf.cap_units = cap_rows;
+    return pf;
+}
+
+PrefetchPlan prefetch_plan_flat(const void* a, const void* b, size_t bytes_each) {
+    PrefetchPlan pf;
+    pf.base[0] = a, pf.base[1] = b;
+    pf.unit_bytes = 4096;
+    pf.units = (int)(bytes_each / 4096);
+    pf.next_grid = sm_count();
+    pf.cap_units = 1 << 30;
+    pf.skip_units = 0;
+    return pf;
+}
 
 static GemvPlan plan_gemv(const GemvArgs& a, bool pair) {
     GemvPlan pl;
@@ -601,8 +693,8 @@ static bool plan_rows8(const GemvArgs& a, GemvPlan& pl) {
     if (a.B > 8 || a.K % 32 != 0) return false;
     if ((size_t)a.B * (a.K + 8) * 2 > 64 * 1024) return false;  // keep room for a deep ring of whole rows
     const size_t cap = (size_t)max_smem_optin();
-    const size_t xs = align_up((size_t)a.B * (a.K + 8) * 2, 128);
-    const size_t fixed = kHeaderBytes + kRed8Bytes + xs;
+    const size_t xs = align_up((size_t)a.B * (a.K + kXsPad8) * 2, 128);
+    const size_t fixed = kHeaderBytes + kRed8Bytes + kResidualSlots * sizeof(float) + xs;
     int best_kc = 0, best_ns = 0;
     int forced = tuning(EZB_TUNE_GEMV_KC);
     for (int kc = 4096; kc >= 256; kc >>= 1) {
@@ -666,8 +758,13 @@ cudaError_t launch_gemv(const GemvArgs& a, cudaStream_t stream) {
     p.residual = a.residual, p.ldres = a.ldres;
     p.out = a.out, p.ldout = a.ldout;
     p.kc = pl.kc, p.nstages = pl.nstages, p.prefetch = pl.prefetch;
+    p.window = tuning(EZB_TUNE_GEMV_WINDOW);
     p.status = status_ptr();
     if (!p.status) return cudaErrorUnknown;
+    p.next = a.next;
+    if (!tuning(EZB_TUNE_L2_PREFETCH)) p.next.plan[0].units = p.next.plan[1].units = 0;
+    p.trace = trace_handle();
+    p.trace_id = a.trace_id;
 
     if (!pl.xres && a.prologue != PRO_NONE) {
         // The activation block does not fit next to the ring: run the prologue

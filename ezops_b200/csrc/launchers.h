@@ -40,7 +40,13 @@ struct GemvArgs {
     void* out = nullptr;  // [B, ldout] bf16 (fp32 for EPI_STORE_F32)
     long long ldout = 0;
     bf16* xn_scratch = nullptr;  // [B, K] bf16: needed when the prologue cannot be fused (see gemv_needs_scratch)
+    PrefetchList next = {};  // what the following kernels stream first (optional)
+    int trace_id = 0;  // label in timeline traces
 };
+
+// Prefetch descriptors for the operands of a following kernel.
+PrefetchPlan prefetch_plan_rows(const bf16* W0, const bf16* W1, int N, int K, int cap_rows, int skip_rows = 0);  // a GEMV's weight rows
+PrefetchPlan prefetch_plan_flat(const void* a, const void* b, size_t bytes_each);            // whole regions
 
 // True when the activation block is too large to stay resident in shared memory
 // next to the weight ring, so a prologue has to run as a kernel of its own
@@ -96,6 +102,7 @@ struct AttnArgs {
     bf16* K_cache_w = nullptr;
     bf16* V_cache_w = nullptr;
     float eps = 1e-6f;
+    PrefetchList next = {};
 };
 size_t attn_workspace_bytes(int B, int H, int NKV, int S, int D);
 size_t attn_counters_bytes(int B, int H, int NKV);  // leading part of the workspace that must be zero before a call

@@ -235,6 +235,7 @@ class Qwen3DenseDecodeSm100Kernel(BaseKernel):
         return self._ws
 
     def __call__(self, hidden, K_cache, V_cache, Wqkv, Wo, Wgu, Wd, out=None):
+        """``out`` (optional) receives the result in place."""
         B, S, H, I, NH, NKV, D = self.B, self.S, self.H, self.I, self.NH, self.NKV, self.D
         _require(hidden, "hidden", (B, H))
         _require(K_cache, "K_cache", (B, NKV, S, D)); _require(V_cache, "V_cache", (B, NKV, S, D))

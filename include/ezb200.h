@@ -58,7 +58,11 @@ typedef struct CUstream_st* ezb_stream_t; /* same type as cudaStream_t */
 #define EZB_TUNE_GEMV_KC 6          /* k-chunk length of a weight stage (0 = automatic)                 */
 #define EZB_TUNE_GEMV_ROWS8 7       /* 1: batch <= 8 uses the whole-row small-batch kernel (default 1)   */
 #define EZB_TUNE_PDL_ACROSS_CALLS 8 /* 1: the first kernel of a call may also start early (default 0)    */
-#define EZB_TUNE_COUNT 9
+#define EZB_TUNE_L2_PREFETCH 9      /* 1: kernels of a chain pull the next kernel's first weights into L2 (default 1) */
+#define EZB_TUNE_L2_PREFETCH_KB 10  /* KB per CTA of a following large weight pulled ahead (default 192)                 */
+#define EZB_TUNE_GEMV_WINDOW 11     /* stages that may be requested but not landed, small-batch kernel (0 = ring depth) */
+#define EZB_TUNE_L2_PREFETCH_ATTN_KB 12 /* KB per CTA of the gate/up weights that the attention kernel pulls ahead (default 0) */
+#define EZB_TUNE_COUNT 13
 
 int ezb_version(void);
 const char* ezb_strerror(int code);
@@ -69,6 +73,15 @@ int ezb_get_tuning(int key);
 /* Reads (and with clear != 0 resets) the status word of the current device.
  * Synchronises the device.  *status_out == 0 means no kernel gave up a wait. */
 int ezb_device_status(unsigned int* status_out_host, int clear);
+
+/* Timeline tracing for performance work (no counterpart in the reference; its
+ * tracing is an ncu wrapper, scripts/ncu_profile.py).  After this call, one
+ * thread per CTA of the streaming and attention kernels appends a record of six
+ * 64-bit words {kernel id, block, t_entry, t_after_dependency, t_first_data,
+ * t_exit} (GPU nanoseconds) at records[6 * atomicAdd(cursor, 1)], while fewer
+ * than `capacity` records exist.  Both buffers are device memory owned by the
+ * caller; pass nulls to switch tracing off.  Not for use during timed runs. */
+int ezb_trace_enable(void* records, unsigned int* cursor, unsigned int capacity);
 
 /* y[N] = W[N,K] . x[K], bf16 in, fp32 accumulate, bf16 out.
  * Replaces the host entries gemv_cu(A,B,C) (ezops/kernels/gemv/gemv_cu.cu:71)
