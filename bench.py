@@ -371,7 +371,7 @@ def main():
     n_roof = 200
     rows_local = sets[0][4].shape[0]
     Y = torch.empty(B, rows_local, dtype=torch.bfloat16, device=device)
-    ws = torch.zeros(256, dtype=torch.uint8, device=device)
+    ws = torch.zeros(lib.ezb_gemv_workspace_bytes(B, rows_local, H), dtype=torch.uint8, device=device)
     X = hidden0
 
     def roof_launch(i):

@@ -36,6 +36,7 @@ TUNE = {
     "l2_prefetch_kb": 10,
     "gemv_window": 11,
     "l2_prefetch_attn_kb": 12,
+    "tc": 13,
 }
 
 # name -> (restype, argtypes); every symbol include/ezb200.h declares
@@ -48,7 +49,7 @@ SIGNATURES = {
     "ezb_device_status": (c_int, [POINTER(c_uint), c_int]),
     "ezb_trace_enable": (c_int, [c_void_p, c_void_p, c_uint]),
     "ezb_gemv_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
-    "ezb_gemv_workspace_bytes": (c_size_t, [c_int, c_int]),
+    "ezb_gemv_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "ezb_gemv_batched_bf16": (c_int, [c_void_p] * 4 + [c_size_t] + [c_int] * 3 + [c_void_p]),
     "ezb_rmsnorm_f32": (c_int, [c_void_p, c_void_p, c_int, c_int, c_float, c_void_p]),
     "ezb_rmsnorm_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p]),

@@ -91,10 +91,11 @@ static const int kTuningDefaults[EZB_TUNE_COUNT] = {
     192,  // EZB_TUNE_L2_PREFETCH_KB
     0,    // EZB_TUNE_GEMV_WINDOW
     0,    // EZB_TUNE_L2_PREFETCH_ATTN_KB
+    1,    // EZB_TUNE_TC
 };
 static const char* kTuningEnv[EZB_TUNE_COUNT] = {
     "EZB_TUNE_PDL",          "EZB_TUNE_GEMV_SMEM_KB",   "EZB_TUNE_GEMV_PREFETCH", "EZB_TUNE_GEMV_CTAS_PER_SM",
-    "EZB_TUNE_ATTN_MIN_CHUNK", "EZB_TUNE_ATTN_WAVES", "EZB_TUNE_GEMV_KC", "EZB_TUNE_GEMV_ROWS8", "EZB_TUNE_PDL_ACROSS_CALLS", "EZB_TUNE_L2_PREFETCH", "EZB_TUNE_L2_PREFETCH_KB", "EZB_TUNE_GEMV_WINDOW", "EZB_TUNE_L2_PREFETCH_ATTN_KB",
+    "EZB_TUNE_ATTN_MIN_CHUNK", "EZB_TUNE_ATTN_WAVES", "EZB_TUNE_GEMV_KC", "EZB_TUNE_GEMV_ROWS8", "EZB_TUNE_PDL_ACROSS_CALLS", "EZB_TUNE_L2_PREFETCH", "EZB_TUNE_L2_PREFETCH_KB", "EZB_TUNE_GEMV_WINDOW", "EZB_TUNE_L2_PREFETCH_ATTN_KB", "EZB_TUNE_TC",
 };
 
 static void tuning_init() {
@@ -118,9 +119,21 @@ static size_t round256(size_t v) { return (v + 255) / 256 * 256; }
 // the counters that must start at zero.
 struct LayerWorkspace {
     void* attn;
+    void* tc;  // tensor-core path: split counters (zero between calls) and partial tiles; null at batch 1
     bf16 *qkv, *attn_out, *x2, *h, *xn;
     size_t total;
 };
+
+// Largest tensor-core workspace any projection of a layer with these sizes needs.
+static size_t layer_tc_bytes(int B, int H, int I, int rows_qkv) {
+    if (B < 2) return 0;
+    size_t m = gemm_tc_workspace_bytes(B, rows_qkv, false);
+    size_t v = gemm_tc_workspace_bytes(B, H, false);
+    if (v > m) m = v;
+    v = gemm_tc_workspace_bytes(B, I, true);
+    if (v > m) m = v;
+    return m;
+}
 
 static LayerWorkspace carve_layer_ws(void* base, int B, int S, int H, int I, int NH, int NKV, int D) {
     LayerWorkspace w;
@@ -132,6 +145,8 @@ static LayerWorkspace carve_layer_ws(void* base, int B, int S, int H, int I, int
         return r;
     };
     w.attn = take(attn_workspace_bytes(B, NH, NKV, S, D));
+    const size_t tc_bytes = layer_tc_bytes(B, H, I, (NH + 2 * NKV) * D);
+    w.tc = tc_bytes ? take(tc_bytes) : nullptr;
     w.qkv = reinterpret_cast<bf16*>(take((size_t)B * (NH + 2 * NKV) * D * 2));
     w.attn_out = reinterpret_cast<bf16*>(take((size_t)B * NH * D * 2));
     w.x2 = reinterpret_cast<bf16*>(take((size_t)B * H * 2));
@@ -142,6 +157,7 @@ static LayerWorkspace carve_layer_ws(void* base, int B, int S, int H, int I, int
 }
 
 struct FfnWorkspace {
+    void* tc;
     bf16 *x2, *h, *xn;
     size_t total;
 };
@@ -155,6 +171,8 @@ static FfnWorkspace carve_ffn_ws(void* base, int B, int H, int I) {
         off += round256(bytes);
         return r;
     };
+    const size_t tc_bytes = layer_tc_bytes(B, H, I, H);
+    w.tc = tc_bytes ? take(tc_bytes) : nullptr;
     w.x2 = reinterpret_cast<bf16*>(take((size_t)B * H * 2));
     w.h = reinterpret_cast<bf16*>(take((size_t)B * I * 2));
     w.xn = reinterpret_cast<bf16*>(take((size_t)B * H * 2));
@@ -186,16 +204,13 @@ static PrefetchList one_plan(const PrefetchPlan& a) {
     l.plan[0] = a;
     return l;
 }
-static PrefetchList two_plans(const PrefetchPlan& a, const PrefetchPlan& b) {
-    PrefetchList l = {};
-    l.plan[0] = a, l.plan[1] = b;
-    return l;
-}
 
 // o_proj (+residual or fp32 partial), gate/up + SwiGLU, down (+residual or fp32 partial)
 static cudaError_t launch_o_proj(const bf16* attn, const bf16* Wo, int B, int H, int Q, const bf16* residual, void* out,
-                                 bool f32_partial, cudaStream_t stream, const PrefetchList& next = kNoPrefetch) {
+                                 bool f32_partial, cudaStream_t stream, const PrefetchList& next = kNoPrefetch,
+                                 void* tc = nullptr) {
     GemvArgs g;
+    g.tc_workspace = tc;
     g.W0 = Wo, g.ldw = Q, g.N = H, g.K = Q, g.B = B;
     g.x = attn, g.ldx = Q;
     g.prologue = PRO_NONE;
@@ -209,8 +224,9 @@ static cudaError_t launch_o_proj(const bf16* attn, const bf16* Wo, int B, int H,
 
 static cudaError_t launch_gate_up(const bf16* x, const float* x_add, bf16* x_sum_out, const bf16* norm_w, const bf16* Wg,
                                   const bf16* Wu, int B, int H, int I, float eps, bf16* h, bf16* xn_scratch,
-                                  cudaStream_t stream, const PrefetchList& next = kNoPrefetch) {
+                                  cudaStream_t stream, const PrefetchList& next = kNoPrefetch, void* tc = nullptr) {
     GemvArgs g;
+    g.tc_workspace = tc;
     g.W0 = Wg, g.W1 = Wu, g.ldw = H, g.N = I, g.K = H, g.B = B;
     g.x = x, g.ldx = H;
     g.x_add = x_add, g.ldadd = H, g.x_sum_out = x_sum_out, g.ldsum = H;
@@ -225,8 +241,10 @@ static cudaError_t launch_gate_up(const bf16* x, const float* x_add, bf16* x_sum
 }
 
 static cudaError_t launch_down(const bf16* h, const bf16* Wd, int B, int H, int I, const bf16* residual, void* out,
-                               bool f32_partial, cudaStream_t stream, const PrefetchList& next = kNoPrefetch) {
+                               bool f32_partial, cudaStream_t stream, const PrefetchList& next = kNoPrefetch,
+                               void* tc = nullptr) {
     GemvArgs g;
+    g.tc_workspace = tc;
     g.W0 = Wd, g.ldw = I, g.N = H, g.K = I, g.B = B;
     g.x = h, g.ldx = I;
     g.prologue = PRO_NONE;
@@ -248,6 +266,7 @@ static cudaError_t launch_qkv_and_attention(const bf16* hidden, bf16* Kc, bf16* 
     g.eps = eps, g.prologue = PRO_RMSNORM, g.epilogue = EPI_STORE;
     g.out = w.qkv, g.ldout = rows;
     g.xn_scratch = w.xn;
+    g.tc_workspace = w.tc;
     g.trace_id = 1;
     // while the projection drains, start pulling the KV cache (if it is small enough to sit in L2)
     const size_t kv_bytes = (size_t)B * NKV * S * D * 2;
@@ -344,16 +363,20 @@ int ezb_gemv_bf16(const void* x, const void* W, void* y, int N, int K, ezb_strea
     return EZB_OK;
 }
 
-size_t ezb_gemv_workspace_bytes(int B, int K) {
-    (void)B, (void)K;
-    return 256;  // no prologue runs in this entry point, so no scratch rows are needed
+size_t ezb_gemv_workspace_bytes(int B, int N, int K) {
+    (void)K;
+    if (B < 2 || N < 1) return 256;
+    return gemm_tc_workspace_bytes(B, N, false);  // split counters and partial tiles of the tensor-core path
 }
 
 int ezb_gemv_batched_bf16(const void* X, const void* W, void* Y, void* workspace, size_t workspace_bytes, int B, int N, int K,
                           ezb_stream_t stream) {
-    (void)workspace, (void)workspace_bytes;
     EZB_REQUIRE(X && W && Y, "null pointer");
     EZB_REQUIRE(N >= 1 && K >= 1 && B >= 1, "B, N and K must be positive");
+    if (B >= 2 && (!workspace || workspace_bytes < gemm_tc_workspace_bytes(B, N, false))) {
+        set_last_message("workspace missing or smaller than ezb_gemv_workspace_bytes()");
+        return EZB_ERR_WORKSPACE;
+    }
     EZB_REQUIRE_SHAPE(B <= 64, "batch above 64 is not supported");
     EZB_REQUIRE_SHAPE(K % 16 == 0, "K must be divisible by 16");
     EZB_REQUIRE(aligned16(X) && aligned16(W), "X and W must be 16-byte aligned");
@@ -361,6 +384,7 @@ int ezb_gemv_batched_bf16(const void* X, const void* W, void* Y, void* workspace
     g.W0 = static_cast<const bf16*>(W), g.ldw = K, g.N = N, g.K = K, g.B = B;
     g.x = static_cast<const bf16*>(X), g.ldx = K;
     g.out = Y, g.ldout = N;
+    g.tc_workspace = B >= 2 ? workspace : nullptr;
     chain_begin();
     EZB_CUDA_TRY(launch_gemv(g, stream));
     return EZB_OK;
@@ -462,11 +486,11 @@ int ezb_o_proj_ffn(const void* attn, const void* residual, const void* Wo, const
     const int pf_kb = tuning(EZB_TUNE_L2_PREFETCH_KB);
     EZB_CUDA_TRY(launch_o_proj(static_cast<const bf16*>(attn), static_cast<const bf16*>(Wo), B, H, Q,
                                static_cast<const bf16*>(residual), w.x2, false, stream,
-                               one_plan(next_rows(static_cast<const bf16*>(Wg), static_cast<const bf16*>(Wu), I, H, pf_kb))));
+                               one_plan(next_rows(static_cast<const bf16*>(Wg), static_cast<const bf16*>(Wu), I, H, pf_kb)), w.tc));
     EZB_CUDA_TRY(launch_gate_up(w.x2, nullptr, nullptr, static_cast<const bf16*>(post_norm_w), static_cast<const bf16*>(Wg),
                                 static_cast<const bf16*>(Wu), B, H, I, eps, w.h, w.xn, stream,
-                                one_plan(next_rows(static_cast<const bf16*>(Wd), nullptr, H, I, pf_kb))));
-    EZB_CUDA_TRY(launch_down(w.h, static_cast<const bf16*>(Wd), B, H, I, w.x2, out, false, stream));
+                                one_plan(next_rows(static_cast<const bf16*>(Wd), nullptr, H, I, pf_kb)), w.tc));
+    EZB_CUDA_TRY(launch_down(w.h, static_cast<const bf16*>(Wd), B, H, I, w.x2, out, false, stream, kNoPrefetch, w.tc));
     return EZB_OK;
 }
 
@@ -499,10 +523,10 @@ int ezb_qwen3_decode_layer(const void* hidden, void* K_cache, void* V_cache, con
                                           static_cast<const bf16*>(Wqkv), w, B, S, H, NH, NKV, D, eps, stream,
                                           static_cast<const bf16*>(Wo), pf_attn_kb > 0 ? &gu_head : nullptr));
     EZB_CUDA_TRY(launch_o_proj(w.attn_out, static_cast<const bf16*>(Wo), B, H, NH * D, hid, w.x2, false, stream,
-                               one_plan(next_rows(wgu, wgu + (size_t)I * H, I, H, pf_kb, pf_attn_kb > 0 ? pf_attn_kb : 0))));
+                               one_plan(next_rows(wgu, wgu + (size_t)I * H, I, H, pf_kb, pf_attn_kb > 0 ? pf_attn_kb : 0)), w.tc));
     EZB_CUDA_TRY(launch_gate_up(w.x2, nullptr, nullptr, nullptr, wgu, wgu + (size_t)I * H, B, H, I, eps, w.h, w.xn, stream,
-                                one_plan(next_rows(static_cast<const bf16*>(Wd), nullptr, H, I, pf_kb))));
-    EZB_CUDA_TRY(launch_down(w.h, static_cast<const bf16*>(Wd), B, H, I, w.x2, out, false, stream));
+                                one_plan(next_rows(static_cast<const bf16*>(Wd), nullptr, H, I, pf_kb)), w.tc));
+    EZB_CUDA_TRY(launch_down(w.h, static_cast<const bf16*>(Wd), B, H, I, w.x2, out, false, stream, kNoPrefetch, w.tc));
     return EZB_OK;
 }
 
@@ -526,7 +550,7 @@ int ezb_qwen3_decode_layer_tp_attn(const void* hidden, void* K_cache, void* V_ca
                                           static_cast<bf16*>(V_cache), static_cast<const bf16*>(Wqkv_local), w, B, S, H,
                                           NH_local, NKV_local, D, eps, stream, static_cast<const bf16*>(Wo_local)));
     EZB_CUDA_TRY(launch_o_proj(w.attn_out, static_cast<const bf16*>(Wo_local), B, H, NH_local * D, nullptr, partial_o, true,
-                               stream));
+                               stream, kNoPrefetch, w.tc));
     return EZB_OK;
 }
 
@@ -547,8 +571,9 @@ int ezb_qwen3_decode_layer_tp_ffn(const void* hidden, const float* summed_o, con
     chain_begin();
     EZB_CUDA_TRY(launch_gate_up(static_cast<const bf16*>(hidden), summed_o, static_cast<bf16*>(x2), nullptr, wgu,
                                 wgu + (size_t)I_local * H, B, H, I_local, eps, w.h, w.xn, stream,
-                                one_plan(next_rows(static_cast<const bf16*>(Wd_local), nullptr, H, I_local, tuning(EZB_TUNE_L2_PREFETCH_KB)))));
-    EZB_CUDA_TRY(launch_down(w.h, static_cast<const bf16*>(Wd_local), B, H, I_local, nullptr, partial_d, true, stream));
+                                one_plan(next_rows(static_cast<const bf16*>(Wd_local), nullptr, H, I_local, tuning(EZB_TUNE_L2_PREFETCH_KB))), w.tc));
+    EZB_CUDA_TRY(launch_down(w.h, static_cast<const bf16*>(Wd_local), B, H, I_local, nullptr, partial_d, true, stream,
+                             kNoPrefetch, w.tc));
     return EZB_OK;
 }
 

@@ -26,6 +26,7 @@ enum DeviceFault : unsigned int {
     FAULT_GEMV_FULL_WAIT = 0x101,   // consumer never saw a weight stage arrive
     FAULT_GEMV_EMPTY_WAIT = 0x102,  // producer never got a stage back
     FAULT_GEMV_DRAIN = 0x103,       // copies still in flight at exit
+    FAULT_TC_ACC_WAIT = 0x104,      // tensor-memory accumulator hand-over never happened
     FAULT_AR_FLAG_WAIT = 0x201,     // a peer's all-reduce flag never arrived
 };
 

@@ -1,0 +1,476 @@
+// Batched projections on the 5th-generation tensor cores:
+//   Y[b, n] = epi( sum_k X[b, k] * W[n, k] ),   2 <= b <= 64,
+// used once the batch turns the weight-streaming GEMV into a skinny GEMM.
+//
+// The weights are still read from HBM exactly once, so the kernel is built like
+// the GEMV -- persistent CTAs, a deep TMA ring, programmatic dependent launch --
+// but the arithmetic moves to tcgen05:
+//   * "swap AB": a tile is 128 weight rows (the MMA's M) by the whole batch
+//     (the MMA's N = 16, 32 or 64) and walks K in blocks of 64 elements;
+//   * one elected thread issues cp.async.bulk.tensor (2-D tiled TMA, 128-byte
+//     swizzle) for the W block [128 x 64] and the X block [N x 64] of a stage;
+//     one elected thread issues tcgen05.mma (kind::f16, bf16 x bf16 -> fp32)
+//     with the accumulator in tensor memory, and tcgen05.commit hands the stage
+//     back to the producer when the MMAs that read it have retired;
+//   * four epilogue warps read the accumulator with tcgen05.ld (thread = weight
+//     row, registers = batch columns) and apply the same epilogues as the GEMV;
+//     the accumulator is double buffered in tensor memory, so the epilogue of
+//     one tile overlaps the MMAs of the next;
+//   * work is split "stream-K": the (tile, k-block) units are dealt evenly to
+//     the CTAs in order, whatever the matrix shape (a 4096-row matrix has only
+//     32 tiles for 148 SMs).  A CTA that covers only part of a tile's K range
+//     stores its fp32 partial tile in the workspace; the last contributor of the
+//     tile (one atomic ticket, no waiting) adds the partials in CTA order, so
+//     results are bit-reproducible.
+// Every mbarrier wait is bounded; on a time-out the CTA records a fault, stops
+// issuing work, waits (bounded) for copies in flight, frees its tensor memory
+// and returns.
+#include <cuda.h>
+
+#include "launchers.h"
+
+namespace ezb {
+
+static constexpr int kTcRows = 128;     // weight rows per tile (MMA M)
+static constexpr int kTcBlockK = 64;    // k elements per stage: 128 bytes, one swizzle row
+static constexpr int kTcThreads = 192;  // TMA warp, MMA warp, four epilogue warps
+static constexpr int kTcMaxStages = 10;
+static constexpr int kTcABytes = kTcRows * kTcBlockK * 2;
+
+struct TcParams {
+    int N, K, B;          // output units (rows, or gate/up pairs), reduction length, batch
+    int tiles, kblocks;   // ceil(N / units per tile), ceil(K / 64)
+    int nstages;
+    int pair;             // 1: tile = 64 gate rows + 64 up rows, SwiGLU epilogue
+    int epilogue;
+    const bf16* residual;
+    long long ldres;
+    void* out;
+    long long ldout;
+    float* partial;          // [grid][2][NB][128] fp32 partial tiles
+    unsigned int* counters;  // [tiles], zero between launches
+    unsigned int* status;
+    Trace trace;
+    int trace_id;
+};
+
+// ---- tcgen05 / TMA wrappers -------------------------------------------------
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 32 lanes x 16 consecutive 32-bit columns: thread i of the warp gets lane (base lane + i)
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor for a K-major bf16 tile whose rows are 128
+// bytes (64 elements) with the 128-byte swizzle that the tiled TMA wrote:
+// start address / 16, stride between 8-row groups 1024 bytes, descriptor
+// version 1 (sm_100), layout type 2 (128-byte swizzle).
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)(1024u >> 4) << 32;
+    d |= 1ull << 46;
+    d |= 2ull << 61;
+    return d;
+}
+
+// Instruction descriptor, kind::f16: fp32 accumulator, bf16 A and B, both
+// K-major, N in units of 8 at bit 17, M in units of 16 at bit 24.
+__host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+// First unit of CTA c when T units are dealt to G CTAs in order.
+__device__ __forceinline__ long long tc_first_unit(long long T, int G, int c) { return T * c / G; }
+// CTA that owns unit u.
+__device__ __forceinline__ int tc_owner(long long T, int G, long long u) {
+    int c = (int)(u * G / T);
+    while (c + 1 < G && tc_first_unit(T, G, c + 1) <= u) ++c;
+    while (c > 0 && tc_first_unit(T, G, c) > u) --c;
+    return c;
+}
+
+template <int NB>
+__global__ void __launch_bounds__(kTcThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap mapW0, const __grid_constant__ CUtensorMap mapW1,
+               const __grid_constant__ CUtensorMap mapX, const TcParams p) {
+    constexpr int B_BYTES = NB * kTcBlockK * 2;
+    constexpr int STAGE_BYTES = kTcABytes + B_BYTES;
+    constexpr int TMEM_COLS = (2 * NB < 32) ? 32 : 2 * NB;  // two accumulators, power of two >= 32
+    constexpr uint32_t IDESC = umma_idesc_bf16(kTcRows, NB);
+
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    unsigned char* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);  // swizzled tiles need 1024-byte alignment
+    unsigned char* stages = smem;
+    unsigned char* tail = smem + (size_t)p.nstages * STAGE_BYTES;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(tail);
+    uint64_t* empty_bar = full_bar + kTcMaxStages;
+    uint64_t* acc_full = empty_bar + kTcMaxStages;  // [2] accumulator ready for the epilogue
+    uint64_t* acc_empty = acc_full + 2;             // [2] accumulator drained
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    int* ticket = reinterpret_cast<int*>(tmem_slot + 2);
+    float* xch = reinterpret_cast<float*>(tail + 256);  // [64][NB + 1]: up values handed to the gate warps
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int NS = p.nstages;
+    const int G = gridDim.x, cta = blockIdx.x;
+    const long long T = (long long)p.tiles * p.kblocks;
+    const long long u0 = tc_first_unit(T, G, cta), u1 = tc_first_unit(T, G, cta + 1);
+    const int KB = p.kblocks;
+
+    if (tid == 0) {
+        for (int s = 0; s < NS; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(smem_u32(&acc_full[a]), 1);
+            mbar_init(smem_u32(&acc_empty[a]), 4);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    unsigned long long* trec = (tid == 64) ? trace_open(p.trace, (unsigned)p.trace_id, blockIdx.x) : nullptr;
+    pdl_trigger();
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            auto stage_addr = [&](long long it) { return smem_u32(stages + (size_t)(it % NS) * STAGE_BYTES); };
+            auto load_w = [&](long long u, long long it) {
+                const int tile = (int)(u / KB), kb = (int)(u % KB);
+                const uint32_t bar = smem_u32(&full_bar[it % NS]);
+                mbar_arrive_expect_tx(bar, STAGE_BYTES);
+                const uint32_t a = stage_addr(it);
+                if (p.pair) {
+                    tma_load_2d(a, &mapW0, kb * kTcBlockK, tile * (kTcRows / 2), bar);
+                    tma_load_2d(a + kTcABytes / 2, &mapW1, kb * kTcBlockK, tile * (kTcRows / 2), bar);
+                } else {
+                    tma_load_2d(a, &mapW0, kb * kTcBlockK, tile * kTcRows, bar);
+                }
+            };
+            auto load_x = [&](long long u, long long it) {
+                const int kb = (int)(u % KB);
+                tma_load_2d(stage_addr(it) + kTcABytes, &mapX, kb * kTcBlockK, 0, smem_u32(&full_bar[it % NS]));
+            };
+            // weights do not depend on the kernel in front: request them before the dependency wait
+            const long long n_units = u1 - u0;
+            const long long npre = n_units < NS ? n_units : NS;
+            for (long long i = 0; i < npre; ++i) load_w(u0 + i, i);
+            pdl_wait();
+            for (long long i = 0; i < npre; ++i) load_x(u0 + i, i);
+            long long issued = npre;
+            for (long long i = npre; i < n_units; ++i) {
+                const uint32_t parity = (uint32_t)(((i / NS) & 1) ^ 1);
+                if (!mbar_wait_bounded(smem_u32(&empty_bar[i % NS]), parity, abort_flag, p.status, FAULT_GEMV_EMPTY_WAIT)) break;
+                load_w(u0 + i, i);
+                load_x(u0 + i, i);
+                issued = i + 1;
+            }
+            if (*abort_flag) {  // nothing may still be landing in this CTA's shared memory when it exits
+                const long long first = issued > NS ? issued - NS : 0;
+                for (long long i = first; i < issued; ++i) {
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(smem_u32(&full_bar[i % NS]), (uint32_t)((i / NS) & 1)))
+                        if (clock64() - t0 > kWaitLimitCycles) {
+                            report_fault(p.status, FAULT_GEMV_DRAIN);
+                            break;
+                        }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            long long it = 0;
+            int seg = 0;
+            for (long long u = u0; u < u1 && !(*abort_flag);) {
+                const int kb0 = (int)(u % KB);
+                const long long left = u1 - u;
+                const int kb1 = (KB - kb0 < left) ? KB : kb0 + (int)left;
+                const int acc = seg & 1;
+                // wait until the epilogue has drained this accumulator (passes at once for its first use)
+                if (!mbar_wait_bounded(smem_u32(&acc_empty[acc]), (uint32_t)(((seg >> 1) & 1) ^ 1), abort_flag, p.status,
+                                       FAULT_TC_ACC_WAIT))
+                    break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * NB);
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                    const int s = (int)(it % NS);
+                    if (!mbar_wait_bounded(smem_u32(&full_bar[s]), (uint32_t)((it / NS) & 1), abort_flag, p.status,
+                                           FAULT_GEMV_FULL_WAIT))
+                        break;
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(stages + (size_t)s * STAGE_BYTES);
+                    const uint64_t adesc = umma_desc_sw128(a_addr);
+                    const uint64_t bdesc = umma_desc_sw128(a_addr + kTcABytes);
+#pragma unroll
+                    for (int k = 0; k < kTcBlockK / 16; ++k)  // 32 bytes along K per MMA: +2 in the 16-byte address field
+                        tc_mma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, IDESC, (kb > kb0 || k > 0) ? 1u : 0u);
+                    tc_commit(smem_u32(&empty_bar[s]));  // stage reusable once these MMAs have read it
+                }
+                tc_commit(smem_u32(&acc_full[acc]));
+                u += kb1 - kb0;
+                ++seg;
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue warps
+        const int q = warp & 3;          // tensor-memory lane quarter this warp may read
+        const int row = q * 32 + lane;   // row of the tile held by this thread
+        const int et = (warp - 2) * 32 + lane;
+        pdl_wait();
+        trace_mark(trec, 3);
+        int seg = 0;
+        for (long long u = u0; u < u1; ++seg) {
+            const int tile = (int)(u / KB), kb0 = (int)(u % KB);
+            const long long left = u1 - u;
+            const int kb1 = (KB - kb0 < left) ? KB : kb0 + (int)left;
+            const int acc = seg & 1;
+            mbar_wait_bounded(smem_u32(&acc_full[acc]), (uint32_t)((seg >> 1) & 1), abort_flag, p.status, FAULT_TC_ACC_WAIT);
+            if (seg == 0) trace_mark(trec, 4);
+            tc_fence_after();
+            float v[NB];
+#pragma unroll
+            for (int c = 0; c < NB; c += 16) {
+                float t[16];
+                tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * NB + c), t);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[c + i] = t[i];
+            }
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&acc_empty[acc]));
+            u += kb1 - kb0;
+
+            const bool whole = (kb0 == 0 && kb1 == KB);
+            bool finish = whole;
+            if (!whole) {
+                // partial tile: park it, take a ticket; the last contributor adds all parts in CTA order
+                const bool leading = (seg == 0);
+                float* mine = p.partial + ((size_t)cta * 2 + (leading ? 0 : 1)) * (NB * kTcRows);
+#pragma unroll
+                for (int b = 0; b < NB; ++b) mine[b * kTcRows + row] = v[b];
+                named_bar_sync(2, 128);
+                const long long t_first = (long long)tile * KB, t_last = t_first + KB - 1;
+                const int c_first = tc_owner(T, G, t_first), c_last = tc_owner(T, G, t_last);
+                if (et == 0) {
+                    unsigned int prev;
+                    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(prev) : "l"(p.counters + tile) : "memory");
+                    *ticket = (prev == (unsigned int)(c_last - c_first)) ? 1 : 0;
+                    if (*ticket) p.counters[tile] = 0u;
+                }
+                named_bar_sync(2, 128);
+                finish = (*ticket != 0);
+                if (finish) {
+#pragma unroll
+                    for (int b = 0; b < NB; ++b) v[b] = 0.f;
+                    for (int c = c_first; c <= c_last; ++c) {
+                        const bool first_seg = (tc_first_unit(T, G, c) / KB) == tile;
+                        const float* part = p.partial + ((size_t)c * 2 + (first_seg ? 0 : 1)) * (NB * kTcRows);
+#pragma unroll
+                        for (int b = 0; b < NB; ++b) v[b] += __ldcg(part + b * kTcRows + row);
+                    }
+                }
+                named_bar_sync(2, 128);  // `ticket` may be rewritten by the next segment
+            }
+            if (!finish || *abort_flag) continue;
+
+            if (!p.pair) {
+                const int n = tile * kTcRows + row;
+                if (n < p.N) {
+#pragma unroll
+                    for (int b = 0; b < NB; ++b) {
+                        if (b >= p.B) break;
+                        const long long o = (long long)b * p.ldout + n;
+                        if (p.epilogue == EPI_STORE_F32) {
+                            reinterpret_cast<float*>(p.out)[o] = v[b];
+                        } else if (p.epilogue == EPI_RESIDUAL) {
+                            const float res = __bfloat162float(p.residual[(long long)b * p.ldres + n]);
+                            reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16_rn(res + round_bf16(v[b]));
+                        } else {
+                            reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16_rn(v[b]);
+                        }
+                    }
+                }
+            } else {
+                // rows 0..63 hold gate values of pairs 0..63, rows 64..127 the matching up values
+                if (row >= 64) {
+#pragma unroll
+                    for (int b = 0; b < NB; ++b) xch[(row - 64) * (NB + 1) + b] = v[b];
+                }
+                named_bar_sync(2, 128);
+                if (row < 64) {
+                    const int n = tile * (kTcRows / 2) + row;
+                    if (n < p.N) {
+#pragma unroll
+                        for (int b = 0; b < NB; ++b) {
+                            if (b >= p.B) break;
+                            const float gate = round_bf16(v[b]), up = round_bf16(xch[row * (NB + 1) + b]);
+                            reinterpret_cast<bf16*>(p.out)[(long long)b * p.ldout + n] =
+                                __float2bfloat16_rn(round_bf16(silu_f32(gate)) * up);
+                        }
+                    }
+                }
+                named_bar_sync(2, 128);
+            }
+        }
+        trace_mark(trec, 5);
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// 2-D bf16 row-major [rows, cols] with leading dimension ld; box = [64 cols, box_rows], 128-byte swizzle,
+// out-of-range elements read as zero.
+static bool make_map(CUtensorMap* map, const bf16* base, long long rows, long long cols, long long ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)kTcBlockK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<bf16*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static int tc_batch_tile(int B) { return B <= 16 ? 16 : (B <= 32 ? 32 : 64); }
+
+bool gemm_tc_supported(int B, int K) { return B >= 2 && B <= 64 && K % 8 == 0 && encode_fn() != nullptr; }
+
+size_t gemm_tc_workspace_bytes(int B, int N, bool pair) {
+    const int NB = tc_batch_tile(B);
+    const int tiles = (N + (pair ? 63 : 127)) / (pair ? 64 : 128);
+    const size_t counters = ((size_t)tiles * 4 + 255) / 256 * 256;
+    return counters + (size_t)sm_count() * 2 * NB * kTcRows * sizeof(float);
+}
+
+template <int NB>
+static cudaError_t launch_tc_instance(const CUtensorMap& m0, const CUtensorMap& m1, const CUtensorMap& mx, TcParams& p,
+                                      int grid, cudaStream_t stream) {
+    auto kernel = gemm_tc_kernel<NB>;
+    constexpr size_t stage = kTcABytes + (size_t)NB * kTcBlockK * 2;
+    const size_t tail = 256 + (size_t)64 * (NB + 1) * sizeof(float);
+    const size_t cap = (size_t)max_smem_optin();
+    int ns = (int)((cap - 1024 - tail) / stage);
+    if (ns > kTcMaxStages) ns = kTcMaxStages;
+    p.nstages = ns;
+    const size_t smem = 1024 + (size_t)ns * stage + tail;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cap);
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    return launch_pdl(kernel, dim3(grid), dim3(kTcThreads), smem, stream, m0, m1, mx, p);
+}
+
+// x must already hold what the MMA consumes (any norm prologue has been run by the caller).
+cudaError_t launch_gemm_tc(const GemvArgs& a, const bf16* x, long long ldx, void* workspace, cudaStream_t stream) {
+    const bool pair = a.epilogue == EPI_SWIGLU;
+    const int NB = tc_batch_tile(a.B);
+    TcParams p;
+    p.N = a.N, p.K = a.K, p.B = a.B;
+    p.tiles = (a.N + (pair ? 63 : 127)) / (pair ? 64 : 128);
+    p.kblocks = (a.K + kTcBlockK - 1) / kTcBlockK;
+    p.pair = pair ? 1 : 0;
+    p.epilogue = a.epilogue;
+    p.residual = a.residual, p.ldres = a.ldres;
+    p.out = a.out, p.ldout = a.ldout;
+    const size_t counters = ((size_t)p.tiles * 4 + 255) / 256 * 256;
+    p.counters = reinterpret_cast<unsigned int*>(workspace);
+    p.partial = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + counters);
+    p.status = status_ptr();
+    if (!p.status) return cudaErrorUnknown;
+    p.trace = trace_handle();
+    p.trace_id = a.trace_id;
+
+    alignas(64) CUtensorMap m0, m1, mx;
+    const int box_rows = pair ? 64 : 128;
+    if (!make_map(&m0, a.W0, a.N, a.K, a.ldw, box_rows)) return cudaErrorInvalidValue;
+    if (!make_map(&m1, pair ? a.W1 : a.W0, a.N, a.K, a.ldw, box_rows)) return cudaErrorInvalidValue;
+    if (!make_map(&mx, x, a.B, a.K, ldx, NB)) return cudaErrorInvalidValue;
+
+    long long T = (long long)p.tiles * p.kblocks;
+    int grid = sm_count();
+    if (grid > T) grid = (int)T;
+    switch (NB) {
+        case 16: return launch_tc_instance<16>(m0, m1, mx, p, grid, stream);
+        case 32: return launch_tc_instance<32>(m0, m1, mx, p, grid, stream);
+        default: return launch_tc_instance<64>(m0, m1, mx, p, grid, stream);
+    }
+}
+
+}  // namespace ezb

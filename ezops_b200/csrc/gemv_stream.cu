@@ -691,7 +691,7 @@ static cudaError_t dispatch_nt(const GemvParams& p, const GemvPlan& pl, cudaStre
 // Plan for the small-batch kernel; returns false when the shape is outside it.
 static bool plan_rows8(const GemvArgs& a, GemvPlan& pl) {
     if (a.B > 8 || a.K % 32 != 0) return false;
-    if ((size_t)a.B * (a.K + 8) * 2 > 64 * 1024) return false;  // keep room for a deep ring of whole rows
+    if ((size_t)a.B * (a.K + kXsPad8) * 2 > 72 * 1024) return false;  // keep room for a ring of whole rows
     const size_t cap = (size_t)max_smem_optin();
     const size_t xs = align_up((size_t)a.B * (a.K + kXsPad8) * 2, 128);
     const size_t fixed = kHeaderBytes + kRed8Bytes + kResidualSlots * sizeof(float) + xs;
@@ -766,9 +766,10 @@ cudaError_t launch_gemv(const GemvArgs& a, cudaStream_t stream) {
     p.trace = trace_handle();
     p.trace_id = a.trace_id;
 
-    if (!pl.xres && a.prologue != PRO_NONE) {
-        // The activation block does not fit next to the ring: run the prologue
-        // as its own (tiny) kernel into the scratch rows, then stream those.
+    const bool use_tc = !rows8 && a.tc_workspace && tuning(EZB_TUNE_TC) != 0 && gemm_tc_supported(a.B, a.K);
+    if ((use_tc || !pl.xres) && a.prologue != PRO_NONE) {
+        // The activation block is not resident in this path: run the prologue as
+        // its own (tiny) kernel into the scratch rows, then stream those.
         RowPrepArgs rp;
         rp.x = a.x, rp.ldx = a.ldx;
         rp.add = (a.prologue == PRO_ADD_RMSNORM) ? a.x_add : nullptr, rp.ldadd = a.ldadd;
@@ -781,6 +782,7 @@ cudaError_t launch_gemv(const GemvArgs& a, cudaStream_t stream) {
         p.x = a.xn_scratch, p.ldx = a.K;
         p.prologue = PRO_NONE;
     }
+    if (use_tc) return launch_gemm_tc(a, p.x, p.ldx, a.tc_workspace, stream);
 
     if (rows8) return pair ? launch_rows8<true>(p, pl, stream) : launch_rows8<false>(p, pl, stream);
     if (pl.xres) return pair ? dispatch_nt<true, true>(p, pl, stream) : dispatch_nt<true, false>(p, pl, stream);

@@ -42,7 +42,13 @@ struct GemvArgs {
     bf16* xn_scratch = nullptr;  // [B, K] bf16: needed when the prologue cannot be fused (see gemv_needs_scratch)
     PrefetchList next = {};  // what the following kernels stream first (optional)
     int trace_id = 0;  // label in timeline traces
+    void* tc_workspace = nullptr;  // gemm_tc_workspace_bytes(): enables the tensor-core path for batch >= 2
 };
+
+// Tensor-core (tcgen05) path for batched projections, see gemm_tc.cu.
+bool gemm_tc_supported(int B, int K);
+size_t gemm_tc_workspace_bytes(int B, int N, bool pair);
+cudaError_t launch_gemm_tc(const GemvArgs& a, const bf16* x, long long ldx, void* workspace, cudaStream_t stream);
 
 // Prefetch descriptors for the operands of a following kernel.
 PrefetchPlan prefetch_plan_rows(const bf16* W0, const bf16* W1, int N, int K, int cap_rows, int skip_rows = 0);  // a GEMV's weight rows

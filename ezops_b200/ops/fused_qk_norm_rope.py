@@ -134,7 +134,9 @@ class FusedQkNormRopeOp(Op):
             V_cache[:, :, self.position, :] = v
             return q_out, k_out
         # one position per batch row: the same formula row by row
-        pos = torch.as_tensor(self.position, device=q.device)
+        pos = getattr(self, "_pos_cache", None)
+        if pos is None or pos.device != q.device:  # kept on the device so the call can be graph-captured
+            pos = self._pos_cache = torch.as_tensor(self.position, device=q.device)
         c, s = cos[pos].float()[:, None, :], sin[pos].float()[:, None, :]
         q_out = self._rope(self._rmsnorm(q, q_norm_w), c, s)
         k_out = self._rope(self._rmsnorm(k, k_norm_w), c, s)

@@ -62,7 +62,8 @@ typedef struct CUstream_st* ezb_stream_t; /* same type as cudaStream_t */
 #define EZB_TUNE_L2_PREFETCH_KB 10  /* KB per CTA of a following large weight pulled ahead (default 192)                 */
 #define EZB_TUNE_GEMV_WINDOW 11     /* stages that may be requested but not landed, small-batch kernel (0 = ring depth) */
 #define EZB_TUNE_L2_PREFETCH_ATTN_KB 12 /* KB per CTA of the gate/up weights that the attention kernel pulls ahead (default 0) */
-#define EZB_TUNE_COUNT 13
+#define EZB_TUNE_TC 13              /* 1: batched projections run on tcgen05 tensor cores (default 1)                   */
+#define EZB_TUNE_COUNT 14
 
 int ezb_version(void);
 const char* ezb_strerror(int code);
@@ -92,9 +93,11 @@ int ezb_gemv_bf16(const void* x, const void* W, void* y, int N, int K, ezb_strea
 /* Batched form of the same kernel: Y[b, :] = W[N,K] . X[b, :] for b < B <= 64,
  * X [B,K], Y [B,N]; the weight is still streamed once for the whole batch.
  * (The reference op is batch 1 only; its fused ops hold the batched
- * projections, e.g. ezops/ops/qwen3_dense_decode.py:157.)  `workspace` is only
- * touched when B > 8 or B*K is large; it needs ezb_gemv_workspace_bytes(). */
-size_t ezb_gemv_workspace_bytes(int B, int K);
+ * projections, e.g. ezops/ops/qwen3_dense_decode.py:157.)  For B >= 2 the
+ * workspace of ezb_gemv_workspace_bytes() is required (zero-filled once): larger
+ * batches run on the tensor cores with a split over K that parks partial tiles
+ * there. */
+size_t ezb_gemv_workspace_bytes(int B, int N, int K);
 int ezb_gemv_batched_bf16(const void* X, const void* W, void* Y, void* workspace, size_t workspace_bytes, int B, int N,
                           int K, ezb_stream_t stream);
 

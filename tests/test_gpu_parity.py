@@ -90,8 +90,8 @@ def test_gemv_batched(ez, B, N, K):
     W = (torch.randn(N, K, generator=g) * 0.05).bfloat16()
     Y = torch.full((B, N), float("nan"), dtype=torch.bfloat16, device="cuda")
     Xd, Wd = dev(X, W)
-    ws = torch.zeros(256, dtype=torch.uint8, device="cuda")
     lib = _lib.load()
+    ws = torch.zeros(lib.ezb_gemv_workspace_bytes(B, N, K), dtype=torch.uint8, device="cuda")
     _lib.check(lib.ezb_gemv_batched_bf16(Xd.data_ptr(), Wd.data_ptr(), Y.data_ptr(), ws.data_ptr(), ws.numel(), B, N, K,
                                          torch.cuda.current_stream().cuda_stream))
     ref = (X.float() @ W.float().T).to(torch.bfloat16)
