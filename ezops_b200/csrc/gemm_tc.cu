@@ -36,6 +36,11 @@ static constexpr int kTcBlockK = 64;    // k elements per stage: 128 bytes, one 
 static constexpr int kTcThreads = 192;  // TMA warp, MMA warp, four epilogue warps
 static constexpr int kTcMaxStages = 10;
 static constexpr int kTcABytes = kTcRows * kTcBlockK * 2;
+// Projections of different shapes share one workspace, so the region of the
+// ticket counters (which must stay zero between launches) has one fixed size
+// and never overlaps the partial tiles of another projection.
+static constexpr size_t kTcCounterBytes = 16384;
+static constexpr int kTcMaxTiles = (int)(kTcCounterBytes / 4);
 
 struct TcParams {
     int N, K, B;          // output units (rows, or gate/up pairs), reduction length, batch
@@ -407,12 +412,12 @@ static bool make_map(CUtensorMap* map, const bf16* base, long long rows, long lo
 static int tc_batch_tile(int B) { return B <= 16 ? 16 : (B <= 32 ? 32 : 64); }
 
 bool gemm_tc_supported(int B, int K) { return B >= 2 && B <= 64 && K % 8 == 0 && encode_fn() != nullptr; }
+bool gemm_tc_fits(int N, bool pair) { return (N + (pair ? 63 : 127)) / (pair ? 64 : 128) <= kTcMaxTiles; }
 
 size_t gemm_tc_workspace_bytes(int B, int N, bool pair) {
+    (void)N, (void)pair;
     const int NB = tc_batch_tile(B);
-    const int tiles = (N + (pair ? 63 : 127)) / (pair ? 64 : 128);
-    const size_t counters = ((size_t)tiles * 4 + 255) / 256 * 256;
-    return counters + (size_t)sm_count() * 2 * NB * kTcRows * sizeof(float);
+    return kTcCounterBytes + (size_t)sm_count() * 2 * NB * kTcRows * sizeof(float);
 }
 
 template <int NB>
@@ -449,9 +454,9 @@ cudaError_t launch_gemm_tc(const GemvArgs& a, const bf16* x, long long ldx, void
     p.epilogue = a.epilogue;
     p.residual = a.residual, p.ldres = a.ldres;
     p.out = a.out, p.ldout = a.ldout;
-    const size_t counters = ((size_t)p.tiles * 4 + 255) / 256 * 256;
+    if (p.tiles > kTcMaxTiles) return cudaErrorInvalidValue;
     p.counters = reinterpret_cast<unsigned int*>(workspace);
-    p.partial = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + counters);
+    p.partial = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + kTcCounterBytes);
     p.status = status_ptr();
     if (!p.status) return cudaErrorUnknown;
     p.trace = trace_handle();

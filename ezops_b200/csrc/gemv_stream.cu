@@ -766,7 +766,7 @@ cudaError_t launch_gemv(const GemvArgs& a, cudaStream_t stream) {
     p.trace = trace_handle();
     p.trace_id = a.trace_id;
 
-    const bool use_tc = !rows8 && a.tc_workspace && tuning(EZB_TUNE_TC) != 0 && gemm_tc_supported(a.B, a.K);
+    const bool use_tc = !rows8 && a.tc_workspace && tuning(EZB_TUNE_TC) != 0 && gemm_tc_supported(a.B, a.K) && gemm_tc_fits(a.N, pair);
     if ((use_tc || !pl.xres) && a.prologue != PRO_NONE) {
         // The activation block is not resident in this path: run the prologue as
         // its own (tiny) kernel into the scratch rows, then stream those.

@@ -47,6 +47,7 @@ struct GemvArgs {
 
 // Tensor-core (tcgen05) path for batched projections, see gemm_tc.cu.
 bool gemm_tc_supported(int B, int K);
+bool gemm_tc_fits(int N, bool pair);  // tile count within the fixed ticket-counter region
 size_t gemm_tc_workspace_bytes(int B, int N, bool pair);
 cudaError_t launch_gemm_tc(const GemvArgs& a, const bf16* x, long long ldx, void* workspace, cudaStream_t stream);
 
