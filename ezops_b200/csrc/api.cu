@@ -83,7 +83,7 @@ static const int kTuningDefaults[EZB_TUNE_COUNT] = {
     0,    // EZB_TUNE_GEMV_PREFETCH (all stages)
     1,    // EZB_TUNE_GEMV_CTAS_PER_SM
     128,  // EZB_TUNE_ATTN_MIN_CHUNK
-    16,   // EZB_TUNE_ATTN_WAVES
+    8,    // EZB_TUNE_ATTN_WAVES
     0,    // EZB_TUNE_GEMV_KC (automatic)
     1,    // EZB_TUNE_GEMV_ROWS8
     0,    // EZB_TUNE_PDL_ACROSS_CALLS

@@ -185,40 +185,55 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapW0, const __grid_constant_
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            auto stage_addr = [&](long long it) { return smem_u32(stages + (size_t)(it % NS) * STAGE_BYTES); };
-            auto load_w = [&](long long u, long long it) {
-                const int tile = (int)(u / KB), kb = (int)(u % KB);
-                const uint32_t bar = smem_u32(&full_bar[it % NS]);
+            // One thread feeds the whole ring, so its per-unit cost matters: all counters
+            // are 32-bit and advance incrementally (no divisions in the loop).
+            const int n_units = (int)(u1 - u0);
+            int tile = (int)(u0 / KB), kb = (int)(u0 % KB);  // unit being requested
+            int stage = 0;
+            uint32_t empty_parity = 1;  // a fresh barrier passes a wait on parity 1
+            auto request_w = [&](int st, int t, int k) {
+                const uint32_t bar = smem_u32(&full_bar[st]);
                 mbar_arrive_expect_tx(bar, STAGE_BYTES);
-                const uint32_t a = stage_addr(it);
+                const uint32_t a = smem_u32(stages + (size_t)st * STAGE_BYTES);
                 if (p.pair) {
-                    tma_load_2d(a, &mapW0, kb * kTcBlockK, tile * (kTcRows / 2), bar);
-                    tma_load_2d(a + kTcABytes / 2, &mapW1, kb * kTcBlockK, tile * (kTcRows / 2), bar);
+                    tma_load_2d(a, &mapW0, k * kTcBlockK, t * (kTcRows / 2), bar);
+                    tma_load_2d(a + kTcABytes / 2, &mapW1, k * kTcBlockK, t * (kTcRows / 2), bar);
                 } else {
-                    tma_load_2d(a, &mapW0, kb * kTcBlockK, tile * kTcRows, bar);
+                    tma_load_2d(a, &mapW0, k * kTcBlockK, t * kTcRows, bar);
                 }
             };
-            auto load_x = [&](long long u, long long it) {
-                const int kb = (int)(u % KB);
-                tma_load_2d(stage_addr(it) + kTcABytes, &mapX, kb * kTcBlockK, 0, smem_u32(&full_bar[it % NS]));
+            auto request_x = [&](int st, int k) {
+                tma_load_2d(smem_u32(stages + (size_t)st * STAGE_BYTES) + kTcABytes, &mapX, k * kTcBlockK, 0,
+                            smem_u32(&full_bar[st]));
             };
             // weights do not depend on the kernel in front: request them before the dependency wait
-            const long long n_units = u1 - u0;
-            const long long npre = n_units < NS ? n_units : NS;
-            for (long long i = 0; i < npre; ++i) load_w(u0 + i, i);
+            const int npre = n_units < NS ? n_units : NS;
+            {
+                int t = tile, k = kb;
+                for (int i = 0; i < npre; ++i) {
+                    request_w(i, t, k);
+                    if (++k == KB) k = 0, ++t;
+                }
+            }
             pdl_wait();
-            for (long long i = 0; i < npre; ++i) load_x(u0 + i, i);
-            long long issued = npre;
-            for (long long i = npre; i < n_units; ++i) {
-                const uint32_t parity = (uint32_t)(((i / NS) & 1) ^ 1);
-                if (!mbar_wait_bounded(smem_u32(&empty_bar[i % NS]), parity, abort_flag, p.status, FAULT_GEMV_EMPTY_WAIT)) break;
-                load_w(u0 + i, i);
-                load_x(u0 + i, i);
+            for (int i = 0; i < npre; ++i) {
+                request_x(i, kb);
+                if (++kb == KB) kb = 0, ++tile;
+            }
+            int issued = npre;
+            stage = (npre == NS) ? 0 : npre;
+            if (npre == NS) empty_parity = 0;
+            for (int i = npre; i < n_units; ++i) {
+                if (!mbar_wait_bounded(smem_u32(&empty_bar[stage]), empty_parity, abort_flag, p.status, FAULT_GEMV_EMPTY_WAIT)) break;
+                request_w(stage, tile, kb);
+                request_x(stage, kb);
+                if (++kb == KB) kb = 0, ++tile;
+                if (++stage == NS) stage = 0, empty_parity ^= 1;
                 issued = i + 1;
             }
             if (*abort_flag) {  // nothing may still be landing in this CTA's shared memory when it exits
-                const long long first = issued > NS ? issued - NS : 0;
-                for (long long i = first; i < issued; ++i) {
+                const int first = issued > NS ? issued - NS : 0;
+                for (int i = first; i < issued; ++i) {
                     const long long t0 = clock64();
                     while (!mbar_try_wait(smem_u32(&full_bar[i % NS]), (uint32_t)((i / NS) & 1)))
                         if (clock64() - t0 > kWaitLimitCycles) {
@@ -231,12 +246,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapW0, const __grid_constant_
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            long long it = 0;
-            int seg = 0;
-            for (long long u = u0; u < u1 && !(*abort_flag);) {
-                const int kb0 = (int)(u % KB);
-                const long long left = u1 - u;
-                const int kb1 = (KB - kb0 < left) ? KB : kb0 + (int)left;
+            const int n_units = (int)(u1 - u0);
+            int kb0 = (int)(u0 % KB);
+            int done = 0, seg = 0, stage = 0;
+            uint32_t full_parity = 0;
+            while (done < n_units && !(*abort_flag)) {
+                const int left = n_units - done;
+                const int kb1 = (KB - kb0 < left) ? KB : kb0 + left;
                 const int acc = seg & 1;
                 // wait until the epilogue has drained this accumulator (passes at once for its first use)
                 if (!mbar_wait_bounded(smem_u32(&acc_empty[acc]), (uint32_t)(((seg >> 1) & 1) ^ 1), abort_flag, p.status,
@@ -244,22 +260,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapW0, const __grid_constant_
                     break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * NB);
-                for (int kb = kb0; kb < kb1; ++kb, ++it) {
-                    const int s = (int)(it % NS);
-                    if (!mbar_wait_bounded(smem_u32(&full_bar[s]), (uint32_t)((it / NS) & 1), abort_flag, p.status,
-                                           FAULT_GEMV_FULL_WAIT))
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!mbar_wait_bounded(smem_u32(&full_bar[stage]), full_parity, abort_flag, p.status, FAULT_GEMV_FULL_WAIT))
                         break;
                     tc_fence_after();
-                    const uint32_t a_addr = smem_u32(stages + (size_t)s * STAGE_BYTES);
+                    const uint32_t a_addr = smem_u32(stages + (size_t)stage * STAGE_BYTES);
                     const uint64_t adesc = umma_desc_sw128(a_addr);
                     const uint64_t bdesc = umma_desc_sw128(a_addr + kTcABytes);
 #pragma unroll
                     for (int k = 0; k < kTcBlockK / 16; ++k)  // 32 bytes along K per MMA: +2 in the 16-byte address field
                         tc_mma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, IDESC, (kb > kb0 || k > 0) ? 1u : 0u);
-                    tc_commit(smem_u32(&empty_bar[s]));  // stage reusable once these MMAs have read it
+                    tc_commit(smem_u32(&empty_bar[stage]));  // stage reusable once these MMAs have read it
+                    if (++stage == NS) stage = 0, full_parity ^= 1;
                 }
                 tc_commit(smem_u32(&acc_full[acc]));
-                u += kb1 - kb0;
+                done += kb1 - kb0;
+                kb0 = 0;  // every later segment starts a new tile
                 ++seg;
             }
         }
@@ -270,12 +286,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapW0, const __grid_constant_
         const int et = (warp - 2) * 32 + lane;
         pdl_wait();
         trace_mark(trec, 3);
-        int seg = 0;
-        for (long long u = u0; u < u1; ++seg) {
-            const int tile = (int)(u / KB), kb0 = (int)(u % KB);
-            const long long left = u1 - u;
-            const int kb1 = (KB - kb0 < left) ? KB : kb0 + (int)left;
+        const int n_units = (int)(u1 - u0);
+        int tile = (int)(u0 / KB), kb0 = (int)(u0 % KB), done = 0;
+        for (int seg = 0; done < n_units; ++seg, ++tile, kb0 = 0) {
+            const int left = n_units - done;
+            const int kb1 = (KB - kb0 < left) ? KB : kb0 + left;
             const int acc = seg & 1;
+            done += kb1 - kb0;
             mbar_wait_bounded(smem_u32(&acc_full[acc]), (uint32_t)((seg >> 1) & 1), abort_flag, p.status, FAULT_TC_ACC_WAIT);
             if (seg == 0) trace_mark(trec, 4);
             tc_fence_after();
@@ -291,7 +308,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapW0, const __grid_constant_
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&acc_empty[acc]));
-            u += kb1 - kb0;
 
             const bool whole = (kb0 == 0 && kb1 == KB);
             bool finish = whole;
@@ -329,18 +345,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapW0, const __grid_constant_
             if (!p.pair) {
                 const int n = tile * kTcRows + row;
                 if (n < p.N) {
+                    if (p.epilogue == EPI_RESIDUAL) {
+                        // all residual values are fetched before the first store: the stores may alias
+                        // them as far as the compiler knows, which would serialise 64 L2 round trips
+                        float res[NB];
 #pragma unroll
-                    for (int b = 0; b < NB; ++b) {
-                        if (b >= p.B) break;
-                        const long long o = (long long)b * p.ldout + n;
-                        if (p.epilogue == EPI_STORE_F32) {
-                            reinterpret_cast<float*>(p.out)[o] = v[b];
-                        } else if (p.epilogue == EPI_RESIDUAL) {
-                            const float res = __bfloat162float(p.residual[(long long)b * p.ldres + n]);
-                            reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16_rn(res + round_bf16(v[b]));
-                        } else {
-                            reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16_rn(v[b]);
-                        }
+                        for (int b = 0; b < NB; ++b)
+                            res[b] = (b < p.B) ? __bfloat162float(p.residual[(long long)b * p.ldres + n]) : 0.f;
+#pragma unroll
+                        for (int b = 0; b < NB; ++b)
+                            if (b < p.B)
+                                reinterpret_cast<bf16*>(p.out)[(long long)b * p.ldout + n] =
+                                    __float2bfloat16_rn(res[b] + round_bf16(v[b]));
+                    } else if (p.epilogue == EPI_STORE_F32) {
+#pragma unroll
+                        for (int b = 0; b < NB; ++b)
+                            if (b < p.B) reinterpret_cast<float*>(p.out)[(long long)b * p.ldout + n] = v[b];
+                    } else {
+#pragma unroll
+                        for (int b = 0; b < NB; ++b)
+                            if (b < p.B) reinterpret_cast<bf16*>(p.out)[(long long)b * p.ldout + n] = __float2bfloat16_rn(v[b]);
                     }
                 }
             } else {
