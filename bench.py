@@ -28,6 +28,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import signal
 import sys
 import threading
 import time
@@ -419,10 +420,22 @@ def main():
             "roofline": roofline, "cpu_baseline": cpu, "check_vs_torch_ref": check, "device_status": status,
         }
         print(json.dumps(line), flush=True)
+    sys.stdout.flush()
+    sys.stderr.flush()
     if world > 1:
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+    # Leave without tearing NCCL down: destroying the communicator while CUDA graphs that captured
+    # its kernels are still alive was seen to block for minutes.  Everything is already printed.
+    os._exit(0)
+
+
+def _watchdog(signum, frame):  # a benchmark must never sit in a hang until the caller's limit
+    print(json.dumps({"error": "bench.py watchdog: no result within the time limit", "impl": "ours"}), flush=True)
+    os._exit(3)
 
 
 if __name__ == "__main__":
+    signal.signal(signal.SIGALRM, _watchdog)
+    signal.alarm(int(os.environ.get("EZB_BENCH_LIMIT_S", "900")))
     main()
