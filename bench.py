@@ -47,6 +47,8 @@ UNIT = "GB/s"
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--exchange", choices=["auto", "fused", "nccl"], default="auto",
+                    help="N > 1: how the two sums over ranks of a layer are done")
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
@@ -198,7 +200,7 @@ def workload_config(args, shape, n):
         "workload": f"{shape.name} dense decode layer, batch {args.batch}, kv_len {args.seq_len}, bf16, tp{n}",
         "hidden": shape.hidden, "intermediate": shape.inter, "heads": f"{shape.num_heads}q/{shape.num_kv_heads}kv x {shape.head_dim}",
         "parallelism": f"tp{n}",
-        "cache_policy": f"inputs larger than L2: steps rotate over {NUM_WEIGHT_SETS} weight+KV sets",
+        "cache_policy": f"inputs larger than L2: steps rotate over {NUM_WEIGHT_SETS * n} weight+KV sets per GPU",
         "pdl_across_calls": not getattr(args, "no_cross_call_pdl", False),
     }
 
@@ -241,10 +243,13 @@ def main():
     B, S, H, I = args.batch, args.seq_len, shape.hidden, shape.inter
     NH, NKV, D = shape.num_heads, shape.num_kv_heads, shape.head_dim
 
-    # ---- resident state: NUM_WEIGHT_SETS layers' weights and KV caches ----
+    # ---- resident state: nsets layers' weights and KV caches (a rank's shard shrinks
+    # with the number of ranks, so the number of sets grows with it: every rank
+    # always rotates over more than four times the L2 capacity) ----
+    nsets = NUM_WEIGHT_SETS * tp
     gen = torch.Generator(device=device)
     sets = []
-    for i in range(NUM_WEIGHT_SETS):
+    for i in range(nsets):
         gen.manual_seed(1000 + i)  # same seed on every rank: consistent shards
         rn = lambda *s, std=1.0: (torch.randn(*s, generator=gen, device=device, dtype=torch.float32) * std).to(torch.bfloat16)
         Wqkv, Wo = rn(shape.q_rows + 2 * shape.kv_rows, H, std=0.02), rn(H, shape.q_rows, std=0.02)
@@ -266,8 +271,14 @@ def main():
         def layer(hidden, wset, out):
             return kernel(hidden, *wset, out=out)
     else:
-        lay = tpm.TensorParallelDecodeLayer(B, S, H, I, NH, D, NKV)
-        launches_per_step = 6
+        # Sums over ranks inside the projection kernels (peer stores over NVLink) when the
+        # batch allows it, NCCL all-reduce between the three local parts otherwise.
+        exchange = args.exchange
+        if exchange == "auto":
+            fits = all(B * (k + 32) * 2 <= 72 * 1024 for k in (H, NH // tp * D, I // tp))
+            exchange = "fused" if B <= 8 and fits else "nccl"
+        lay = tpm.TensorParallelDecodeLayer(B, S, H, I, NH, D, NKV, exchange=exchange)
+        launches_per_step = 6 if exchange == "fused" else 7
 
         def layer(hidden, wset, out):
             return lay(hidden, *wset, out=out)
@@ -287,7 +298,7 @@ def main():
         h = hidden0
         for i in range(n):
             out = bufs[(first + i) & 1]
-            layer(h, sets[(first + i) % NUM_WEIGHT_SETS], out)
+            layer(h, sets[(first + i) % nsets], out)
             h = out
 
     def sync_all():
@@ -345,7 +356,7 @@ def main():
 
         def e2e_step(i):
             dev_in.copy_(host_in, non_blocking=True)
-            layer(dev_in, sets[i % NUM_WEIGHT_SETS], dev_out)
+            layer(dev_in, sets[i % nsets], dev_out)
             host_out.copy_(dev_out, non_blocking=True)
             stream.synchronize()
 
@@ -376,7 +387,7 @@ def main():
     X = hidden0
 
     def roof_launch(i):
-        W = sets[i % NUM_WEIGHT_SETS][4]
+        W = sets[i % nsets][4]
         _lib.check(lib.ezb_gemv_batched_bf16(X.data_ptr(), W.data_ptr(), Y.data_ptr(), ws.data_ptr(), ws.numel(), B,
                                              rows_local, H, torch.cuda.current_stream().cuda_stream))
 
@@ -393,10 +404,10 @@ def main():
     kernel_bytes = 2 * (rows_local * H + B * H + B * rows_local)
     achieved = kernel_bytes / launch_s / 1e9
     roofline = {
-        "bound": "hbm", "kernel": "gemv_stream_kernel", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+        "bound": "hbm", "kernel": "gemv_rows8_kernel" if B <= 8 else "gemm_tc_kernel", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
         "frac": achieved / peaks["hbm_gbs"], "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs, burst copy)",
         "traffic": None, "bytes_per_launch": kernel_bytes, "us_per_launch": launch_s * 1e6,
-        "workload": f"W [{rows_local}, {H}] bf16 (gate/up-sized), batch {B}, {n_roof} back-to-back launches over {NUM_WEIGHT_SETS} weights",
+        "workload": f"W [{rows_local}, {H}] bf16 (gate/up-sized), batch {B}, {n_roof} back-to-back launches over {nsets} weights",
     }
 
     # ---- CPU oracle beside it (rank 0, single-GPU run only) ----

@@ -64,6 +64,13 @@ SIGNATURES = {
     "ezb_qwen3_decode_layer_tp_attn": (c_int, [c_void_p] * 7 + [c_size_t] + [c_int] * 6 + [c_float, c_void_p]),
     "ezb_qwen3_decode_layer_tp_ffn": (c_int, [c_void_p] * 7 + [c_size_t] + [c_int] * 3 + [c_float, c_void_p]),
     "ezb_residual_add_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "ezb_tp_comm_bytes": (c_size_t, [c_int, c_int]),
+    "ezb_tp_comm_alloc": (c_int, [c_size_t, POINTER(c_void_p)]),
+    "ezb_tp_comm_free": (c_int, [c_void_p]),
+    "ezb_ipc_export": (c_int, [c_void_p, c_void_p]),
+    "ezb_ipc_open": (c_int, [c_void_p, POINTER(c_void_p)]),
+    "ezb_ipc_close": (c_int, [c_void_p]),
+    "ezb_qwen3_decode_layer_tp_fused": (c_int, [c_void_p] * 9 + [c_size_t, POINTER(c_void_p)] + [c_int] * 9 + [c_float, c_void_p]),
 }
 
 _lib = None

@@ -577,6 +577,131 @@ int ezb_qwen3_decode_layer_tp_ffn(const void* hidden, const float* summed_o, con
     return EZB_OK;
 }
 
+size_t ezb_tp_comm_bytes(int B, int H) {
+    if (B < 1 || H < 1) return 0;
+    return (size_t)kTpCtrlBytes + (size_t)2 * kTpSlots * B * H * sizeof(unsigned long long);
+}
+
+int ezb_tp_comm_alloc(size_t bytes, void** out) {
+    EZB_REQUIRE(out && bytes >= (size_t)kTpCtrlBytes, "bad arguments");
+    void* p = nullptr;
+    EZB_CUDA_TRY(cudaMalloc(&p, bytes));
+    cudaError_t e = cudaMemset(p, 0, bytes);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        set_last_cuda_error(e);
+        return EZB_ERR_CUDA;
+    }
+    *out = p;
+    return EZB_OK;
+}
+
+int ezb_tp_comm_free(void* p) {
+    if (p) EZB_CUDA_TRY(cudaFree(p));
+    return EZB_OK;
+}
+
+int ezb_ipc_export(void* ptr, void* handle64) {
+    EZB_REQUIRE(ptr && handle64, "null pointer");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaIpcMemHandle_t h;
+    EZB_CUDA_TRY(cudaIpcGetMemHandle(&h, ptr));
+    std::memcpy(handle64, &h, sizeof(h));
+    return EZB_OK;
+}
+
+int ezb_ipc_open(const void* handle64, void** out) {
+    EZB_REQUIRE(handle64 && out, "null pointer");
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle64, sizeof(h));
+    void* p = nullptr;
+    EZB_CUDA_TRY(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    *out = p;
+    return EZB_OK;
+}
+
+int ezb_ipc_close(void* ptr) {
+    if (ptr) EZB_CUDA_TRY(cudaIpcCloseMemHandle(ptr));
+    return EZB_OK;
+}
+
+int ezb_qwen3_decode_layer_tp_fused(const void* hidden, void* K_cache, void* V_cache, const void* Wqkv_local,
+                                    const void* Wo_local, const void* Wgu_local, const void* Wd_local, void* out,
+                                    void* workspace, size_t workspace_bytes, void* const* comm_bases_host, int world,
+                                    int rank, int B, int S, int H, int I_local, int NH_local, int NKV_local, int D, float eps,
+                                    ezb_stream_t stream) {
+    EZB_REQUIRE(hidden && K_cache && V_cache && Wqkv_local && Wo_local && Wgu_local && Wd_local && out && comm_bases_host,
+                "null pointer");
+    EZB_REQUIRE(world >= 1 && world <= kTpSlots && rank >= 0 && rank < world, "world must be 1..8 and rank inside it");
+    if (int rc = check_layer_args(B, S, H, I_local, NH_local, NKV_local, D)) return rc;
+    EZB_REQUIRE_SHAPE(gemv_small_batch_eligible(B, H) && gemv_small_batch_eligible(B, NH_local * D) &&
+                          gemv_small_batch_eligible(B, I_local),
+                      "the fused exchange needs a batch small enough for the resident-activation kernel");
+    EZB_REQUIRE(aligned16(hidden) && aligned16(K_cache) && aligned16(V_cache) && aligned16(Wqkv_local) &&
+                    aligned16(Wo_local) && aligned16(Wgu_local) && aligned16(Wd_local) && aligned16(out),
+                "pointers must be 16-byte aligned");
+    for (int w = 0; w < world; ++w) EZB_REQUIRE(comm_bases_host[w] && aligned16(comm_bases_host[w]), "bad comm buffer pointer");
+    LayerWorkspace w = carve_layer_ws(workspace, B, S, H, I_local, NH_local, NKV_local, D);
+    if (!workspace || workspace_bytes < w.total) {
+        set_last_message("workspace missing or smaller than ezb_qwen3_decode_layer_workspace_bytes()");
+        return EZB_ERR_WORKSPACE;
+    }
+    TpLink base = {world, rank, {}, {}, (long long)B * H, -1, -1, -1};
+    for (int r = 0; r < world; ++r) {
+        base.ctrl_peer[r] = static_cast<unsigned int*>(comm_bases_host[r]);
+        base.inbox_peer[r] = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(comm_bases_host[r]) + kTpCtrlBytes);
+    }
+    const bf16* hid = static_cast<const bf16*>(hidden);
+    const bf16* wgu = static_cast<const bf16*>(Wgu_local);
+    const int Q = NH_local * D;
+    const int pf_kb = tuning(EZB_TUNE_L2_PREFETCH_KB);
+    chain_begin();
+    EZB_CUDA_TRY(launch_qkv_and_attention(hid, static_cast<bf16*>(K_cache), static_cast<bf16*>(V_cache),
+                                          static_cast<const bf16*>(Wqkv_local), w, B, S, H, NH_local, NKV_local, D, eps, stream,
+                                          static_cast<const bf16*>(Wo_local)));
+    {   // o_proj: partial -> inbox 0 of every rank; its last CTA also opens the next epoch of inbox 1
+        GemvArgs g;
+        g.W0 = static_cast<const bf16*>(Wo_local), g.ldw = Q, g.N = H, g.K = Q, g.B = B;
+        g.x = w.attn_out, g.ldx = Q;
+        g.epilogue = EPI_PUSH_F32, g.ldout = H;
+        g.link = base, g.link.push_inbox = 0, g.link.bump_inbox = 1;
+        g.next = one_plan(next_rows(wgu, wgu + (size_t)I_local * H, I_local, H, pf_kb));
+        g.trace_id = 3;
+        EZB_CUDA_TRY(launch_gemv(g, stream));
+    }
+    {   // gate/up: x2 = hidden + sum(inbox 0), norm, SwiGLU
+        GemvArgs g;
+        g.W0 = wgu, g.W1 = wgu + (size_t)I_local * H, g.ldw = H, g.N = I_local, g.K = H, g.B = B;
+        g.x = hid, g.ldx = H;
+        g.x_sum_out = w.x2, g.ldsum = H;
+        g.eps = eps, g.prologue = PRO_ADD_RMSNORM, g.epilogue = EPI_SWIGLU;
+        g.out = w.h, g.ldout = I_local;
+        g.link = base, g.link.gather_inbox = 0;
+        g.next = one_plan(next_rows(static_cast<const bf16*>(Wd_local), nullptr, H, I_local, pf_kb));
+        g.trace_id = 4;
+        EZB_CUDA_TRY(launch_gemv(g, stream));
+    }
+    {   // down: partial -> inbox 1 of every rank; opens the next epoch of inbox 0
+        GemvArgs g;
+        g.W0 = static_cast<const bf16*>(Wd_local), g.ldw = I_local, g.N = H, g.K = I_local, g.B = B;
+        g.x = w.h, g.ldx = I_local;
+        g.epilogue = EPI_PUSH_F32, g.ldout = H;
+        g.link = base, g.link.push_inbox = 1, g.link.bump_inbox = 0;
+        g.trace_id = 5;
+        EZB_CUDA_TRY(launch_gemv(g, stream));
+    }
+    {   // out = x2 + sum(inbox 1)
+        RowPrepArgs a;
+        a.x = w.x2, a.ldx = H;
+        a.sum_out = static_cast<bf16*>(out), a.ldsum = H;
+        a.rows = B, a.dim = H, a.normalize = 0;
+        a.link = base, a.link.gather_inbox = 1;
+        EZB_CUDA_TRY(launch_row_prep(a, stream));
+    }
+    return EZB_OK;
+}
+
 int ezb_residual_add_f32(const void* x2, const float* summed_d, void* out, int B, int H, ezb_stream_t stream) {
     EZB_REQUIRE(x2 && summed_d && out, "null pointer");
     EZB_REQUIRE(B >= 1 && H >= 1, "sizes must be positive");

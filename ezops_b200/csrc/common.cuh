@@ -27,7 +27,7 @@ enum DeviceFault : unsigned int {
     FAULT_GEMV_EMPTY_WAIT = 0x102,  // producer never got a stage back
     FAULT_GEMV_DRAIN = 0x103,       // copies still in flight at exit
     FAULT_TC_ACC_WAIT = 0x104,      // tensor-memory accumulator hand-over never happened
-    FAULT_AR_FLAG_WAIT = 0x201,     // a peer's all-reduce flag never arrived
+    FAULT_AR_FLAG_WAIT = 0x201,     // a peer's partial result never arrived in the inbox
 };
 
 __device__ __forceinline__ void report_fault(unsigned int* status, unsigned int code) {
@@ -37,6 +37,102 @@ __device__ __forceinline__ void report_fault(unsigned int* status, unsigned int 
 // About one second at B200 clocks; no legitimate wait in this library comes
 // within five orders of magnitude of it.
 static constexpr long long kWaitLimitCycles = 2000000000LL;
+
+// ---------------------------------------------------------------------------
+// Tensor-parallel exchange over peer memory (one-shot all-reduce split between
+// the kernel that produces a partial result and the kernel that consumes the
+// sum).  Every rank owns one buffer, mapped by all ranks:
+//   control words (u32): [0],[1] epoch of inbox 0 / 1;
+//   then two inboxes of 8 slots x slot_elems 64-bit cells: slot r of an inbox
+//   holds the partial [B, H] that rank r pushed, every cell = {fp32 value in
+//   the low half, epoch in the high half}.
+// A producer stores each fp32 output, tagged with epoch+1, into slot `rank` of
+// the chosen inbox of EVERY rank: one 64-bit peer store per value over NVLink,
+// single-copy atomic, no fence and no flag behind it.  A consumer polls the cells
+// of its own inbox (bounded) until their tag shows epoch+1 and adds the values
+// in rank order, so every rank computes the same bits; a value is usable the
+// moment its own store lands.  Epochs live on the device and are advanced by a
+// later kernel of the chain, so a captured CUDA graph can be replayed.  Two
+// inboxes alternate (after o_proj / after down_proj); a rank can only push to an
+// inbox again after every peer has consumed its previous content, because the
+// pushes and polls of the other inbox lie in between.
+// ---------------------------------------------------------------------------
+struct TpLink {
+    int world;  // 0: no fused exchange
+    int rank;
+    unsigned int* ctrl_peer[8];
+    unsigned long long* inbox_peer[8];
+    long long slot_elems;
+    int push_inbox;    // -1 or the inbox this kernel's outputs are pushed into
+    int gather_inbox;  // -1 or the inbox whose slots this kernel's prologue sums
+    int bump_inbox;    // -1 or the inbox whose epoch this kernel advances
+};
+static constexpr int kTpEpoch = 0;
+static constexpr int kTpCtrlBytes = 256;
+static constexpr int kTpSlots = 8;
+
+__device__ __forceinline__ unsigned long long* tp_slot(const TpLink& l, int on_rank, int inbox, int slot) {
+    return l.inbox_peer[on_rank] + ((long long)inbox * kTpSlots + slot) * l.slot_elems;
+}
+// The tag the next push into / poll of `inbox` uses.
+__device__ __forceinline__ unsigned int tp_next_epoch(const TpLink& l, int inbox) {
+    return l.ctrl_peer[l.rank][kTpEpoch + inbox] + 1u;
+}
+__device__ __forceinline__ void tp_push(const TpLink& l, long long elem, float v, unsigned int epoch) {
+    const unsigned long long cell = ((unsigned long long)epoch << 32) | (unsigned long long)__float_as_uint(v);
+    for (int w = 0; w < l.world; ++w)
+        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(tp_slot(l, w, l.push_inbox, l.rank) + elem), "l"(cell) : "memory");
+}
+// Called by exactly one thread of the grid, anywhere in the kernel.
+__device__ __forceinline__ void tp_bump(const TpLink& l) { l.ctrl_peer[l.rank][kTpEpoch + l.bump_inbox] += 1u; }
+
+// add[0..7] += sum over ranks (in rank order) of the 8 consecutive cells starting
+// at `elem` of this rank's inbox; polls until every cell carries `epoch`.
+// Returns false (and records the fault) if the wait limit ran out.
+__device__ __forceinline__ bool tp_gather8(const TpLink& l, unsigned int epoch, long long elem, float (&add)[8],
+                                           unsigned int* status, long long t0) {
+    constexpr int G = 4;  // ranks polled together
+    for (int w0 = 0; w0 < l.world; w0 += G) {
+        unsigned long long c[G][8];
+        unsigned int pending = 0;
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+            if (w0 + g < l.world) pending |= 1u << g;
+        while (true) {
+#pragma unroll
+            for (int g = 0; g < G; ++g)
+                if (pending & (1u << g)) {
+                    const unsigned long long* src = tp_slot(l, l.rank, l.gather_inbox, w0 + g) + elem;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];"
+                                     : "=l"(c[g][2 * q]), "=l"(c[g][2 * q + 1])
+                                     : "l"(src + 2 * q)
+                                     : "memory");
+                }
+#pragma unroll
+            for (int g = 0; g < G; ++g)
+                if (pending & (1u << g)) {
+                    bool all = true;
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) all = all && ((unsigned int)(c[g][e] >> 32) == epoch);
+                    if (all) pending &= ~(1u << g);
+                }
+            if (!pending) break;
+            if (clock64() - t0 > kWaitLimitCycles) {
+                report_fault(status, FAULT_AR_FLAG_WAIT);
+                return false;
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+            if (w0 + g < l.world) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) add[e] += __uint_as_float((unsigned int)c[g][e]);
+            }
+    }
+    return true;
+}
 
 // ---------------------------------------------------------------------------
 // Optional timeline tracing (off unless ezb_trace_enable() was called): thread 0

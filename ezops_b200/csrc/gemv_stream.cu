@@ -72,6 +72,7 @@ struct GemvParams {
     PrefetchList next;
     Trace trace;
     int trace_id;
+    TpLink link;
 };
 
 __host__ __device__ constexpr size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -126,6 +127,51 @@ __device__ __forceinline__ void stage_activations(const GemvParams& p, bf16* xs,
                                                   int cw, int lane) {
     constexpr int U = 8;  // independent 16-byte loads in flight per thread
     const int nvec = p.K / 8;
+    if (p.link.world > 0 && p.link.gather_inbox >= 0) {
+        // Fused tensor-parallel sum: x <- rmsnorm(bf16(x + bf16(sum over ranks of the inbox slots))).
+        const TpLink& l = p.link;
+        const unsigned int epoch = tp_next_epoch(l, l.gather_inbox);
+        const long long t0 = clock64();
+        for (int b = 0; b < p.B; ++b) {
+            const bf16* xrow = p.x + (long long)b * p.ldx;
+            bf16* srow = xs + (size_t)b * xs_stride;
+            float ssq = 0.f;
+            for (int i = ct; i < nvec; i += kConsumerThreads) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(xrow + i * 8);
+                float add[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                tp_gather8(l, epoch, (long long)b * p.K + i * 8, add, p.status, t0);
+                uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    w4[e] = pack_bf16(bf16_lo(w4[e]) + round_bf16(add[2 * e]), bf16_hi(w4[e]) + round_bf16(add[2 * e + 1]));
+                if (blockIdx.x == 0 && p.x_sum_out)
+                    *reinterpret_cast<uint4*>(p.x_sum_out + (long long)b * p.ldsum + i * 8) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float lo = bf16_lo(w4[e]), hi = bf16_hi(w4[e]);
+                    ssq += lo * lo + hi * hi;
+                }
+                store_x8<PERMUTE32>(srow, i, w4);
+            }
+            ssq = warp_sum(ssq);
+            if (lane == 0) scratch[cw] = ssq;
+            named_bar_sync(1, kConsumerThreads);
+            float tot = 0.f;
+#pragma unroll
+            for (int w = 0; w < kConsumerWarps; ++w) tot += scratch[w];
+            const float r = 1.0f / sqrtf(tot / (float)p.K + p.eps);
+            for (int i = ct; i < nvec; i += kConsumerThreads) {
+                uint32_t w4[4];
+                load_x8<PERMUTE32>(srow, i, w4);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) w4[e] = pack_bf16(bf16_lo(w4[e]) * r, bf16_hi(w4[e]) * r);
+                store_x8<PERMUTE32>(srow, i, w4);
+            }
+            named_bar_sync(1, kConsumerThreads);
+        }
+        named_bar_sync(1, kConsumerThreads);
+        return;
+    }
     for (int b = 0; b < p.B; ++b) {
         const bf16* xrow = p.x + (long long)b * p.ldx;
         bf16* srow = xs + (size_t)b * xs_stride;
@@ -526,6 +572,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_rows8_kernel(const GemvP
             const int b = i / rows_here, r = i - b * rows_here;
             res_s[i] = __bfloat162float(p.residual[(long long)b * p.ldres + r0 + r]);
         }
+    const unsigned int push_epoch = (p.link.world > 0 && p.link.push_inbox >= 0) ? tp_next_epoch(p.link, p.link.push_inbox) : 0u;
     stage_activations<true>(p, xs, xs_stride, red, ct, cw, lane);  // ends with a barrier among the consumers
 
     const int g4 = lane >> 2, t4 = lane & 3;
@@ -577,12 +624,16 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_rows8_kernel(const GemvP
                 if (res_in_smem) {
                     const float res = res_s[b * rows_here + (n - r0)];
                     reinterpret_cast<bf16*>(p.out)[(long long)b * p.ldout + n] = __float2bfloat16_rn(res + round_bf16(v0));
+                } else if (p.epilogue == EPI_PUSH_F32) {
+                    // this rank's partial goes into its slot of the inbox on every rank
+                    tp_push(p.link, (long long)b * p.ldout + n, v0, push_epoch);
                 } else {
                     store_output(p, b, n, v0, v1);
                 }
             }
         }
     }
+    if (p.link.world > 0 && p.link.bump_inbox >= 0 && blockIdx.x == 0 && ct == 0) tp_bump(p.link);
     trace_mark(trec, 5);
 }
 
@@ -602,6 +653,7 @@ static int pick_nt(int B) { return B <= 8 ? 1 : (B <= 16 ? 2 : (B <= 32 ? 4 : 8)
 static bool x_fits_resident(int B, int K) { return (size_t)B * (K + 8) * 2 <= 72 * 1024 && B <= 8; }
 
 bool gemv_needs_scratch(int B, int K) { return !x_fits_resident(B, K); }
+
 
 PrefetchPlan prefetch_plan_rows(const bf16* W0, const bf16* W1, int N, int K, int cap_rows, int skip_rows) {
     PrefetchPlan pf;
@@ -727,6 +779,14 @@ static bool plan_rows8(const GemvArgs& a, GemvPlan& pl) {
     return true;
 }
 
+bool gemv_small_batch_eligible(int B, int K) {
+    if (tuning(EZB_TUNE_GEMV_ROWS8) == 0) return false;
+    GemvArgs a;
+    a.B = B, a.K = K, a.N = 1 << 20;
+    GemvPlan pl;
+    return plan_rows8(a, pl);
+}
+
 template <bool PAIR>
 static cudaError_t launch_rows8(const GemvParams& p, const GemvPlan& pl, cudaStream_t stream) {
     auto kernel = gemv_rows8_kernel<PAIR>;
@@ -765,7 +825,9 @@ cudaError_t launch_gemv(const GemvArgs& a, cudaStream_t stream) {
     if (!tuning(EZB_TUNE_L2_PREFETCH)) p.next.plan[0].units = p.next.plan[1].units = 0;
     p.trace = trace_handle();
     p.trace_id = a.trace_id;
+    p.link = a.link;
 
+    if (a.link.world > 0 && !rows8) return cudaErrorNotSupported;  // the fused exchange lives in the small-batch kernel
     const bool use_tc = !rows8 && a.tc_workspace && tuning(EZB_TUNE_TC) != 0 && gemm_tc_supported(a.B, a.K) && gemm_tc_fits(a.N, pair);
     if ((use_tc || !pl.xres) && a.prologue != PRO_NONE) {
         // The activation block is not resident in this path: run the prologue as

@@ -18,6 +18,7 @@ enum GemvEpilogue : int {
     EPI_RESIDUAL = 1,   // out = bf16(residual + bf16(acc))
     EPI_SWIGLU = 2,     // out = bf16(bf16(silu(bf16(acc_gate))) * bf16(acc_up))
     EPI_STORE_F32 = 3,  // out = acc (fp32)
+    EPI_PUSH_F32 = 4,   // acc (fp32) stored into this rank's slot of an inbox on every rank (see TpLink)
 };
 
 struct GemvArgs {
@@ -43,7 +44,9 @@ struct GemvArgs {
     PrefetchList next = {};  // what the following kernels stream first (optional)
     int trace_id = 0;  // label in timeline traces
     void* tc_workspace = nullptr;  // gemm_tc_workspace_bytes(): enables the tensor-core path for batch >= 2
+    TpLink link = {0, 0, {}, {}, 0, -1, -1, -1};  // fused tensor-parallel exchange (small-batch kernel only)
 };
+bool gemv_small_batch_eligible(int B, int K);  // true when launch_gemv would run the small-batch kernel
 
 // Tensor-core (tcgen05) path for batched projections, see gemm_tc.cu.
 bool gemm_tc_supported(int B, int K);
@@ -76,6 +79,7 @@ struct RowPrepArgs {
     int rows = 0, dim = 0;
     float eps = 1e-6f;
     int normalize = 1;
+    TpLink link = {0, 0, {}, {}, 0, -1, -1, -1};  // gather_inbox >= 0: `add` is the sum of that inbox's slots
 };
 cudaError_t launch_row_prep(const RowPrepArgs& a, cudaStream_t stream);
 cudaError_t launch_rmsnorm_f32(const float* X, float* Out, int rows, int dim, float eps, cudaStream_t stream);

@@ -83,11 +83,21 @@ struct RowPrepParams {
     int dim;
     float eps;
     int normalize;
+    TpLink link;
+    unsigned int* status;
 };
 
-__device__ __forceinline__ uint4 load_row8(const RowPrepParams& p, long long row, int i) {
+__device__ __forceinline__ uint4 load_row8(const RowPrepParams& p, long long row, int i, unsigned int epoch, long long t0) {
     uint4 raw = *reinterpret_cast<const uint4*>(p.x + row * p.ldx + i * 8);
-    if (p.add) {
+    if (p.link.world > 0 && p.link.gather_inbox >= 0) {
+        // the term to add is the sum, in rank order, of the partials in this rank's inbox
+        float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        tp_gather8(p.link, epoch, row * p.dim + i * 8, a, p.status, t0);
+        raw.x = pack_bf16(bf16_lo(raw.x) + round_bf16(a[0]), bf16_hi(raw.x) + round_bf16(a[1]));
+        raw.y = pack_bf16(bf16_lo(raw.y) + round_bf16(a[2]), bf16_hi(raw.y) + round_bf16(a[3]));
+        raw.z = pack_bf16(bf16_lo(raw.z) + round_bf16(a[4]), bf16_hi(raw.z) + round_bf16(a[5]));
+        raw.w = pack_bf16(bf16_lo(raw.w) + round_bf16(a[6]), bf16_hi(raw.w) + round_bf16(a[7]));
+    } else if (p.add) {
         const float4 a0 = *reinterpret_cast<const float4*>(p.add + row * p.ldadd + i * 8);
         const float4 a1 = *reinterpret_cast<const float4*>(p.add + row * p.ldadd + i * 8 + 4);
         raw.x = pack_bf16(bf16_lo(raw.x) + round_bf16(a0.x), bf16_hi(raw.x) + round_bf16(a0.y));
@@ -102,11 +112,14 @@ __global__ void __launch_bounds__(kRowThreads) row_prep_kernel(const RowPrepPara
     __shared__ float scratch[8];
     pdl_trigger();
     pdl_wait();
+    const bool gather = p.link.world > 0 && p.link.gather_inbox >= 0;
+    const unsigned int epoch = gather ? tp_next_epoch(p.link, p.link.gather_inbox) : 0u;
+    const long long t0 = clock64();
     const long long row = blockIdx.x;
     const int nvec = p.dim / 8;
     float ssq = 0.f;
     for (int i = threadIdx.x; i < nvec; i += kRowThreads) {
-        const uint4 s = load_row8(p, row, i);
+        const uint4 s = load_row8(p, row, i, epoch, t0);
         if (p.sum_out) *reinterpret_cast<uint4*>(p.sum_out + row * p.ldsum + i * 8) = s;
         const uint32_t w[4] = {s.x, s.y, s.z, s.w};
 #pragma unroll
@@ -119,7 +132,7 @@ __global__ void __launch_bounds__(kRowThreads) row_prep_kernel(const RowPrepPara
         r = 1.0f / sqrtf(tot / (float)p.dim + p.eps);
     }
     for (int i = threadIdx.x; i < nvec; i += kRowThreads) {
-        const uint4 s = load_row8(p, row, i);
+        const uint4 s = load_row8(p, row, i, epoch, t0);
         uint32_t v[4] = {s.x, s.y, s.z, s.w};
         if (p.normalize) {
             uint32_t nw[4] = {0, 0, 0, 0};
@@ -143,6 +156,9 @@ cudaError_t launch_row_prep(const RowPrepArgs& a, cudaStream_t stream) {
     p.x = a.x, p.ldx = a.ldx, p.add = a.add, p.ldadd = a.ldadd;
     p.sum_out = a.sum_out, p.ldsum = a.ldsum, p.w = a.w, p.y = a.y, p.ldy = a.ldy;
     p.dim = a.dim, p.eps = a.eps, p.normalize = a.normalize;
+    p.link = a.link;
+    p.status = status_ptr();
+    if (!p.status) return cudaErrorUnknown;
     return launch_pdl(row_prep_kernel, dim3(a.rows), dim3(kRowThreads), 0, stream, p);
 }
 

@@ -9,10 +9,16 @@ Sharding (``tp`` ranks, rank ``r``):
     Wgu rows  : gate rows and up rows [r*I/tp, (r+1)*I/tp)
     Wd        : the same columns                       -> partial [B, H], summed
 Hidden states, residuals and norms are replicated.  Partials are exchanged in
-fp32 with ``torch.distributed.all_reduce`` (NCCL over NVLink on GPUs).
+fp32, either with ``torch.distributed.all_reduce`` (NCCL over NVLink on GPUs;
+``exchange="nccl"``) or inside the projection kernels themselves, which store
+their partial into an inbox on every rank over NVLink peer memory and publish an
+epoch flag that the consuming kernel waits for (``exchange="fused"``: one C call
+and six kernels per layer, no collective launch in between).
 """
 
 from __future__ import annotations
+
+import ctypes
 
 import torch
 import torch.distributed as dist
@@ -56,7 +62,12 @@ class TensorParallelDecodeLayer:
 
     rms_eps = 1e-6
 
-    def __init__(self, batch, seq_len, hidden_size, intermediate_size, num_heads, head_dim, num_kv_heads, group=None):
+    def __init__(self, batch, seq_len, hidden_size, intermediate_size, num_heads, head_dim, num_kv_heads, group=None,
+                 exchange: str = "nccl"):
+        if exchange not in ("nccl", "fused"):
+            raise ValueError(f"exchange must be 'nccl' or 'fused', got {exchange!r}")
+        self.exchange = exchange
+        self._comm = None
         self.group = group
         self.tp = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -111,10 +122,66 @@ class TensorParallelDecodeLayer:
         if self.tp > 1:
             dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
 
+    # -- fused exchange: peer-mapped inboxes ------------------------------------
+    def _fused_comm(self, device):
+        """Allocates this rank's communication buffer, exchanges IPC handles over the
+        process group and maps every peer's buffer.  Collective: all ranks call it
+        together (it happens inside the first ``__call__``)."""
+        if self._comm is not None:
+            return self._comm
+        lib = _lib.load()
+        nbytes = lib.ezb_tp_comm_bytes(self.B, self.H)
+        own = ctypes.c_void_p()
+        _lib.check(lib.ezb_tp_comm_alloc(nbytes, ctypes.byref(own)))
+        handle = ctypes.create_string_buffer(64)
+        _lib.check(lib.ezb_ipc_export(own, handle))
+        handles = [None] * self.tp
+        if self.tp > 1:
+            dist.all_gather_object(handles, handle.raw, group=self.group)
+        bases = (ctypes.c_void_p * self.tp)()
+        mapped = []
+        for r in range(self.tp):
+            if r == self.rank:
+                bases[r] = own.value
+                continue
+            peer = ctypes.c_void_p()
+            _lib.check(lib.ezb_ipc_open(ctypes.create_string_buffer(handles[r], 64), ctypes.byref(peer)))
+            bases[r] = peer.value
+            mapped.append(peer)
+        torch.cuda.synchronize(device)
+        if self.tp > 1:
+            dist.barrier(group=self.group)  # every inbox is zeroed and mapped before anyone pushes
+        self._comm = dict(own=own, bases=bases, mapped=mapped)
+        return self._comm
+
+    def close(self):
+        """Unmaps the peers' buffers and frees this rank's (call on every rank, after a device sync)."""
+        if self._comm is None:
+            return
+        lib = _lib.load()
+        for peer in self._comm["mapped"]:
+            lib.ezb_ipc_close(peer)
+        if self.tp > 1:
+            dist.barrier(group=self.group)
+        lib.ezb_tp_comm_free(self._comm["own"])
+        self._comm = None
+
+    def _call_fused(self, hidden, K_l, V_l, Wqkv_l, Wo_l, Wgu_l, Wd_l, out, bufs):
+        lib = _lib.load()
+        comm = self._fused_comm(hidden.device)
+        s = torch.cuda.current_stream().cuda_stream
+        _lib.check(lib.ezb_qwen3_decode_layer_tp_fused(
+            hidden.data_ptr(), K_l.data_ptr(), V_l.data_ptr(), Wqkv_l.data_ptr(), Wo_l.data_ptr(), Wgu_l.data_ptr(),
+            Wd_l.data_ptr(), out.data_ptr(), bufs["ws1"].data_ptr(), bufs["ws1"].numel(), comm["bases"], self.tp,
+            self.rank, self.B, self.S, self.H, self.I_l, self.NH_l, self.NKV_l, self.D, self.rms_eps, s))
+
     def __call__(self, hidden, K_local, V_local, Wqkv_l, Wo_l, Wgu_l, Wd_l, out=None):
         bufs = self._buffers(hidden.device)
         if out is None:
             out = torch.empty_like(hidden)
+        if self.exchange == "fused":
+            self._call_fused(hidden, K_local, V_local, Wqkv_l, Wo_l, Wgu_l, Wd_l, out, bufs)
+            return out
         self._part_attn(hidden, K_local, V_local, Wqkv_l, Wo_l, bufs)
         self._sum_over_ranks(bufs["partial_o"])
         self._part_ffn(hidden, Wgu_l, Wd_l, bufs)

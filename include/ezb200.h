@@ -199,6 +199,33 @@ int ezb_qwen3_decode_layer_tp_ffn(const void* hidden, const float* summed_o, con
                                   size_t workspace_bytes, int B, int H, int I_local, float eps, ezb_stream_t stream);
 int ezb_residual_add_f32(const void* x2, const float* summed_d, void* out, int B, int H, ezb_stream_t stream);
 
+/* The same tensor-parallel layer as ONE call with the two sums over ranks done
+ * inside the kernels, over peer memory instead of NCCL (no counterpart in the
+ * reference).  Every rank owns a communication buffer of ezb_tp_comm_bytes(B, H)
+ * (ezb_tp_comm_alloc zero-fills it; this is the one place where the library
+ * allocates, at set-up time) and maps the buffers of all ranks (ezb_ipc_export /
+ * ezb_ipc_open, one process per GPU on one node); comm_bases_host[r] is rank r's
+ * buffer as seen from this process.  o_proj and down_proj store every fp32
+ * output of their partial [B,H], tagged with an epoch in the same 64-bit word,
+ * into the caller's slot of an inbox on every rank; the consuming kernel polls
+ * its own inbox (bounded, about one second, then records a device fault) until
+ * every word carries the expected epoch and adds the slots in rank order, so
+ * all ranks get identical bits.  Ranks must make the same sequence of calls; a
+ * buffer serves one stream.  Limited to batches for which every projection
+ * runs the resident-activation kernel (EZB_ERR_UNSUPPORTED_SHAPE
+ * otherwise; use the three-part form with NCCL then). */
+size_t ezb_tp_comm_bytes(int B, int H);
+int ezb_tp_comm_alloc(size_t bytes, void** out_host);
+int ezb_tp_comm_free(void* buffer);
+int ezb_ipc_export(void* buffer, void* handle64_host);
+int ezb_ipc_open(const void* handle64_host, void** out_host);
+int ezb_ipc_close(void* mapped);
+int ezb_qwen3_decode_layer_tp_fused(const void* hidden, void* K_cache, void* V_cache, const void* Wqkv_local,
+                                    const void* Wo_local, const void* Wgu_local, const void* Wd_local, void* out,
+                                    void* workspace, size_t workspace_bytes, void* const* comm_bases_host, int world,
+                                    int rank, int B, int S, int H, int I_local, int NH_local, int NKV_local, int D,
+                                    float eps, ezb_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

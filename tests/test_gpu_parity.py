@@ -469,3 +469,40 @@ def test_tp_parts_sum_to_the_layer(ez, tp, batch):
     for r in range(tp):
         assert torch.allclose(caches[r][0][:, :, -1].cpu().float(), Kr[:, r * n:(r + 1) * n, -1].float(), atol=1e-2, rtol=1e-2)
         assert torch.equal(caches[r][0][:, :, :-1].cpu(), K0[:, r * n:(r + 1) * n, :-1])
+
+
+@pytest.mark.parametrize("batch", [1, 4])
+def test_tp_fused_exchange_world_one_matches_the_layer(ez, batch):
+    """The fused exchange with one rank pushes into its own inbox: same bits as the
+    single-GPU layer, on every one of several calls in a row (the epochs advance)."""
+    from ezops_b200 import _lib
+    from ezops_b200 import tp as tpm
+    from ezops_b200 import workloads as wl
+
+    sh, S = wl.QWEN3_VL_2B, 520
+    data = wl.decode_layer_inputs(sh, batch, S)
+    op = ez.Qwen3DenseDecodeOp(batch, S, sh.hidden, sh.inter, sh.num_heads, sh.head_dim, backend="cuda", num_kv_heads=sh.num_kv_heads)
+    want = op(*dev(*data))
+    lay = tpm.TensorParallelDecodeLayer(batch, S, sh.hidden, sh.inter, sh.num_heads, sh.head_dim, sh.num_kv_heads, exchange="fused")
+    try:
+        for _ in range(3):
+            got = lay(*dev(*data))
+            assert torch.equal(got, want)
+        assert _lib.device_status() == 0
+    finally:
+        torch.cuda.synchronize()
+        lay.close()
+
+
+def test_tp_fused_exchange_rejects_large_batches(ez):
+    from ezops_b200 import tp as tpm
+    from ezops_b200 import workloads as wl
+
+    sh, S, batch = wl.QWEN3_VL_2B, 300, 16
+    data = wl.decode_layer_inputs(sh, batch, S)
+    lay = tpm.TensorParallelDecodeLayer(batch, S, sh.hidden, sh.inter, sh.num_heads, sh.head_dim, sh.num_kv_heads, exchange="fused")
+    try:
+        with pytest.raises(ValueError):
+            lay(*dev(*data))
+    finally:
+        lay.close()
