@@ -58,6 +58,8 @@ def parse_args():
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a CUDA graph")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--roofline-only", action="store_true",
+                    help="run only the roofline leg (a few launches of the dominant kernel): the command an ncu capture wraps")
     ap.add_argument("--no-cross-call-pdl", action="store_true",
                     help="order the first kernel of every layer call fully after the previous call")
     return ap.parse_args()
@@ -205,6 +207,51 @@ def workload_config(args, shape, n):
     }
 
 
+# DRAM traffic of one launch of the roofline leg's kernel (dram__bytes_read.sum + dram__bytes_write.sum)
+# from the ncu capture summarised in profiles/gemv_rows8_gate_up_sized_b1_ncu_full.md; the key is
+# (weight rows, weight columns, batch).
+NCU_TRAFFIC_BYTES = {(24576, 4096, 1): 201_408_512 + 3_995_648}
+
+
+def roofline_leg(sets, nsets, hidden0, B, H, device, n_roof):
+    """The dominant kernel timed alone: a GEMV over a gate/up-sized weight (rank 0's shard at N > 1)."""
+    import torch
+
+    from ezops_b200 import _lib
+
+    peaks, peak_kind = measured_peaks()
+    lib = _lib.load()
+    rows_local = sets[0][4].shape[0]
+    Y = torch.empty(B, rows_local, dtype=torch.bfloat16, device=device)
+    ws = torch.zeros(lib.ezb_gemv_workspace_bytes(B, rows_local, H), dtype=torch.uint8, device=device)
+    X = hidden0
+
+    def roof_launch(i):
+        W = sets[i % nsets][4]
+        _lib.check(lib.ezb_gemv_batched_bf16(X.data_ptr(), W.data_ptr(), Y.data_ptr(), ws.data_ptr(), ws.numel(), B,
+                                             rows_local, H, torch.cuda.current_stream().cuda_stream))
+
+    for i in range(8):
+        roof_launch(i)
+    torch.cuda.synchronize()
+    r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    r0.record()
+    for i in range(n_roof):
+        roof_launch(i)
+    r1.record()
+    torch.cuda.synchronize()
+    launch_s = r0.elapsed_time(r1) * 1e-3 / n_roof
+    kernel_bytes = 2 * (rows_local * H + B * H + B * rows_local)
+    achieved = kernel_bytes / launch_s / 1e9
+    roofline = {
+        "bound": "hbm", "kernel": "gemv_rows8_kernel" if B <= 8 else "gemm_tc_kernel", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+        "frac": achieved / peaks["hbm_gbs"], "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs, burst copy)",
+        "traffic": NCU_TRAFFIC_BYTES.get((rows_local, H, B)), "bytes_per_launch": kernel_bytes, "us_per_launch": launch_s * 1e6,
+        "workload": f"W [{rows_local}, {H}] bf16 (gate/up-sized), batch {B}, {n_roof} back-to-back launches over {nsets} weights",
+    }
+    return roofline
+
+
 # ------------------------------------------------------------------- main ---
 def main():
     args = parse_args()
@@ -262,6 +309,10 @@ def main():
         torch.cuda.empty_cache()
     gen.manual_seed(7)
     hidden0 = torch.randn(B, H, generator=gen, device=device, dtype=torch.float32).to(torch.bfloat16)
+
+    if args.roofline_only:
+        print(json.dumps({"roofline": roofline_leg(sets, nsets, hidden0, B, H, device, 4)}), flush=True)
+        os._exit(0)
 
     if tp == 1:
         op = ez.Qwen3DenseDecodeOp(B, S, H, I, NH, D, backend="cuda", num_kv_heads=NKV)
@@ -377,38 +428,8 @@ def main():
                "h2d_bytes_per_step": B * H * 2, "d2h_bytes_per_step": B * H * 2,
                "note": "weights and KV cache are resident device state; per-step input/output cross PCIe"}
 
-    # ---- roofline of the dominant kernel, timed alone (rank 0's shard) ----
-    peaks, peak_kind = measured_peaks()
-    lib = _lib.load()
-    n_roof = 200
-    rows_local = sets[0][4].shape[0]
-    Y = torch.empty(B, rows_local, dtype=torch.bfloat16, device=device)
-    ws = torch.zeros(lib.ezb_gemv_workspace_bytes(B, rows_local, H), dtype=torch.uint8, device=device)
-    X = hidden0
-
-    def roof_launch(i):
-        W = sets[i % nsets][4]
-        _lib.check(lib.ezb_gemv_batched_bf16(X.data_ptr(), W.data_ptr(), Y.data_ptr(), ws.data_ptr(), ws.numel(), B,
-                                             rows_local, H, torch.cuda.current_stream().cuda_stream))
-
-    for i in range(8):
-        roof_launch(i)
-    torch.cuda.synchronize()
-    r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    r0.record()
-    for i in range(n_roof):
-        roof_launch(i)
-    r1.record()
-    torch.cuda.synchronize()
-    launch_s = r0.elapsed_time(r1) * 1e-3 / n_roof
-    kernel_bytes = 2 * (rows_local * H + B * H + B * rows_local)
-    achieved = kernel_bytes / launch_s / 1e9
-    roofline = {
-        "bound": "hbm", "kernel": "gemv_rows8_kernel" if B <= 8 else "gemm_tc_kernel", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-        "frac": achieved / peaks["hbm_gbs"], "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs, burst copy)",
-        "traffic": None, "bytes_per_launch": kernel_bytes, "us_per_launch": launch_s * 1e6,
-        "workload": f"W [{rows_local}, {H}] bf16 (gate/up-sized), batch {B}, {n_roof} back-to-back launches over {nsets} weights",
-    }
+    roofline = roofline_leg(sets, nsets, hidden0, B, H, device, 200)
+    peaks, _ = measured_peaks()
 
     # ---- CPU oracle beside it (rank 0, single-GPU run only) ----
     cpu = None
