@@ -310,8 +310,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapW0, const __grid_constant_
             if (lane == 0) mbar_arrive(smem_u32(&acc_empty[acc]));
 
             const bool whole = (kb0 == 0 && kb1 == KB);
-            bool finish = whole;
             if (!whole) {
+                bool finish;
                 // partial tile: park it, take a ticket; the last contributor adds all parts in CTA order
                 const bool leading = (seg == 0);
                 float* mine = p.partial + ((size_t)cta * 2 + (leading ? 0 : 1)) * (NB * kTcRows);
@@ -328,19 +328,77 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapW0, const __grid_constant_
                 }
                 named_bar_sync(2, 128);
                 finish = (*ticket != 0);
-                if (finish) {
+                named_bar_sync(2, 128);  // `ticket` may be rewritten by the next segment
+                if (!finish || *abort_flag) continue;
+
+                // Fix-up by the last contributor.  Every value now comes from the parked parts, so the
+                // threads regroup for memory-level parallelism: a thread owns 4 consecutive rows
+                // (one 16-byte load per part and batch row) of a quarter of the batch, and the parts
+                // of two contributors are in flight together.  Parts are added in CTA order, which
+                // fixes the bits whatever the arrival order was.
+                constexpr int NBG = NB / 4;
+                const int r4 = lane * 4, b0 = (et >> 5) * NBG;
+                float4 acc[NBG];
 #pragma unroll
-                    for (int b = 0; b < NB; ++b) v[b] = 0.f;
-                    for (int c = c_first; c <= c_last; ++c) {
-                        const bool first_seg = (tc_first_unit(T, G, c) / KB) == tile;
-                        const float* part = p.partial + ((size_t)c * 2 + (first_seg ? 0 : 1)) * (NB * kTcRows);
+                for (int j = 0; j < NBG; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 2
+                for (int c = c_first; c <= c_last; ++c) {
+                    const bool first_seg = (tc_first_unit(T, G, c) / KB) == tile;
+                    const float* part = p.partial + ((size_t)c * 2 + (first_seg ? 0 : 1)) * (NB * kTcRows) + b0 * kTcRows + r4;
 #pragma unroll
-                        for (int b = 0; b < NB; ++b) v[b] += __ldcg(part + b * kTcRows + row);
+                    for (int j = 0; j < NBG; ++j) {
+                        const float4 t = __ldcg(reinterpret_cast<const float4*>(part + j * kTcRows));
+                        acc[j].x += t.x, acc[j].y += t.y, acc[j].z += t.z, acc[j].w += t.w;
                     }
                 }
-                named_bar_sync(2, 128);  // `ticket` may be rewritten by the next segment
+                if (!p.pair) {
+                    const int n = tile * kTcRows + r4;
+                    if (n < p.N) {
+                        if (p.epilogue == EPI_RESIDUAL) {
+                            uint2 res[NBG];
+#pragma unroll
+                            for (int j = 0; j < NBG; ++j)
+                                res[j] = (b0 + j < p.B) ? *reinterpret_cast<const uint2*>(p.residual + (long long)(b0 + j) * p.ldres + n)
+                                                        : make_uint2(0u, 0u);
+#pragma unroll
+                            for (int j = 0; j < NBG; ++j)
+                                if (b0 + j < p.B)
+                                    *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(p.out) + (long long)(b0 + j) * p.ldout + n) =
+                                        make_uint2(pack_bf16(bf16_lo(res[j].x) + round_bf16(acc[j].x), bf16_hi(res[j].x) + round_bf16(acc[j].y)),
+                                                   pack_bf16(bf16_lo(res[j].y) + round_bf16(acc[j].z), bf16_hi(res[j].y) + round_bf16(acc[j].w)));
+                        } else if (p.epilogue == EPI_STORE_F32) {
+#pragma unroll
+                            for (int j = 0; j < NBG; ++j)
+                                if (b0 + j < p.B) *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + (long long)(b0 + j) * p.ldout + n) = acc[j];
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < NBG; ++j)
+                                if (b0 + j < p.B)
+                                    *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(p.out) + (long long)(b0 + j) * p.ldout + n) =
+                                        make_uint2(pack_bf16(acc[j].x, acc[j].y), pack_bf16(acc[j].z, acc[j].w));
+                        }
+                    }
+                } else {
+                    // lanes 0..15 hold gate rows 0..63, lanes 16..31 the matching up rows
+                    const int n = tile * (kTcRows / 2) + r4;
+#pragma unroll
+                    for (int j = 0; j < NBG; ++j) {
+                        float4 up;
+                        up.x = __shfl_down_sync(0xffffffffu, acc[j].x, 16), up.y = __shfl_down_sync(0xffffffffu, acc[j].y, 16);
+                        up.z = __shfl_down_sync(0xffffffffu, acc[j].z, 16), up.w = __shfl_down_sync(0xffffffffu, acc[j].w, 16);
+                        if (lane < 16 && n < p.N && b0 + j < p.B) {
+                            const float o0 = round_bf16(silu_f32(round_bf16(acc[j].x))) * round_bf16(up.x);
+                            const float o1 = round_bf16(silu_f32(round_bf16(acc[j].y))) * round_bf16(up.y);
+                            const float o2 = round_bf16(silu_f32(round_bf16(acc[j].z))) * round_bf16(up.z);
+                            const float o3 = round_bf16(silu_f32(round_bf16(acc[j].w))) * round_bf16(up.w);
+                            *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(p.out) + (long long)(b0 + j) * p.ldout + n) =
+                                make_uint2(pack_bf16(o0, o1), pack_bf16(o2, o3));
+                        }
+                    }
+                }
+                continue;
             }
-            if (!finish || *abort_flag) continue;
+            if (*abort_flag) continue;
 
             if (!p.pair) {
                 const int n = tile * kTcRows + row;
