@@ -64,11 +64,17 @@ def bench(fn, args):
     return bench_kernel(fn, args=args, n_warmup=WARMUP, n_repeat=N_REPEAT, n_trials=N_TRIALS) * 1e3  # us
 
 
+SOL_HBM_GBS = None  # effective HBM bandwidth of the GPU profile (assets/<profile>.yaml), set in main()
+
+
 def row(name, us, ref_us, nbytes, ok, cpu_us, peak):
+    """``sol_score`` = time at the profile's effective HBM bandwidth / measured time, the
+    reference's speed-of-light score for a memory-bound op (benchmarks/bench_gemv.py:62-86)."""
     gbs = nbytes / us / 1e3
+    sol_peak = SOL_HBM_GBS or peak
     return {
         "workload": name, "us": us, "torch_ref_us": ref_us, "GB/s": gbs, "frac_8TBs": gbs / HBM_NOMINAL_GBS,
-        "frac_measured": gbs / peak, "sol_score": (nbytes / (peak * 1e9)) / (us * 1e-6), "check": ok,
+        "frac_measured": gbs / peak, "sol_score": (nbytes / (sol_peak * 1e9)) / (us * 1e-6), "check": ok,
         "cpu_ref_us": cpu_us, "algorithmic_bytes": nbytes,
     }
 
@@ -169,15 +175,23 @@ def main():
     ap.add_argument("-k", "--ops", default=",".join(RUNNERS))
     ap.add_argument("--cpu", action="store_true", help="also time the torch reference on the host cores")
     ap.add_argument("--json", default=None)
+    ap.add_argument("--profile", default=None, help="GPU profile under assets/ for the SOL score (default: detected)")
     args = ap.parse_args()
     peak = measured_hbm_gbs()
+    from benchmarks.hardware.gpu_specs import detect_profile, load_profile
+
+    global SOL_HBM_GBS
+    profile_name = args.profile or detect_profile(torch.cuda.get_device_properties(0).name)
+    profile = load_profile(profile_name) if profile_name else None
+    if profile and profile.get("hbm", {}).get("effective"):
+        SOL_HBM_GBS = profile["hbm"]["effective"] / 1e9
     rows = []
     for name in args.ops.split(","):
         rows += RUNNERS[name.strip()](args.cpu, peak)
     hdr = ["workload", "us", "torch_ref_us", "GB/s", "frac_8TBs", "frac_measured", "sol_score", "check", "cpu_ref_us"]
     fmt = lambda v: f"{v:.3g}" if isinstance(v, float) else v
     print(tabulate([[fmt(r[h]) for h in hdr] for r in rows], headers=hdr, tablefmt="github"))
-    print(f"\nprotocol: bench_kernel (CUDA graph, L2 flush per iteration, {N_TRIALS}x{N_REPEAT}); measured HBM copy peak {peak} GB/s; "
+    print(f"\nprotocol: bench_kernel (CUDA graph, L2 flush per iteration, {N_TRIALS}x{N_REPEAT}); measured HBM copy peak {peak} GB/s; SOL against {SOL_HBM_GBS or peak:.0f} GB/s (profile {profile_name}); "
           f"host threads {len(os.sched_getaffinity(0))}")
     if args.json:
         Path(args.json).write_text(json.dumps(rows, indent=1))

@@ -7,7 +7,7 @@ not load, importing the kernel backends raises -- there is no fallback path.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_char_p, c_float, c_int, c_size_t, c_uint, c_void_p, POINTER
+from ctypes import c_char_p, c_float, c_int, c_longlong, c_size_t, c_uint, c_void_p, POINTER
 from pathlib import Path
 
 import os
@@ -64,6 +64,7 @@ SIGNATURES = {
     "ezb_qwen3_decode_layer_tp_attn": (c_int, [c_void_p] * 7 + [c_size_t] + [c_int] * 6 + [c_float, c_void_p]),
     "ezb_qwen3_decode_layer_tp_ffn": (c_int, [c_void_p] * 7 + [c_size_t] + [c_int] * 3 + [c_float, c_void_p]),
     "ezb_residual_add_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "ezb_hbm_stream": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_float, c_int, c_int, c_void_p]),
     "ezb_tp_comm_bytes": (c_size_t, [c_int, c_int]),
     "ezb_tp_comm_alloc": (c_int, [c_size_t, POINTER(c_void_p)]),
     "ezb_tp_comm_free": (c_int, [c_void_p]),

@@ -577,6 +577,20 @@ int ezb_qwen3_decode_layer_tp_ffn(const void* hidden, const float* summed_o, con
     return EZB_OK;
 }
 
+int ezb_hbm_stream(int op, const void* b, const void* c, void* a, long long n_vec4, float scalar, int block_size,
+                   int blocks_per_sm, ezb_stream_t stream) {
+    EZB_REQUIRE(op >= 0 && op <= 3, "op must be 0 (read), 1 (write), 2 (copy) or 3 (triad)");
+    EZB_REQUIRE(a && (op == 1 || b) && (op != 3 || c), "null pointer");
+    EZB_REQUIRE(n_vec4 >= 1 && block_size >= 32 && block_size <= 1024 && block_size % 32 == 0 && blocks_per_sm >= 1 &&
+                    blocks_per_sm <= 32,
+                "bad size, block size or blocks per SM");
+    EZB_REQUIRE(aligned16(a) && aligned16(b) && aligned16(c), "pointers must be 16-byte aligned");
+    // a read-only pass parks its (never written) checksum in the first word of `a`
+    EZB_CUDA_TRY(launch_hbm_stream(op, b, c, a, n_vec4, scalar, block_size, blocks_per_sm, static_cast<float*>(a),
+                                   static_cast<cudaStream_t>(stream)));
+    return EZB_OK;
+}
+
 size_t ezb_tp_comm_bytes(int B, int H) {
     if (B < 1 || H < 1) return 0;
     return (size_t)kTpCtrlBytes + (size_t)2 * kTpSlots * B * H * sizeof(unsigned long long);

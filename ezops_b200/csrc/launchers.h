@@ -120,4 +120,9 @@ size_t attn_counters_bytes(int B, int H, int NKV);  // leading part of the works
 int attn_chunk_keys(int B, int NKV, int S);  // keys per KV split chosen for this shape
 cudaError_t launch_attn_decode(const AttnArgs& a, cudaStream_t stream);
 
+// STREAM-style calibration kernels (hbm_stream.cu): op 0 read b, 1 write a, 2 copy b->a, 3 triad a = b + s*c.
+cudaError_t launch_hbm_stream(int op, const void* b, const void* c, void* a, long long n_vec4, float s, int block,
+                              int blocks_per_sm, float* sink, cudaStream_t stream);
+
 }  // namespace ezb
+

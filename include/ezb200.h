@@ -199,6 +199,16 @@ int ezb_qwen3_decode_layer_tp_ffn(const void* hidden, const float* summed_o, con
                                   size_t workspace_bytes, int B, int H, int I_local, float eps, ezb_stream_t stream);
 int ezb_residual_add_f32(const void* x2, const float* summed_d, void* out, int B, int H, ezb_stream_t stream);
 
+/* Bandwidth calibration for the roofline profile of a GPU: one pass of a
+ * STREAM-style kernel over n_vec4 128-bit elements; op 0 reads b, 1 writes a, 2
+ * copies b to a, 3 is the triad a = b + scalar*c.  Replaces the stand-alone
+ * calibrator the reference compiles at run time
+ * (benchmarks/hardware/memory/hbm_saturation.cu:49-93, driven by
+ * benchmarks/hardware/memory/hbm_bandwidth.py:52-75); the caller times it
+ * with events.  Grid = blocks_per_sm x SM count, block_size threads. */
+int ezb_hbm_stream(int op, const void* b, const void* c, void* a, long long n_vec4, float scalar, int block_size,
+                   int blocks_per_sm, ezb_stream_t stream);
+
 /* The same tensor-parallel layer as ONE call with the two sums over ranks done
  * inside the kernels, over peer memory instead of NCCL (no counterpart in the
  * reference).  Every rank owns a communication buffer of ezb_tp_comm_bytes(B, H)
