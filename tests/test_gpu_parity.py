@@ -506,3 +506,27 @@ def test_tp_fused_exchange_rejects_large_batches(ez):
             lay(*dev(*data))
     finally:
         lay.close()
+
+
+# ------------------------------------------------- calibration kernels (STREAM) ---
+@pytest.mark.parametrize("n_vec4", [1, 1000, 148 * 256 * 4 * 3 + 17])
+def test_hbm_stream_kernels_compute_what_they_say(ez, n_vec4):
+    from ezops_b200 import _lib
+
+    lib = _lib.load()
+    g = torch.Generator(device="cuda").manual_seed(5)
+    b = torch.randn(n_vec4 * 4, device="cuda", generator=g)
+    c = torch.randn(n_vec4 * 4, device="cuda", generator=g)
+    a = torch.zeros(n_vec4 * 4, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    _lib.check(lib.ezb_hbm_stream(3, b.data_ptr(), c.data_ptr(), a.data_ptr(), n_vec4, 0.5, 256, 4, s))
+    # the compiler contracts b + s*c into one fma; torch rounds the product first: allow that one rounding
+    assert torch.allclose(a, b + 0.5 * c, rtol=0, atol=1e-6)
+    _lib.check(lib.ezb_hbm_stream(2, b.data_ptr(), c.data_ptr(), a.data_ptr(), n_vec4, 0.0, 512, 2, s))
+    assert torch.equal(a, b)
+    _lib.check(lib.ezb_hbm_stream(1, b.data_ptr(), c.data_ptr(), a.data_ptr(), n_vec4, 3.0, 1024, 1, s))
+    assert torch.equal(a, torch.full_like(a, 3.0))
+    _lib.check(lib.ezb_hbm_stream(0, b.data_ptr(), c.data_ptr(), a.data_ptr(), n_vec4, 0.0, 256, 8, s))
+    assert torch.equal(a, torch.full_like(a, 3.0))  # a read pass writes nothing
+    with pytest.raises(ValueError):
+        _lib.check(lib.ezb_hbm_stream(7, b.data_ptr(), c.data_ptr(), a.data_ptr(), n_vec4, 0.0, 256, 8, s))
