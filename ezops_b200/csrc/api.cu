@@ -80,7 +80,7 @@ static std::atomic<bool> g_tuning_ready{false};
 static const int kTuningDefaults[EZB_TUNE_COUNT] = {
     1,    // EZB_TUNE_PDL
     220,  // EZB_TUNE_GEMV_SMEM_KB
-    0,    // EZB_TUNE_GEMV_PREFETCH (all stages)
+    1,    // EZB_TUNE_GEMV_PREFETCH (one stage ahead of the dependency wait measured fastest in the chained layer)
     1,    // EZB_TUNE_GEMV_CTAS_PER_SM
     128,  // EZB_TUNE_ATTN_MIN_CHUNK
     8,    // EZB_TUNE_ATTN_WAVES

@@ -51,7 +51,7 @@ typedef struct CUstream_st* ezb_stream_t; /* same type as cudaStream_t */
 /* Tuning knobs for ezb_set_tuning / ezb_get_tuning (process-wide, read at launch). */
 #define EZB_TUNE_PDL 0              /* 1: chain kernels with programmatic dependent launch (default 1) */
 #define EZB_TUNE_GEMV_SMEM_KB 1     /* shared-memory budget per CTA of the weight-streaming kernel      */
-#define EZB_TUNE_GEMV_PREFETCH 2    /* weight stages requested before the dependency wait (0 = all)     */
+#define EZB_TUNE_GEMV_PREFETCH 2    /* weight stages requested before the dependency wait (0 = all; default 1) */
 #define EZB_TUNE_GEMV_CTAS_PER_SM 3 /* persistent CTAs per SM of the weight-streaming kernel            */
 #define EZB_TUNE_ATTN_MIN_CHUNK 4   /* smallest KV split, in keys (multiple of 64)                      */
 #define EZB_TUNE_ATTN_WAVES 5       /* target number of KV splits per SM                                */
