@@ -8,6 +8,7 @@ from .ops import (
     FusedQkNormRopeOp,
     GemvOp,
     Op,
+    Qwen3DecodeStackOp,
     Qwen3DenseDecodeOp,
     RmsNormOp,
     RooflineResult,
@@ -20,6 +21,7 @@ __all__ = [
     "FusedQkNormRopeOp",
     "GemvOp",
     "Op",
+    "Qwen3DecodeStackOp",
     "Qwen3DenseDecodeOp",
     "RmsNormOp",
     "RooflineResult",

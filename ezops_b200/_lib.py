@@ -64,6 +64,9 @@ SIGNATURES = {
     "ezb_qwen3_decode_layer_tp_attn": (c_int, [c_void_p] * 7 + [c_size_t] + [c_int] * 6 + [c_float, c_void_p]),
     "ezb_qwen3_decode_layer_tp_ffn": (c_int, [c_void_p] * 7 + [c_size_t] + [c_int] * 3 + [c_float, c_void_p]),
     "ezb_residual_add_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "ezb_qwen3_decode_stack_workspace_bytes": (c_size_t, [c_int] * 7),
+    "ezb_qwen3_decode_stack": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_size_t]
+                               + [c_int] * 7 + [c_float, c_void_p]),
     "ezb_hbm_stream": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_float, c_int, c_int, c_void_p]),
     "ezb_tp_comm_bytes": (c_size_t, [c_int, c_int]),
     "ezb_tp_comm_alloc": (c_int, [c_size_t, POINTER(c_void_p)]),
@@ -98,6 +101,13 @@ def load() -> ctypes.CDLL:
         fn.argtypes = argtypes
     _lib = lib
     return lib
+
+
+class LayerStruct(ctypes.Structure):
+    """``ezb_layer_t``: one decoder layer's device pointers (0 for an absent norm weight)."""
+
+    _fields_ = [(name, c_void_p) for name in ("K_cache", "V_cache", "Wqkv", "Wo", "Wgu", "Wd", "input_norm_w", "post_norm_w",
+                                              "q_norm_w", "k_norm_w")]
 
 
 def check(rc: int) -> None:

@@ -256,13 +256,29 @@ static cudaError_t launch_down(const bf16* h, const bf16* Wd, int B, int H, int 
     return launch_gemv(g, stream);
 }
 
+// What a layer of a decoder stack has beyond the reference's layer operator: norm weights
+// (null = unit), the rotary table rows of the token's position (null = no rotation), and the
+// weights the last kernel should start pulling into L2 for the layer that follows.
+struct LayerExtras {
+    const bf16* input_norm_w = nullptr;
+    const bf16* post_norm_w = nullptr;
+    const bf16* q_norm_w = nullptr;
+    const bf16* k_norm_w = nullptr;
+    const bf16* rope_cos = nullptr;
+    const bf16* rope_sin = nullptr;
+    const bf16* next_Wqkv = nullptr;
+};
+static const LayerExtras kPlainLayer = {};
+
 static cudaError_t launch_qkv_and_attention(const bf16* hidden, bf16* Kc, bf16* Vc, const bf16* Wqkv, const LayerWorkspace& w,
                                             int B, int S, int H, int NH, int NKV, int D, float eps, cudaStream_t stream,
-                                            const bf16* Wo, const PrefetchPlan* after_wo = nullptr) {
+                                            const bf16* Wo, const PrefetchPlan* after_wo = nullptr,
+                                            const LayerExtras& ex = kPlainLayer) {
     const int rows = (NH + 2 * NKV) * D;
     GemvArgs g;
     g.W0 = Wqkv, g.ldw = H, g.N = rows, g.K = H, g.B = B;
     g.x = hidden, g.ldx = H;
+    g.norm_w = ex.input_norm_w;
     g.eps = eps, g.prologue = PRO_RMSNORM, g.epilogue = EPI_STORE;
     g.out = w.qkv, g.ldout = rows;
     g.xn_scratch = w.xn;
@@ -283,6 +299,7 @@ static cudaError_t launch_qkv_and_attention(const bf16* hidden, bf16* Kc, bf16* 
     a.qkv = w.qkv, a.qkv_bstride = rows;
     a.K_cache_w = Kc, a.V_cache_w = Vc;
     a.eps = eps;
+    a.q_norm_w = ex.q_norm_w, a.k_norm_w = ex.k_norm_w, a.rope_cos = ex.rope_cos, a.rope_sin = ex.rope_sin;
     // attention is latency-bound at small batch: let HBM stream the output projection meanwhile
     if ((size_t)H * NH * D * 2 <= ((size_t)64 << 20)) {
         a.next = one_plan(next_rows(Wo, nullptr, H, NH * D, 1 << 20));
@@ -499,6 +516,25 @@ size_t ezb_qwen3_decode_layer_workspace_bytes(int B, int S, int H, int I, int NH
     return carve_layer_ws(nullptr, B, S, H, I, NH, NKV, D).total;
 }
 
+// One layer's five (seven with the tensor-core path) launches.  The caller has opened the chain.
+static int run_layer(const bf16* hid, bf16* Kc, bf16* Vc, const bf16* Wqkv, const bf16* Wo, const bf16* wgu, const bf16* Wd,
+                     bf16* out, const LayerWorkspace& w, int B, int S, int H, int I, int NH, int NKV, int D, float eps,
+                     const LayerExtras& ex, cudaStream_t stream) {
+    const int pf_kb = tuning(EZB_TUNE_L2_PREFETCH_KB);
+    const int pf_attn_kb = tuning(EZB_TUNE_L2_PREFETCH_ATTN_KB);
+    // attention is latency-bound: besides Wo it can pull the head of the gate/up rows; o_proj then pulls the rows after those
+    const PrefetchPlan gu_head = next_rows(wgu, wgu + (size_t)I * H, I, H, pf_attn_kb);
+    EZB_CUDA_TRY(launch_qkv_and_attention(hid, Kc, Vc, Wqkv, w, B, S, H, NH, NKV, D, eps, stream, Wo,
+                                          pf_attn_kb > 0 ? &gu_head : nullptr, ex));
+    EZB_CUDA_TRY(launch_o_proj(w.attn_out, Wo, B, H, NH * D, hid, w.x2, false, stream,
+                               one_plan(next_rows(wgu, wgu + (size_t)I * H, I, H, pf_kb, pf_attn_kb > 0 ? pf_attn_kb : 0)), w.tc));
+    EZB_CUDA_TRY(launch_gate_up(w.x2, nullptr, nullptr, ex.post_norm_w, wgu, wgu + (size_t)I * H, B, H, I, eps, w.h, w.xn, stream,
+                                one_plan(next_rows(Wd, nullptr, H, I, pf_kb)), w.tc));
+    const PrefetchList after = ex.next_Wqkv ? one_plan(next_rows(ex.next_Wqkv, nullptr, (NH + 2 * NKV) * D, H, pf_kb)) : kNoPrefetch;
+    EZB_CUDA_TRY(launch_down(w.h, Wd, B, H, I, w.x2, out, false, stream, after, w.tc));
+    return EZB_OK;
+}
+
 int ezb_qwen3_decode_layer(const void* hidden, void* K_cache, void* V_cache, const void* Wqkv, const void* Wo,
                            const void* Wgu, const void* Wd, void* out, void* workspace, size_t workspace_bytes, int B,
                            int S, int H, int I, int NH, int NKV, int D, float eps, ezb_stream_t stream) {
@@ -512,21 +548,59 @@ int ezb_qwen3_decode_layer(const void* hidden, void* K_cache, void* V_cache, con
         set_last_message("workspace missing or smaller than ezb_qwen3_decode_layer_workspace_bytes()");
         return EZB_ERR_WORKSPACE;
     }
-    const bf16* hid = static_cast<const bf16*>(hidden);
-    const bf16* wgu = static_cast<const bf16*>(Wgu);
     chain_begin();
-    const int pf_kb = tuning(EZB_TUNE_L2_PREFETCH_KB);
-    const int pf_attn_kb = tuning(EZB_TUNE_L2_PREFETCH_ATTN_KB);
-    // attention is latency-bound: besides Wo it pulls the head of the gate/up rows; o_proj then pulls the rows after those
-    const PrefetchPlan gu_head = next_rows(wgu, wgu + (size_t)I * H, I, H, pf_attn_kb);
-    EZB_CUDA_TRY(launch_qkv_and_attention(hid, static_cast<bf16*>(K_cache), static_cast<bf16*>(V_cache),
-                                          static_cast<const bf16*>(Wqkv), w, B, S, H, NH, NKV, D, eps, stream,
-                                          static_cast<const bf16*>(Wo), pf_attn_kb > 0 ? &gu_head : nullptr));
-    EZB_CUDA_TRY(launch_o_proj(w.attn_out, static_cast<const bf16*>(Wo), B, H, NH * D, hid, w.x2, false, stream,
-                               one_plan(next_rows(wgu, wgu + (size_t)I * H, I, H, pf_kb, pf_attn_kb > 0 ? pf_attn_kb : 0)), w.tc));
-    EZB_CUDA_TRY(launch_gate_up(w.x2, nullptr, nullptr, nullptr, wgu, wgu + (size_t)I * H, B, H, I, eps, w.h, w.xn, stream,
-                                one_plan(next_rows(static_cast<const bf16*>(Wd), nullptr, H, I, pf_kb)), w.tc));
-    EZB_CUDA_TRY(launch_down(w.h, static_cast<const bf16*>(Wd), B, H, I, w.x2, out, false, stream, kNoPrefetch, w.tc));
+    return run_layer(static_cast<const bf16*>(hidden), static_cast<bf16*>(K_cache), static_cast<bf16*>(V_cache),
+                     static_cast<const bf16*>(Wqkv), static_cast<const bf16*>(Wo), static_cast<const bf16*>(Wgu),
+                     static_cast<const bf16*>(Wd), static_cast<bf16*>(out), w, B, S, H, I, NH, NKV, D, eps, kPlainLayer,
+                     static_cast<cudaStream_t>(stream));
+}
+
+size_t ezb_qwen3_decode_stack_workspace_bytes(int B, int S, int H, int I, int NH, int NKV, int D) {
+    if (check_layer_args(B, S, H, I, NH, NKV, D)) return 0;
+    return carve_layer_ws(nullptr, B, S, H, I, NH, NKV, D).total + 2 * round256((size_t)B * H * sizeof(bf16));
+}
+
+int ezb_qwen3_decode_stack(const void* hidden, void* out, const ezb_layer_t* layers, int n_layers, const void* rope_cos,
+                           const void* rope_sin, int rope_position, void* workspace, size_t workspace_bytes, int B, int S,
+                           int H, int I, int NH, int NKV, int D, float eps, ezb_stream_t stream) {
+    EZB_REQUIRE(hidden && out && layers && n_layers >= 1, "null pointer or no layers");
+    EZB_REQUIRE((rope_cos == nullptr) == (rope_sin == nullptr) && rope_position >= 0, "rotary tables come as a pair; position >= 0");
+    if (int rc = check_layer_args(B, S, H, I, NH, NKV, D)) return rc;
+    EZB_REQUIRE(aligned16(hidden) && aligned16(out) && aligned16(rope_cos) && aligned16(rope_sin), "pointers must be 16-byte aligned");
+    for (int l = 0; l < n_layers; ++l) {
+        const ezb_layer_t& L = layers[l];
+        EZB_REQUIRE(L.K_cache && L.V_cache && L.Wqkv && L.Wo && L.Wgu && L.Wd, "null pointer in a layer");
+        EZB_REQUIRE(aligned16(L.K_cache) && aligned16(L.V_cache) && aligned16(L.Wqkv) && aligned16(L.Wo) && aligned16(L.Wgu) &&
+                        aligned16(L.Wd) && aligned16(L.input_norm_w) && aligned16(L.post_norm_w) && aligned16(L.q_norm_w) &&
+                        aligned16(L.k_norm_w),
+                    "layer pointers must be 16-byte aligned");
+    }
+    LayerWorkspace w = carve_layer_ws(workspace, B, S, H, I, NH, NKV, D);
+    const size_t hbytes = round256((size_t)B * H * sizeof(bf16));
+    if (!workspace || workspace_bytes < w.total + 2 * hbytes) {
+        set_last_message("workspace missing or smaller than ezb_qwen3_decode_stack_workspace_bytes()");
+        return EZB_ERR_WORKSPACE;
+    }
+    bf16* pp[2] = {reinterpret_cast<bf16*>(static_cast<unsigned char*>(workspace) + w.total),
+                   reinterpret_cast<bf16*>(static_cast<unsigned char*>(workspace) + w.total + hbytes)};
+    const bf16* cos_row = rope_cos ? static_cast<const bf16*>(rope_cos) + (size_t)rope_position * D : nullptr;
+    const bf16* sin_row = rope_sin ? static_cast<const bf16*>(rope_sin) + (size_t)rope_position * D : nullptr;
+    chain_begin();  // one dependency chain through all layers
+    const bf16* x = static_cast<const bf16*>(hidden);
+    for (int l = 0; l < n_layers; ++l) {
+        const ezb_layer_t& L = layers[l];
+        LayerExtras ex;
+        ex.input_norm_w = static_cast<const bf16*>(L.input_norm_w), ex.post_norm_w = static_cast<const bf16*>(L.post_norm_w);
+        ex.q_norm_w = static_cast<const bf16*>(L.q_norm_w), ex.k_norm_w = static_cast<const bf16*>(L.k_norm_w);
+        ex.rope_cos = cos_row, ex.rope_sin = sin_row;
+        ex.next_Wqkv = (l + 1 < n_layers) ? static_cast<const bf16*>(layers[l + 1].Wqkv) : nullptr;
+        bf16* y = (l + 1 == n_layers) ? static_cast<bf16*>(out) : pp[l & 1];
+        if (int rc = run_layer(x, static_cast<bf16*>(L.K_cache), static_cast<bf16*>(L.V_cache), static_cast<const bf16*>(L.Wqkv),
+                               static_cast<const bf16*>(L.Wo), static_cast<const bf16*>(L.Wgu), static_cast<const bf16*>(L.Wd), y,
+                               w, B, S, H, I, NH, NKV, D, eps, ex, static_cast<cudaStream_t>(stream)))
+            return rc;
+        x = y;
+    }
     return EZB_OK;
 }
 

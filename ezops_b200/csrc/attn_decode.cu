@@ -47,9 +47,41 @@ struct AttnParams {
     bf16* K_cache_w;
     bf16* V_cache_w;
     float eps;
+    const bf16* q_norm_w;
+    const bf16* k_norm_w;
+    const bf16* rope_cos;
+    const bf16* rope_sin;
     PrefetchList next;
     Trace trace;
 };
+
+// Head RMSNorm (+ optional weight, + optional rotate-half RoPE) of one head held by a warp:
+// lane owns elements lane + 32*j, so the rotation partner (i +- D/2) is in the same lane.
+// x: in/out fp32 values; returns them ready for the single bf16 rounding.
+template <int D>
+__device__ __forceinline__ void head_norm_rope(float (&x)[D / 32], float eps, const bf16* w, const bf16* cosr, const bf16* sinr,
+                                               int lane) {
+    constexpr int NJ = D / 32, HJ = NJ / 2;
+    float ssq = 0.f;
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) ssq += x[j] * x[j];
+    ssq = warp_sum(ssq);
+    const float r = 1.0f / sqrtf(ssq / (float)D + eps);
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+        x[j] = __fmul_rn(x[j], r);
+        if (w) x[j] = __fmul_rn(x[j], __bfloat162float(w[lane + j * 32]));
+    }
+    if (cosr) {
+#pragma unroll
+        for (int j = 0; j < HJ; ++j) {
+            const int i = lane + j * 32, i2 = i + D / 2;
+            const float n1 = x[j], n2 = x[j + HJ];
+            x[j] = __fadd_rn(__fmul_rn(n1, __bfloat162float(cosr[i])), __fmul_rn(-n2, __bfloat162float(sinr[i])));
+            x[j + HJ] = __fadd_rn(__fmul_rn(n2, __bfloat162float(cosr[i2])), __fmul_rn(n1, __bfloat162float(sinr[i2])));
+        }
+    }
+}
 
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
@@ -148,16 +180,11 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
             // unit-weight RMSNorm over the head, fp32 statistics, one rounding
             for (int row = warp; row < gn; row += 4) {
                 float x[D / 32];
-                float ssq = 0.f;
 #pragma unroll
-                for (int j = 0; j < D / 32; ++j) {
-                    x[j] = __bfloat162float(q_s[row * QS + lane + j * 32]);
-                    ssq += x[j] * x[j];
-                }
-                ssq = warp_sum(ssq);
-                const float r = 1.0f / sqrtf(ssq / (float)D + p.eps);
+                for (int j = 0; j < D / 32; ++j) x[j] = __bfloat162float(q_s[row * QS + lane + j * 32]);
+                head_norm_rope<D>(x, p.eps, p.q_norm_w, p.rope_cos, p.rope_sin, lane);
 #pragma unroll
-                for (int j = 0; j < D / 32; ++j) q_s[row * QS + lane + j * 32] = __float2bfloat16_rn(x[j] * r);
+                for (int j = 0; j < D / 32; ++j) q_s[row * QS + lane + j * 32] = __float2bfloat16_rn(x[j]);
             }
             // new token's k (normalised) and v: kept in shared memory for the patch below and
             // written to cache slot S-1 (nobody reads that slot from memory in this kernel)
@@ -166,17 +193,12 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
                 if (warp == 0) {
                     const bf16* ksrc = p.qkv + (long long)b * p.qkv_bstride + p.q_rows + kvh * D;
                     float x[D / 32];
-                    float ssq = 0.f;
+#pragma unroll
+                    for (int j = 0; j < D / 32; ++j) x[j] = __bfloat162float(ksrc[lane + j * 32]);
+                    head_norm_rope<D>(x, p.eps, p.k_norm_w, p.rope_cos, p.rope_sin, lane);
 #pragma unroll
                     for (int j = 0; j < D / 32; ++j) {
-                        x[j] = __bfloat162float(ksrc[lane + j * 32]);
-                        ssq += x[j] * x[j];
-                    }
-                    ssq = warp_sum(ssq);
-                    const float r = 1.0f / sqrtf(ssq / (float)D + p.eps);
-#pragma unroll
-                    for (int j = 0; j < D / 32; ++j) {
-                        const bf16 kn = __float2bfloat16_rn(x[j] * r);
+                        const bf16 kn = __float2bfloat16_rn(x[j]);
                         kv_new_s[lane + j * 32] = kn;
                         if (qt == 0) p.K_cache_w[slot + lane + j * 32] = kn;
                     }
@@ -534,6 +556,7 @@ cudaError_t launch_attn_decode(const AttnArgs& a, cudaStream_t stream) {
     p.q_rows = a.H * a.D, p.kv_rows = a.NKV * a.D;
     p.K_cache_w = a.K_cache_w, p.V_cache_w = a.V_cache_w;
     p.eps = a.eps;
+    p.q_norm_w = a.q_norm_w, p.k_norm_w = a.k_norm_w, p.rope_cos = a.rope_cos, p.rope_sin = a.rope_sin;
     p.next = a.next;
     if (!tuning(EZB_TUNE_L2_PREFETCH)) p.next.plan[0].units = p.next.plan[1].units = 0;
     p.trace = trace_handle();

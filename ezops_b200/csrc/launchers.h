@@ -113,6 +113,14 @@ struct AttnArgs {
     bf16* K_cache_w = nullptr;
     bf16* V_cache_w = nullptr;
     float eps = 1e-6f;
+    // decode-layer mode, optional: weights of the q / k head norms ([D], null = unit) and the
+    // rows of the rotary tables for the token's position ([D] each, HF layout with the halves
+    // repeated; null = no rotation).  Norm, weight and rotation stay in fp32 with one
+    // rounding at the end, as in the stand-alone q/k-norm + RoPE operator.
+    const bf16* q_norm_w = nullptr;
+    const bf16* k_norm_w = nullptr;
+    const bf16* rope_cos = nullptr;
+    const bf16* rope_sin = nullptr;
     PrefetchList next = {};
 };
 size_t attn_workspace_bytes(int B, int H, int NKV, int S, int D);

@@ -251,3 +251,73 @@ class Qwen3DenseDecodeSm100Kernel(BaseKernel):
             )
         )
         return out
+
+
+@register_kernel("qwen3_decode_stack", "cuda")
+class Qwen3DecodeStackSm100Kernel(BaseKernel):
+    """``num_layers`` decode layers in one C call (``ezb_qwen3_decode_stack``): one chain of
+    kernels through all layers, optional norm weights, RoPE inside the attention kernel.
+    ``__call__(hidden, layers, cos, sin, out=None)`` with ``layers`` as described in
+    ``ops/qwen3_decode_stack.py``.  The pointer table is rebuilt only when a tensor changes."""
+
+    rms_eps = 1e-6
+
+    def __init__(self, batch, seq_len, hidden_size, intermediate_size, num_heads, head_dim, num_layers, num_kv_heads=None):
+        # same shape rules as one layer
+        Qwen3DenseDecodeSm100Kernel.__init__(self, batch, seq_len, hidden_size, intermediate_size, num_heads, head_dim, num_kv_heads)
+        if num_layers < 1:
+            raise ValueError(f"num_layers ({num_layers}) must be >= 1")
+        self.L = num_layers
+        self._table, self._table_key = None, None
+
+    def workspace(self, device):
+        if self._ws is None or self._ws.device != device:
+            need = self._lib.ezb_qwen3_decode_stack_workspace_bytes(self.B, self.S, self.H, self.I, self.NH, self.NKV, self.D)
+            self._ws = _zeros_bytes(need, device)
+        return self._ws
+
+    def _layer_table(self, layers):
+        B, S, H, I, NH, NKV, D = self.B, self.S, self.H, self.I, self.NH, self.NKV, self.D
+        shapes = {"K_cache": (B, NKV, S, D), "V_cache": (B, NKV, S, D), "Wqkv": ((NH + 2 * NKV) * D, H), "Wo": (H, NH * D),
+                  "Wgu": (2 * I, H), "Wd": (H, I), "input_norm_w": (H,), "post_norm_w": (H,), "q_norm_w": (D,), "k_norm_w": (D,)}
+        key = tuple(0 if L.get(n) is None else L[n].data_ptr() for L in layers for n in shapes)
+        if key != self._table_key:
+            table = (_lib.LayerStruct * len(layers))()
+            for i, L in enumerate(layers):
+                for name, shape in shapes.items():
+                    t = L.get(name)
+                    if t is None:
+                        if not name.endswith("_norm_w"):
+                            raise ValueError(f"layer {i}: {name} is required")
+                        setattr(table[i], name, None)
+                        continue
+                    _require(t, f"layer {i} {name}", shape)
+                    setattr(table[i], name, t.data_ptr())
+            self._table, self._table_key = table, key
+        return self._table
+
+    def __call__(self, hidden, layers, cos=None, sin=None, out=None):
+        if len(layers) != self.L:
+            raise ValueError(f"expected {self.L} layers, got {len(layers)}")
+        _require(hidden, "hidden", (self.B, self.H))
+        if (cos is None) != (sin is None):
+            raise ValueError("cos and sin come as a pair")
+        position = self.S - 1
+        if cos is not None:
+            for name, t in (("cos", cos), ("sin", sin)):
+                if t.dim() != 2 or t.shape[1] != self.D or t.shape[0] <= position:
+                    raise ValueError(f"{name} must be [> {position}, {self.D}], got {tuple(t.shape)}")
+                _require(t, name, t.shape)
+        table = self._layer_table(layers)
+        ws = self.workspace(hidden.device)
+        if out is None:
+            out = torch.empty_like(hidden)
+        _lib.check(
+            self._lib.ezb_qwen3_decode_stack(
+                hidden.data_ptr(), out.data_ptr(), table, self.L, cos.data_ptr() if cos is not None else None,
+                sin.data_ptr() if sin is not None else None, position, ws.data_ptr(), ws.numel(), self.B, self.S, self.H, self.I,
+                self.NH, self.NKV, self.D, self.rms_eps, _stream(),
+            )
+        )
+        return out
+

@@ -3,6 +3,7 @@ from .base_op import Op
 from .fused_o_proj_ffn import FusedOProjFfnOp
 from .fused_qk_norm_rope import FusedQkNormRopeOp
 from .gemv import GemvOp
+from .qwen3_decode_stack import Qwen3DecodeStackOp
 from .qwen3_dense_decode import Qwen3DenseDecodeOp
 from .rmsnorm import RmsNormOp
 from .utils.roofline import RooflineResult
@@ -13,6 +14,7 @@ __all__ = [
     "FusedQkNormRopeOp",
     "GemvOp",
     "Op",
+    "Qwen3DecodeStackOp",
     "Qwen3DenseDecodeOp",
     "RmsNormOp",
     "RooflineResult",

@@ -134,6 +134,24 @@ def decode_layer_inputs(shape: LayerShape, batch: int, seq_len: int, seed: int =
     return layer_activations(shape, batch, seq_len, seed + 1, device) + layer_weights(shape, seed, device=device)
 
 
+def decode_stack_inputs(shape: LayerShape, batch: int, seq_len: int, num_layers: int, rope: bool = True, norm_weights: bool = True,
+                        seed: int = 42, device="cpu"):
+    """(hidden, layers, cos, sin) for ``Qwen3DecodeStackOp``: every layer has its own seeded
+    weights N(0, 0.02) and KV cache N(0, 1); norm weights 1 + N(0, 0.1); the reference's rotary tables."""
+    g = _gen(seed + 7)
+    hidden = _randn(g, batch, shape.hidden).to(device)
+    layers = []
+    for l in range(num_layers):
+        Wqkv, Wo, Wgu, Wd = layer_weights(shape, seed + 100 * (l + 1), device=device)
+        _, Kc, Vc = layer_activations(shape, batch, seq_len, seed + 100 * (l + 1) + 1, device=device)
+        layer = {"K_cache": Kc, "V_cache": Vc, "Wqkv": Wqkv, "Wo": Wo, "Wgu": Wgu, "Wd": Wd}
+        for key, n in (("input_norm_w", shape.hidden), ("post_norm_w", shape.hidden), ("q_norm_w", shape.head_dim), ("k_norm_w", shape.head_dim)):
+            layer[key] = _randn(g, n, std=0.1, mean=1.0).to(device) if norm_weights else None
+        layers.append(layer)
+    cos, sin = (t.to(device) for t in rope_tables(seq_len, shape.head_dim)) if rope else (None, None)
+    return hidden, layers, cos, sin
+
+
 def o_proj_ffn_inputs(shape: LayerShape, batch: int, seed: int = 42, device="cpu"):
     g = _gen(seed)
     H, I, Q = shape.hidden, shape.inter, shape.q_rows

@@ -199,6 +199,38 @@ int ezb_qwen3_decode_layer_tp_ffn(const void* hidden, const float* summed_o, con
                                   size_t workspace_bytes, int B, int H, int I_local, float eps, ezb_stream_t stream);
 int ezb_residual_add_f32(const void* x2, const float* summed_d, void* out, int B, int H, ezb_stream_t stream);
 
+/* A stack of decode layers in one call, with what a model has and the
+ * reference's layer operator leaves out (ezops/ops/qwen3_dense_decode.py:27-29:
+ * "RoPE excluded by design", unit norm weights): per-layer norm weights and the
+ * rotary embedding of the new token's q and k, applied exactly as the
+ * stand-alone operator does (ezops/ops/fused_qk_norm_rope.py:149-169: norm,
+ * weight and rotate-half in fp32, one bf16 rounding) inside the attention
+ * kernel.  This is the multi-layer decode loop the reference lists as not yet
+ * implemented (README.md:16).  Layer l reads layer l-1's output from a
+ * ping-pong buffer in the workspace; all kernels of all layers form one
+ * programmatic-dependent-launch chain, and the last kernel of a layer starts
+ * pulling the next layer's Wqkv into L2.  Any of the four norm-weight pointers
+ * may be NULL (unit weight); rope_cos / rope_sin are [>= rope_position + 1, D]
+ * bf16 tables in the reference's layout (halves repeated) or both NULL (no
+ * rotation).  As in the layer operator every cache has S slots and the new
+ * token goes to slot S - 1.  `layers` is a host array, read during the call. */
+typedef struct ezb_layer_t {
+    void* K_cache;
+    void* V_cache;
+    const void* Wqkv;
+    const void* Wo;
+    const void* Wgu;
+    const void* Wd;
+    const void* input_norm_w; /* [H] */
+    const void* post_norm_w;  /* [H] */
+    const void* q_norm_w;     /* [D] */
+    const void* k_norm_w;     /* [D] */
+} ezb_layer_t;
+size_t ezb_qwen3_decode_stack_workspace_bytes(int B, int S, int H, int I, int NH, int NKV, int D);
+int ezb_qwen3_decode_stack(const void* hidden, void* out, const ezb_layer_t* layers, int n_layers, const void* rope_cos,
+                           const void* rope_sin, int rope_position, void* workspace, size_t workspace_bytes, int B, int S,
+                           int H, int I, int NH, int NKV, int D, float eps, ezb_stream_t stream);
+
 /* Bandwidth calibration for the roofline profile of a GPU: one pass of a
  * STREAM-style kernel over n_vec4 128-bit elements; op 0 reads b, 1 writes a, 2
  * copies b to a, 3 is the triad a = b + scalar*c.  Replaces the stand-alone

@@ -530,3 +530,47 @@ def test_hbm_stream_kernels_compute_what_they_say(ez, n_vec4):
     assert torch.equal(a, torch.full_like(a, 3.0))  # a read pass writes nothing
     with pytest.raises(ValueError):
         _lib.check(lib.ezb_hbm_stream(7, b.data_ptr(), c.data_ptr(), a.data_ptr(), n_vec4, 0.0, 256, 8, s))
+
+
+# ----------------------------------------------------- multi-layer stack (RoPE, norm weights) ---
+def _stack_to_device(layers):
+    return [{k: (None if v is None else v.cuda()) for k, v in L.items()} for L in layers]
+
+
+@pytest.mark.parametrize("batch,num_layers,rope,norm_w", [(1, 3, True, True), (4, 2, True, False), (2, 2, False, True), (16, 2, True, True)])
+def test_decode_stack_matches_the_oracle(ez, batch, num_layers, rope, norm_w):
+    import copy
+
+    from ezops_b200 import workloads as wl
+
+    sh, S = wl.QWEN3_VL_2B, 333
+    hid, layers, cos, sin = wl.decode_stack_inputs(sh, batch, S, num_layers, rope=rope, norm_weights=norm_w)
+    ref_layers = copy.deepcopy(layers)
+    ref = orc.qwen3_decode_stack_ref(hid, ref_layers, sh.num_heads, sh.num_kv_heads, sh.head_dim, cos, sin)
+    op = ez.Qwen3DecodeStackOp(batch, S, sh.hidden, sh.inter, sh.num_heads, sh.head_dim, num_layers, backend="cuda",
+                               num_kv_heads=sh.num_kv_heads, rope=int(rope), norm_weights=int(norm_w))
+    dl = _stack_to_device(layers)
+    got = op(hid.cuda(), dl, None if cos is None else cos.cuda(), None if sin is None else sin.cuda())
+    assert op.check(got.cpu(), ref), rel_fro(got, ref)
+    assert rel_fro(got, ref) < 1e-2  # in practice well inside the single-layer bound
+    for L, R in zip(dl, ref_layers):
+        # first layer's new k is computed from identical inputs; later layers inherit the stream's rounding noise
+        assert torch.allclose(L["K_cache"][:, :, -1].cpu().float(), R["K_cache"][:, :, -1].float(), atol=6e-2, rtol=2e-2)
+        assert torch.equal(L["K_cache"][:, :, :-1].cpu(), R["K_cache"][:, :, :-1])
+        assert torch.equal(L["V_cache"][:, :, :-1].cpu(), R["V_cache"][:, :, :-1])
+    assert torch.allclose(dl[0]["K_cache"][:, :, -1].cpu().float(), ref_layers[0]["K_cache"][:, :, -1].float(), atol=1e-2, rtol=1e-2)
+    again = op(hid.cuda(), dl, None if cos is None else cos.cuda(), None if sin is None else sin.cuda())
+    assert torch.equal(again, got)
+
+
+def test_decode_stack_of_one_plain_layer_is_the_layer_op(ez):
+    from ezops_b200 import workloads as wl
+
+    sh, B, S = wl.QWEN3_VL_2B, 2, 200
+    hid, layers, _, _ = wl.decode_stack_inputs(sh, B, S, 1, rope=False, norm_weights=False)
+    L = layers[0]
+    layer_op = ez.Qwen3DenseDecodeOp(B, S, sh.hidden, sh.inter, sh.num_heads, sh.head_dim, backend="cuda", num_kv_heads=sh.num_kv_heads)
+    want = layer_op(*dev(hid, L["K_cache"], L["V_cache"], L["Wqkv"], L["Wo"], L["Wgu"], L["Wd"]))
+    stack_op = ez.Qwen3DecodeStackOp(B, S, sh.hidden, sh.inter, sh.num_heads, sh.head_dim, 1, backend="cuda", num_kv_heads=sh.num_kv_heads)
+    got = stack_op(hid.cuda(), _stack_to_device(layers))
+    assert torch.equal(got, want)
