@@ -167,12 +167,39 @@ def run_layer(cpu, peak, batches=(1, 8, 32, 64)):
     return rows
 
 
-RUNNERS = {"gemv": run_gemv, "rmsnorm": run_rmsnorm, "rope": run_rope, "attn": run_attn, "ffn": run_ffn, "layer": run_layer}
+def run_stack(cpu, peak, num_layers=36, batches=(1, 8)):
+    """All 36 decoder layers of Qwen3-8B in one call (norm weights, RoPE at position S-1): a whole
+    decode step apart from the embedding and the LM head.  Inputs are generated on the device
+    (14 GB of weights); the check compares with the operator's torch reference on the same GPU."""
+    sh, S = wl.QWEN3_8B, 4096
+    rows = []
+    for B in batches:
+        kw = dict(num_kv_heads=sh.num_kv_heads)
+        op = ez.Qwen3DecodeStackOp(B, S, sh.hidden, sh.inter, sh.num_heads, sh.head_dim, num_layers, backend="cuda", **kw)
+        ref = ez.Qwen3DecodeStackOp(B, S, sh.hidden, sh.inter, sh.num_heads, sh.head_dim, num_layers, backend="ref", **kw)
+        torch.manual_seed(42)
+        hidden, layers, cos, sin = op.gen_data()
+        for L in layers:  # the op's default init (fan-in scaling) -> the N(0, 0.02) of the workload definition
+            for name in ("Wqkv", "Wo", "Wgu", "Wd"):
+                L[name].normal_(0.0, 0.02)
+        out_r = ref(hidden, layers, cos, sin)
+        out = op(hidden, layers, cos, sin)
+        ok = op.check(out, out_r)
+        us = bench_kernel(op, args=(hidden, layers, cos, sin), n_warmup=3, n_repeat=10, n_trials=3) * 1e3
+        ref_us = bench_kernel(ref, args=(hidden, layers, cos, sin), n_warmup=2, n_repeat=5, n_trials=2) * 1e3
+        rows.append(row(f"stack qwen3-8b {num_layers} layers s{S} b{B} (rope, norm w)", us, ref_us,
+                        num_layers * sh.algorithmic_bytes(B, S), ok, None, peak))
+        del hidden, layers, out, out_r
+        torch.cuda.empty_cache()
+    return rows
+
+
+RUNNERS = {"stack": run_stack, "gemv": run_gemv, "rmsnorm": run_rmsnorm, "rope": run_rope, "attn": run_attn, "ffn": run_ffn, "layer": run_layer}
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("-k", "--ops", default=",".join(RUNNERS))
+    ap.add_argument("-k", "--ops", default=",".join(k for k in RUNNERS if k != "stack"))
     ap.add_argument("--cpu", action="store_true", help="also time the torch reference on the host cores")
     ap.add_argument("--json", default=None)
     ap.add_argument("--profile", default=None, help="GPU profile under assets/ for the SOL score (default: detected)")
