@@ -91,7 +91,7 @@ __device__ __forceinline__ void tp_bump(const TpLink& l) { l.ctrl_peer[l.rank][k
 // Returns false (and records the fault) if the wait limit ran out.
 __device__ __forceinline__ bool tp_gather8(const TpLink& l, unsigned int epoch, long long elem, float (&add)[8],
                                            unsigned int* status, long long t0) {
-    constexpr int G = 4;  // ranks polled together
+    constexpr int G = 2;  // ranks polled together (more would spill the poll buffers of the calling kernels)
     for (int w0 = 0; w0 < l.world; w0 += G) {
         unsigned long long c[G][8];
         unsigned int pending = 0;

@@ -93,7 +93,7 @@ __host__ __device__ constexpr int stage_rows() {
 // Brings the activation block into shared memory (row stride xs_stride
 // elements), optionally adding an fp32 term first and RMS-normalising:
 // statistics in fp32, (x * r [* w]) in fp32, one rounding to bf16.  Called by
-// the 128 consumer threads; `scratch` needs four floats.
+// all consumer threads; `scratch` needs one float per consumer warp.
 // With PERMUTE32 every group of 32 elements is stored as four 16-byte blocks,
 // block t holding the element pairs (j*8 + 2t, j*8 + 2t + 1), j = 0..3: exactly
 // the four words that lane t of a quad feeds to two consecutive k-steps as its
@@ -122,24 +122,37 @@ __device__ __forceinline__ void load_x8(const bf16* srow, int i, uint32_t (&w)[4
     }
 }
 
-template <bool PERMUTE32>
+template <bool PERMUTE32, bool LINK, bool SINGLE>
 __device__ __forceinline__ void stage_activations(const GemvParams& p, bf16* xs, int xs_stride, float* scratch, int ct,
                                                   int cw, int lane) {
     constexpr int U = 8;  // independent 16-byte loads in flight per thread
     const int nvec = p.K / 8;
-    if (p.link.world > 0 && p.link.gather_inbox >= 0) {
-        // Fused tensor-parallel sum: x <- rmsnorm(bf16(x + bf16(sum over ranks of the inbox slots))).
-        const TpLink& l = p.link;
-        const unsigned int epoch = tp_next_epoch(l, l.gather_inbox);
-        const long long t0 = clock64();
-        for (int b = 0; b < p.B; ++b) {
-            const bf16* xrow = p.x + (long long)b * p.ldx;
-            bf16* srow = xs + (size_t)b * xs_stride;
-            float ssq = 0.f;
-            for (int i = ct; i < nvec; i += kConsumerThreads) {
+    // Rows are staged side by side: the consumer warps are split into groups of `wpr` warps, one
+    // group per batch row, so a batch of 8 rows costs the same number of L2 round trips and
+    // barriers as one row (batch 1: all warps on the one row).
+    // SINGLE (batch 1) fixes the split at compile time: all warps on row 0.
+    int wpr = kConsumerWarps;
+    if (!SINGLE)
+        while (wpr > 1 && kConsumerWarps / wpr < p.B) wpr >>= 1;
+    const int rows_per_pass = kConsumerWarps / wpr;
+    const int sub = SINGLE ? ct : (cw % wpr) * 32 + lane, nthr = wpr * 32;
+    const bool gather = LINK && p.link.world > 0 && p.link.gather_inbox >= 0;
+    const unsigned int epoch = gather ? tp_next_epoch(p.link, p.link.gather_inbox) : 0u;
+    const long long t0 = gather ? clock64() : 0;
+
+    const int nrows = SINGLE ? 1 : p.B;
+    for (int b0 = 0; b0 < nrows; b0 += rows_per_pass) {
+        const int b = SINGLE ? 0 : b0 + cw / wpr;
+        const bool active = SINGLE || b < nrows;
+        const bf16* xrow = p.x + (long long)(active ? b : 0) * p.ldx;
+        bf16* srow = xs + (size_t)(active ? b : 0) * xs_stride;
+        float ssq = 0.f;
+        if (LINK && active && gather) {
+            // Fused tensor-parallel sum: x <- bf16(x + bf16(sum over ranks of the inbox slots)), see TpLink.
+            for (int i = sub; i < nvec; i += nthr) {
                 const uint4 raw = *reinterpret_cast<const uint4*>(xrow + i * 8);
                 float add[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                tp_gather8(l, epoch, (long long)b * p.K + i * 8, add, p.status, t0);
+                tp_gather8(p.link, epoch, (long long)b * p.K + i * 8, add, p.status, t0);
                 uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
                 for (int e = 0; e < 4; ++e)
@@ -153,65 +166,44 @@ __device__ __forceinline__ void stage_activations(const GemvParams& p, bf16* xs,
                 }
                 store_x8<PERMUTE32>(srow, i, w4);
             }
-            ssq = warp_sum(ssq);
-            if (lane == 0) scratch[cw] = ssq;
-            named_bar_sync(1, kConsumerThreads);
-            float tot = 0.f;
+        } else if (active) {
+            for (int base = 0; base < nvec; base += U * nthr) {
+                // all loads of the batch are issued before any of them is used, so the
+                // L2 latency is paid once per batch and not once per vector
+                uint4 raw[U];
+                float4 add0[U], add1[U];
 #pragma unroll
-            for (int w = 0; w < kConsumerWarps; ++w) tot += scratch[w];
-            const float r = 1.0f / sqrtf(tot / (float)p.K + p.eps);
-            for (int i = ct; i < nvec; i += kConsumerThreads) {
-                uint32_t w4[4];
-                load_x8<PERMUTE32>(srow, i, w4);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) w4[e] = pack_bf16(bf16_lo(w4[e]) * r, bf16_hi(w4[e]) * r);
-                store_x8<PERMUTE32>(srow, i, w4);
-            }
-            named_bar_sync(1, kConsumerThreads);
-        }
-        named_bar_sync(1, kConsumerThreads);
-        return;
-    }
-    for (int b = 0; b < p.B; ++b) {
-        const bf16* xrow = p.x + (long long)b * p.ldx;
-        bf16* srow = xs + (size_t)b * xs_stride;
-        float ssq = 0.f;
-        for (int base = 0; base < nvec; base += U * kConsumerThreads) {
-            // all loads of the batch are issued before any of them is used, so the
-            // L2 latency is paid once per batch and not once per vector
-            uint4 raw[U];
-            float4 add0[U], add1[U];
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int i = base + u * kConsumerThreads + ct;
-                if (i < nvec) {
-                    raw[u] = *reinterpret_cast<const uint4*>(xrow + i * 8);
-                    if (p.prologue == PRO_ADD_RMSNORM) {
-                        add0[u] = *reinterpret_cast<const float4*>(p.x_add + (long long)b * p.ldadd + i * 8);
-                        add1[u] = *reinterpret_cast<const float4*>(p.x_add + (long long)b * p.ldadd + i * 8 + 4);
+                for (int u = 0; u < U; ++u) {
+                    const int i = base + u * nthr + sub;
+                    if (i < nvec) {
+                        raw[u] = *reinterpret_cast<const uint4*>(xrow + i * 8);
+                        if (p.prologue == PRO_ADD_RMSNORM) {
+                            add0[u] = *reinterpret_cast<const float4*>(p.x_add + (long long)b * p.ldadd + i * 8);
+                            add1[u] = *reinterpret_cast<const float4*>(p.x_add + (long long)b * p.ldadd + i * 8 + 4);
+                        }
                     }
                 }
-            }
 #pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int i = base + u * kConsumerThreads + ct;
-                if (i < nvec) {
-                    uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
-                    if (p.prologue == PRO_ADD_RMSNORM) {
-                        const float add[8] = {add0[u].x, add0[u].y, add0[u].z, add0[u].w,
-                                              add1[u].x, add1[u].y, add1[u].z, add1[u].w};
+                for (int u = 0; u < U; ++u) {
+                    const int i = base + u * nthr + sub;
+                    if (i < nvec) {
+                        uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+                        if (p.prologue == PRO_ADD_RMSNORM) {
+                            const float add[8] = {add0[u].x, add0[u].y, add0[u].z, add0[u].w,
+                                                  add1[u].x, add1[u].y, add1[u].z, add1[u].w};
 #pragma unroll
-                        for (int e = 0; e < 4; ++e)
-                            w[e] = pack_bf16(bf16_lo(w[e]) + round_bf16(add[2 * e]), bf16_hi(w[e]) + round_bf16(add[2 * e + 1]));
-                        if (blockIdx.x == 0 && p.x_sum_out)
-                            *reinterpret_cast<uint4*>(p.x_sum_out + (long long)b * p.ldsum + i * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                            for (int e = 0; e < 4; ++e)
+                                w[e] = pack_bf16(bf16_lo(w[e]) + round_bf16(add[2 * e]), bf16_hi(w[e]) + round_bf16(add[2 * e + 1]));
+                            if (blockIdx.x == 0 && p.x_sum_out)
+                                *reinterpret_cast<uint4*>(p.x_sum_out + (long long)b * p.ldsum + i * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float lo = bf16_lo(w[e]), hi = bf16_hi(w[e]);
+                            ssq += lo * lo + hi * hi;
+                        }
+                        store_x8<PERMUTE32>(srow, i, w);
                     }
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float lo = bf16_lo(w[e]), hi = bf16_hi(w[e]);
-                        ssq += lo * lo + hi * hi;
-                    }
-                    store_x8<PERMUTE32>(srow, i, w);
                 }
             }
         }
@@ -219,27 +211,29 @@ __device__ __forceinline__ void stage_activations(const GemvParams& p, bf16* xs,
             ssq = warp_sum(ssq);
             if (lane == 0) scratch[cw] = ssq;
             named_bar_sync(1, kConsumerThreads);
-            float tot = 0.f;
+            if (active) {
+                float tot = 0.f;
+                for (int w = 0; w < wpr; ++w) tot += scratch[(cw / wpr) * wpr + w];  // fixed order: reproducible
+                const float r = 1.0f / sqrtf(tot / (float)p.K + p.eps);
+                // every thread rescales exactly the vectors it stored itself: no barrier in between
+                for (int i = sub; i < nvec; i += nthr) {
+                    uint32_t w[4];
+                    load_x8<PERMUTE32>(srow, i, w);
+                    uint32_t nw[4] = {0u, 0u, 0u, 0u};
+                    if (p.norm_w) {
+                        const uint4 q = *reinterpret_cast<const uint4*>(p.norm_w + i * 8);
+                        nw[0] = q.x, nw[1] = q.y, nw[2] = q.z, nw[3] = q.w;
+                    }
 #pragma unroll
-            for (int w = 0; w < kConsumerWarps; ++w) tot += scratch[w];
-            const float r = 1.0f / sqrtf(tot / (float)p.K + p.eps);
-            for (int i = ct; i < p.K / 8; i += kConsumerThreads) {
-                uint32_t w[4];
-                load_x8<PERMUTE32>(srow, i, w);
-                uint32_t nw[4] = {0u, 0u, 0u, 0u};
-                if (p.norm_w) {
-                    const uint4 q = *reinterpret_cast<const uint4*>(p.norm_w + i * 8);
-                    nw[0] = q.x, nw[1] = q.y, nw[2] = q.z, nw[3] = q.w;
+                    for (int e = 0; e < 4; ++e) {
+                        float lo = bf16_lo(w[e]) * r, hi = bf16_hi(w[e]) * r;
+                        if (p.norm_w) lo *= bf16_lo(nw[e]), hi *= bf16_hi(nw[e]);
+                        w[e] = pack_bf16(lo, hi);
+                    }
+                    store_x8<PERMUTE32>(srow, i, w);
                 }
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    float lo = bf16_lo(w[e]) * r, hi = bf16_hi(w[e]) * r;
-                    if (p.norm_w) lo *= bf16_lo(nw[e]), hi *= bf16_hi(nw[e]);
-                    w[e] = pack_bf16(lo, hi);
-                }
-                store_x8<PERMUTE32>(srow, i, w);
             }
-            named_bar_sync(1, kConsumerThreads);  // scratch is reused by the next row
+            if (b0 + rows_per_pass < nrows) named_bar_sync(1, kConsumerThreads);  // scratch is reused by the next pass
         }
     }
     named_bar_sync(1, kConsumerThreads);
@@ -379,7 +373,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_stream_kernel(const Gemv
     const int ct = tid - 32;  // 0..127 among consumer threads
     pdl_wait();
 
-    if (XRES) stage_activations<false>(p, xs, xs_stride, red, ct, cw, lane);
+    if (XRES) stage_activations<false, false, false>(p, xs, xs_stride, red, ct, cw, lane);
 
     const int g4 = lane >> 2, t4 = lane & 3;
     for (int rb = 0; rb < nrb; ++rb) {
@@ -471,7 +465,9 @@ static constexpr int kXsPad8 = 32;  // activation rows 64 bytes apart in bank sp
 static constexpr int kRed8Bytes = 2 * kConsumerWarps * 64 * (int)sizeof(float);  // double buffered
 static constexpr int kResidualSlots = 1024;  // residual values (batch x rows of this CTA) kept in shared memory
 
-template <bool PAIR>
+// LINK: the instance used by the fused tensor-parallel layer (prologue gathers from the inbox,
+// epilogue pushes to the peers).  The plain instance contains none of that code.
+template <bool PAIR, bool LINK, bool SINGLE>
 __global__ void __launch_bounds__(kGemvThreads, 1) gemv_rows8_kernel(const GemvParams p) {
     constexpr int UNITS = PAIR ? 4 : 8;  // outputs per row block
     extern __shared__ __align__(128) unsigned char smem[];
@@ -572,8 +568,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_rows8_kernel(const GemvP
             const int b = i / rows_here, r = i - b * rows_here;
             res_s[i] = __bfloat162float(p.residual[(long long)b * p.ldres + r0 + r]);
         }
-    const unsigned int push_epoch = (p.link.world > 0 && p.link.push_inbox >= 0) ? tp_next_epoch(p.link, p.link.push_inbox) : 0u;
-    stage_activations<true>(p, xs, xs_stride, red, ct, cw, lane);  // ends with a barrier among the consumers
+    const unsigned int push_epoch = (LINK && p.link.world > 0 && p.link.push_inbox >= 0) ? tp_next_epoch(p.link, p.link.push_inbox) : 0u;
+    stage_activations<true, LINK, SINGLE>(p, xs, xs_stride, red, ct, cw, lane);  // ends with a barrier among the consumers
 
     const int g4 = lane >> 2, t4 = lane & 3;
     const bool has_row = g4 < p.B;
@@ -624,7 +620,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_rows8_kernel(const GemvP
                 if (res_in_smem) {
                     const float res = res_s[b * rows_here + (n - r0)];
                     reinterpret_cast<bf16*>(p.out)[(long long)b * p.ldout + n] = __float2bfloat16_rn(res + round_bf16(v0));
-                } else if (p.epilogue == EPI_PUSH_F32) {
+                } else if (LINK && p.epilogue == EPI_PUSH_F32) {
                     // this rank's partial goes into its slot of the inbox on every rank
                     tp_push(p.link, (long long)b * p.ldout + n, v0, push_epoch);
                 } else {
@@ -633,7 +629,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_rows8_kernel(const GemvP
             }
         }
     }
-    if (p.link.world > 0 && p.link.bump_inbox >= 0 && blockIdx.x == 0 && ct == 0) tp_bump(p.link);
+    if (LINK && p.link.world > 0 && p.link.bump_inbox >= 0 && blockIdx.x == 0 && ct == 0) tp_bump(p.link);
     trace_mark(trec, 5);
 }
 
@@ -787,9 +783,9 @@ bool gemv_small_batch_eligible(int B, int K) {
     return plan_rows8(a, pl);
 }
 
-template <bool PAIR>
+template <bool PAIR, bool LINK, bool SINGLE>
 static cudaError_t launch_rows8(const GemvParams& p, const GemvPlan& pl, cudaStream_t stream) {
-    auto kernel = gemv_rows8_kernel<PAIR>;
+    auto kernel = gemv_rows8_kernel<PAIR, LINK, SINGLE>;
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -846,7 +842,19 @@ cudaError_t launch_gemv(const GemvArgs& a, cudaStream_t stream) {
     }
     if (use_tc) return launch_gemm_tc(a, p.x, p.ldx, a.tc_workspace, stream);
 
-    if (rows8) return pair ? launch_rows8<true>(p, pl, stream) : launch_rows8<false>(p, pl, stream);
+    if (rows8) {
+        const int which = (pair ? 4 : 0) | (a.link.world > 0 ? 2 : 0) | (a.B == 1 ? 1 : 0);
+        switch (which) {
+            case 0: return launch_rows8<false, false, false>(p, pl, stream);
+            case 1: return launch_rows8<false, false, true>(p, pl, stream);
+            case 2: return launch_rows8<false, true, false>(p, pl, stream);
+            case 3: return launch_rows8<false, true, true>(p, pl, stream);
+            case 4: return launch_rows8<true, false, false>(p, pl, stream);
+            case 5: return launch_rows8<true, false, true>(p, pl, stream);
+            case 6: return launch_rows8<true, true, false>(p, pl, stream);
+            default: return launch_rows8<true, true, true>(p, pl, stream);
+        }
+    }
     if (pl.xres) return pair ? dispatch_nt<true, true>(p, pl, stream) : dispatch_nt<true, false>(p, pl, stream);
     return pair ? dispatch_nt<false, true>(p, pl, stream) : dispatch_nt<false, false>(p, pl, stream);
 }
