@@ -92,10 +92,12 @@ static const int kTuningDefaults[EZB_TUNE_COUNT] = {
     0,    // EZB_TUNE_GEMV_WINDOW
     0,    // EZB_TUNE_L2_PREFETCH_ATTN_KB
     1,    // EZB_TUNE_TC
+    3,    // EZB_TUNE_ATTN_WAVES_UNIFORM
 };
 static const char* kTuningEnv[EZB_TUNE_COUNT] = {
     "EZB_TUNE_PDL",          "EZB_TUNE_GEMV_SMEM_KB",   "EZB_TUNE_GEMV_PREFETCH", "EZB_TUNE_GEMV_CTAS_PER_SM",
     "EZB_TUNE_ATTN_MIN_CHUNK", "EZB_TUNE_ATTN_WAVES", "EZB_TUNE_GEMV_KC", "EZB_TUNE_GEMV_ROWS8", "EZB_TUNE_PDL_ACROSS_CALLS", "EZB_TUNE_L2_PREFETCH", "EZB_TUNE_L2_PREFETCH_KB", "EZB_TUNE_GEMV_WINDOW", "EZB_TUNE_L2_PREFETCH_ATTN_KB", "EZB_TUNE_TC",
+    "EZB_TUNE_ATTN_WAVES_UNIFORM",
 };
 
 static void tuning_init() {
