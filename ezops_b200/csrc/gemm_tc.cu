@@ -35,6 +35,7 @@ static constexpr int kTcRows = 128;     // weight rows per tile (MMA M)
 static constexpr int kTcBlockK = 64;    // k elements per stage: 128 bytes, one swizzle row
 static constexpr int kTcThreads = 192;  // TMA warp, MMA warp, four epilogue warps
 static constexpr int kTcMaxStages = 10;
+static constexpr int kTcMaxSegs = 32;  // tile segments per CTA: at most tiles / CTAs + 2
 static constexpr int kTcABytes = kTcRows * kTcBlockK * 2;
 // Projections of different shapes share one workspace, so the region of the
 // ticket counters (which must stay zero between launches) has one fixed size
@@ -151,6 +152,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapW0, const __grid_constant_
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* ticket = reinterpret_cast<int*>(tmem_slot + 2);
     float* xch = reinterpret_cast<float*>(tail + 256);  // [64][NB + 1]: up values handed to the gate warps
+    // Segment table of this CTA, in processing order: {tile, first k-block, end k-block, partial slot}.
+    int* segs = reinterpret_cast<int*>(tail + 256 + 64 * (NB + 1) * sizeof(float));
+    int* nseg_s = segs + 4 * kTcMaxSegs;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int NS = p.nstages;
@@ -170,6 +174,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapW0, const __grid_constant_
         }
         *abort_flag = 0;
         mbar_fence_init();
+        // The unit range [u0, u1) cut at tile boundaries.  Partial tiles (shared with a neighbour CTA) are
+        // processed FIRST, whole tiles after them: the fix-up of a shared tile then runs in the epilogue
+        // warps while the producer and the MMA warp are already streaming the whole tiles, instead of
+        // at the very end of the kernel where nothing can hide it.
+        int n = 0;
+        for (int pass = 0; pass < 2; ++pass) {
+            long long u = u0;
+            int natural = 0;
+            while (u < u1) {
+                const int t = (int)(u / KB), k0 = (int)(u % KB);
+                const long long left = u1 - u;
+                const int k1 = (KB - k0 < left) ? KB : k0 + (int)left;
+                const bool whole = (k0 == 0 && k1 == KB);
+                if ((pass == 0) != whole) {
+                    segs[4 * n] = t, segs[4 * n + 1] = k0, segs[4 * n + 2] = k1, segs[4 * n + 3] = natural == 0 ? 0 : 1;
+                    ++n;
+                }
+                u += k1 - k0;
+                ++natural;
+            }
+        }
+        *nseg_s = n;
     }
     if (warp == 1) {
         tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
@@ -188,7 +214,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapW0, const __grid_constant_
             // One thread feeds the whole ring, so its per-unit cost matters: all counters
             // are 32-bit and advance incrementally (no divisions in the loop).
             const int n_units = (int)(u1 - u0);
-            int tile = (int)(u0 / KB), kb = (int)(u0 % KB);  // unit being requested
+            const int nseg = *nseg_s;
+            // two cursors over the segment table: the next unit whose weights / activations are requested
+            int wsi = 0, wkb = nseg ? segs[1] : 0, xsi = 0, xkb = wkb;
+            auto advance = [&](int& si, int& kb) {
+                if (++kb == segs[4 * si + 2]) {
+                    ++si;
+                    kb = si < nseg ? segs[4 * si + 1] : 0;
+                }
+            };
             int stage = 0;
             uint32_t empty_parity = 1;  // a fresh barrier passes a wait on parity 1
             auto request_w = [&](int st, int t, int k) {
@@ -208,26 +242,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapW0, const __grid_constant_
             };
             // weights do not depend on the kernel in front: request them before the dependency wait
             const int npre = n_units < NS ? n_units : NS;
-            {
-                int t = tile, k = kb;
-                for (int i = 0; i < npre; ++i) {
-                    request_w(i, t, k);
-                    if (++k == KB) k = 0, ++t;
-                }
+            for (int i = 0; i < npre; ++i) {
+                request_w(i, segs[4 * wsi], wkb);
+                advance(wsi, wkb);
             }
             pdl_wait();
             for (int i = 0; i < npre; ++i) {
-                request_x(i, kb);
-                if (++kb == KB) kb = 0, ++tile;
+                request_x(i, xkb);
+                advance(xsi, xkb);
             }
             int issued = npre;
             stage = (npre == NS) ? 0 : npre;
             if (npre == NS) empty_parity = 0;
             for (int i = npre; i < n_units; ++i) {
                 if (!mbar_wait_bounded(smem_u32(&empty_bar[stage]), empty_parity, abort_flag, p.status, FAULT_GEMV_EMPTY_WAIT)) break;
-                request_w(stage, tile, kb);
-                request_x(stage, kb);
-                if (++kb == KB) kb = 0, ++tile;
+                request_w(stage, segs[4 * wsi], wkb);
+                request_x(stage, wkb);
+                advance(wsi, wkb);
                 if (++stage == NS) stage = 0, empty_parity ^= 1;
                 issued = i + 1;
             }
@@ -246,13 +277,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapW0, const __grid_constant_
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            const int n_units = (int)(u1 - u0);
-            int kb0 = (int)(u0 % KB);
-            int done = 0, seg = 0, stage = 0;
+            const int nseg = *nseg_s;
+            int stage = 0;
             uint32_t full_parity = 0;
-            while (done < n_units && !(*abort_flag)) {
-                const int left = n_units - done;
-                const int kb1 = (KB - kb0 < left) ? KB : kb0 + left;
+            for (int seg = 0; seg < nseg && !(*abort_flag); ++seg) {
+                const int kb0 = segs[4 * seg + 1], kb1 = segs[4 * seg + 2];
                 const int acc = seg & 1;
                 // wait until the epilogue has drained this accumulator (passes at once for its first use)
                 if (!mbar_wait_bounded(smem_u32(&acc_empty[acc]), (uint32_t)(((seg >> 1) & 1) ^ 1), abort_flag, p.status,
@@ -274,9 +303,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapW0, const __grid_constant_
                     if (++stage == NS) stage = 0, full_parity ^= 1;
                 }
                 tc_commit(smem_u32(&acc_full[acc]));
-                done += kb1 - kb0;
-                kb0 = 0;  // every later segment starts a new tile
-                ++seg;
             }
         }
     } else {
@@ -286,13 +312,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapW0, const __grid_constant_
         const int et = (warp - 2) * 32 + lane;
         pdl_wait();
         trace_mark(trec, 3);
-        const int n_units = (int)(u1 - u0);
-        int tile = (int)(u0 / KB), kb0 = (int)(u0 % KB), done = 0;
-        for (int seg = 0; done < n_units; ++seg, ++tile, kb0 = 0) {
-            const int left = n_units - done;
-            const int kb1 = (KB - kb0 < left) ? KB : kb0 + left;
+        const int nseg = *nseg_s;
+        for (int seg = 0; seg < nseg; ++seg) {
+            const int tile = segs[4 * seg], kb0 = segs[4 * seg + 1], kb1 = segs[4 * seg + 2];
             const int acc = seg & 1;
-            done += kb1 - kb0;
             mbar_wait_bounded(smem_u32(&acc_full[acc]), (uint32_t)((seg >> 1) & 1), abort_flag, p.status, FAULT_TC_ACC_WAIT);
             if (seg == 0) trace_mark(trec, 4);
             tc_fence_after();
@@ -313,8 +336,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapW0, const __grid_constant_
             if (!whole) {
                 bool finish;
                 // partial tile: park it, take a ticket; the last contributor adds all parts in CTA order
-                const bool leading = (seg == 0);
-                float* mine = p.partial + ((size_t)cta * 2 + (leading ? 0 : 1)) * (NB * kTcRows);
+                float* mine = p.partial + ((size_t)cta * 2 + segs[4 * seg + 3]) * (NB * kTcRows);
 #pragma unroll
                 for (int b = 0; b < NB; ++b) mine[b * kTcRows + row] = v[b];
                 named_bar_sync(2, 128);
@@ -507,7 +529,7 @@ static cudaError_t launch_tc_instance(const CUtensorMap& m0, const CUtensorMap& 
                                       int grid, cudaStream_t stream) {
     auto kernel = gemm_tc_kernel<NB>;
     constexpr size_t stage = kTcABytes + (size_t)NB * kTcBlockK * 2;
-    const size_t tail = 256 + (size_t)64 * (NB + 1) * sizeof(float);
+    const size_t tail = 256 + (size_t)64 * (NB + 1) * sizeof(float) + (4 * kTcMaxSegs + 4) * sizeof(int);
     const size_t cap = (size_t)max_smem_optin();
     int ns = (int)((cap - 1024 - tail) / stage);
     if (ns > kTcMaxStages) ns = kTcMaxStages;
