@@ -360,6 +360,12 @@ def main():
 
     run_steps(warmup)
     sync_all()
+    # launches per step, counted by the library while one step is issued eagerly
+    lib_ = _lib.load()
+    n0 = lib_.ezb_launch_count()
+    run_steps(1)
+    launches_per_step = int(lib_.ezb_launch_count() - n0)
+    sync_all()
 
     unroll = 1
     graph = None

@@ -75,6 +75,9 @@ bool chain_take_first() {
     return f;
 }
 
+static std::atomic<unsigned long long> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
 static std::atomic<int> g_tuning[EZB_TUNE_COUNT];
 static std::atomic<bool> g_tuning_ready{false};
 static const int kTuningDefaults[EZB_TUNE_COUNT] = {
@@ -652,6 +655,8 @@ int ezb_qwen3_decode_layer_tp_ffn(const void* hidden, const float* summed_o, con
                              kNoPrefetch, w.tc));
     return EZB_OK;
 }
+
+unsigned long long ezb_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int ezb_hbm_stream(int op, const void* b, const void* c, void* a, long long n_vec4, float scalar, int block_size,
                    int blocks_per_sm, ezb_stream_t stream) {

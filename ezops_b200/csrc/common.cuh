@@ -393,6 +393,7 @@ unsigned int* status_ptr();   // device address of the status word on the curren
 Trace trace_handle();         // tracing buffers of the current device (buf == null when disabled)
 void chain_begin();           // marks the next launch_pdl() of this thread as the first kernel of a call
 bool chain_take_first();      // true once after chain_begin()
+void count_launch();          // one more kernel launch issued by the library (ezb_launch_count)
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -415,6 +416,7 @@ cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
     attr[0].val.programmaticStreamSerializationAllowed = early_start ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    count_launch();
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 }  // namespace ezb

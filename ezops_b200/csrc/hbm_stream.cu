@@ -6,6 +6,7 @@
 // grid stride, four independent 128-bit accesses per thread and step.
 #include <cuda_runtime.h>
 
+#include "common.cuh"
 #include "launchers.h"
 
 namespace ezb {
@@ -62,6 +63,7 @@ cudaError_t launch_hbm_stream(int op, const void* b, const void* c, void* a, lon
     const dim3 grid((unsigned)(sms * blocks_per_sm)), blk((unsigned)block);
     const float4 *pb = static_cast<const float4*>(b), *pc = static_cast<const float4*>(c);
     float4* pa = static_cast<float4*>(a);
+    count_launch();
     switch (op) {
         case 0: hbm_stream_kernel<0><<<grid, blk, 0, stream>>>(pb, pc, pa, n_vec4, s, sink); break;
         case 1: hbm_stream_kernel<1><<<grid, blk, 0, stream>>>(pb, pc, pa, n_vec4, s, sink); break;

@@ -232,6 +232,12 @@ int ezb_qwen3_decode_stack(const void* hidden, void* out, const ezb_layer_t* lay
                            const void* rope_sin, int rope_position, void* workspace, size_t workspace_bytes, int B, int S,
                            int H, int I, int NH, int NKV, int D, float eps, ezb_stream_t stream);
 
+/* Kernel launches issued by the library in this process so far (every kernel of
+ * the library goes through one launch helper).  A diagnostic with no
+ * counterpart in the reference: benchmarks report launches per step from it
+ * instead of a hand-kept constant. */
+unsigned long long ezb_launch_count(void);
+
 /* Bandwidth calibration for the roofline profile of a GPU: one pass of a
  * STREAM-style kernel over n_vec4 128-bit elements; op 0 reads b, 1 writes a, 2
  * copies b to a, 3 is the triad a = b + scalar*c.  Replaces the stand-alone
