@@ -96,11 +96,12 @@ static const int kTuningDefaults[EZB_TUNE_COUNT] = {
     0,    // EZB_TUNE_L2_PREFETCH_ATTN_KB
     1,    // EZB_TUNE_TC
     3,    // EZB_TUNE_ATTN_WAVES_UNIFORM
+    0,    // EZB_TUNE_TP_POLL_ALL
 };
 static const char* kTuningEnv[EZB_TUNE_COUNT] = {
     "EZB_TUNE_PDL",          "EZB_TUNE_GEMV_SMEM_KB",   "EZB_TUNE_GEMV_PREFETCH", "EZB_TUNE_GEMV_CTAS_PER_SM",
     "EZB_TUNE_ATTN_MIN_CHUNK", "EZB_TUNE_ATTN_WAVES", "EZB_TUNE_GEMV_KC", "EZB_TUNE_GEMV_ROWS8", "EZB_TUNE_PDL_ACROSS_CALLS", "EZB_TUNE_L2_PREFETCH", "EZB_TUNE_L2_PREFETCH_KB", "EZB_TUNE_GEMV_WINDOW", "EZB_TUNE_L2_PREFETCH_ATTN_KB", "EZB_TUNE_TC",
-    "EZB_TUNE_ATTN_WAVES_UNIFORM",
+    "EZB_TUNE_ATTN_WAVES_UNIFORM", "EZB_TUNE_TP_POLL_ALL",
 };
 
 static void tuning_init() {
@@ -742,7 +743,8 @@ int ezb_qwen3_decode_layer_tp_fused(const void* hidden, void* K_cache, void* V_c
         set_last_message("workspace missing or smaller than ezb_qwen3_decode_layer_workspace_bytes()");
         return EZB_ERR_WORKSPACE;
     }
-    TpLink base = {world, rank, {}, {}, (long long)B * H, -1, -1, -1};
+    const int poll_mode = tuning(EZB_TUNE_TP_POLL_ALL);
+    TpLink base = {world, rank, {}, {}, (long long)B * H, -1, -1, -1, poll_mode == 1 || (poll_mode == 0 && world > 2) ? 1 : 0};
     for (int r = 0; r < world; ++r) {
         base.ctrl_peer[r] = static_cast<unsigned int*>(comm_bases_host[r]);
         base.inbox_peer[r] = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(comm_bases_host[r]) + kTpCtrlBytes);

@@ -66,6 +66,7 @@ struct TpLink {
     int push_inbox;    // -1 or the inbox this kernel's outputs are pushed into
     int gather_inbox;  // -1 or the inbox whose slots this kernel's prologue sums
     int bump_inbox;    // -1 or the inbox whose epoch this kernel advances
+    int poll_all;      // 1: the gathering prologue polls all ranks together, 4 elements per thread and step
 };
 static constexpr int kTpEpoch = 0;
 static constexpr int kTpCtrlBytes = 256;
@@ -86,14 +87,15 @@ __device__ __forceinline__ void tp_push(const TpLink& l, long long elem, float v
 // Called by exactly one thread of the grid, anywhere in the kernel.
 __device__ __forceinline__ void tp_bump(const TpLink& l) { l.ctrl_peer[l.rank][kTpEpoch + l.bump_inbox] += 1u; }
 
-// add[0..7] += sum over ranks (in rank order) of the 8 consecutive cells starting
-// at `elem` of this rank's inbox; polls until every cell carries `epoch`.
+// add[0..E-1] += sum over ranks (in rank order) of the E consecutive cells starting at `elem` of this
+// rank's inbox; polls until every cell carries `epoch`, G ranks at a time (G x E 64-bit registers).
 // Returns false (and records the fault) if the wait limit ran out.
-__device__ __forceinline__ bool tp_gather8(const TpLink& l, unsigned int epoch, long long elem, float (&add)[8],
-                                           unsigned int* status, long long t0) {
-    constexpr int G = 2;  // ranks polled together (more would spill the poll buffers of the calling kernels)
+template <int G, int E>
+__device__ __forceinline__ bool tp_gather(const TpLink& l, unsigned int epoch, long long elem, float (&add)[E],
+                                          unsigned int* status, long long t0) {
+    static_assert(E % 2 == 0, "cells are fetched in pairs");
     for (int w0 = 0; w0 < l.world; w0 += G) {
-        unsigned long long c[G][8];
+        unsigned long long c[G][E];
         unsigned int pending = 0;
 #pragma unroll
         for (int g = 0; g < G; ++g)
@@ -104,7 +106,7 @@ __device__ __forceinline__ bool tp_gather8(const TpLink& l, unsigned int epoch, 
                 if (pending & (1u << g)) {
                     const unsigned long long* src = tp_slot(l, l.rank, l.gather_inbox, w0 + g) + elem;
 #pragma unroll
-                    for (int q = 0; q < 4; ++q)
+                    for (int q = 0; q < E / 2; ++q)
                         asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];"
                                      : "=l"(c[g][2 * q]), "=l"(c[g][2 * q + 1])
                                      : "l"(src + 2 * q)
@@ -115,7 +117,7 @@ __device__ __forceinline__ bool tp_gather8(const TpLink& l, unsigned int epoch, 
                 if (pending & (1u << g)) {
                     bool all = true;
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) all = all && ((unsigned int)(c[g][e] >> 32) == epoch);
+                    for (int e = 0; e < E; ++e) all = all && ((unsigned int)(c[g][e] >> 32) == epoch);
                     if (all) pending &= ~(1u << g);
                 }
             if (!pending) break;
@@ -128,7 +130,7 @@ __device__ __forceinline__ bool tp_gather8(const TpLink& l, unsigned int epoch, 
         for (int g = 0; g < G; ++g)
             if (w0 + g < l.world) {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) add[e] += __uint_as_float((unsigned int)c[g][e]);
+                for (int e = 0; e < E; ++e) add[e] += __uint_as_float((unsigned int)c[g][e]);
             }
     }
     return true;

@@ -109,6 +109,19 @@ __device__ __forceinline__ void store_x8(bf16* srow, int i, const uint32_t (&w)[
         for (int t = 0; t < 4; ++t) base[t * 4 + j] = w[t];
     }
 }
+// Half of store_x8: the 4 elements (two pairs) of half vector h = 2*i + (0 | 1).
+template <bool PERMUTE32>
+__device__ __forceinline__ void store_x4(bf16* srow, int h, const uint32_t (&w)[2]) {
+    if (!PERMUTE32) {
+        *reinterpret_cast<uint2*>(srow + h * 4) = make_uint2(w[0], w[1]);
+    } else {
+        const int i = h >> 1, t0 = (h & 1) * 2;
+        uint32_t* base = reinterpret_cast<uint32_t*>(srow + (i >> 2) * 32);
+        const int j = i & 3;
+        base[t0 * 4 + j] = w[0];
+        base[(t0 + 1) * 4 + j] = w[1];
+    }
+}
 template <bool PERMUTE32>
 __device__ __forceinline__ void load_x8(const bf16* srow, int i, uint32_t (&w)[4]) {
     if (!PERMUTE32) {
@@ -149,22 +162,44 @@ __device__ __forceinline__ void stage_activations(const GemvParams& p, bf16* xs,
         float ssq = 0.f;
         if (LINK && active && gather) {
             // Fused tensor-parallel sum: x <- bf16(x + bf16(sum over ranks of the inbox slots)), see TpLink.
-            for (int i = sub; i < nvec; i += nthr) {
-                const uint4 raw = *reinterpret_cast<const uint4*>(xrow + i * 8);
-                float add[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                tp_gather8(p.link, epoch, (long long)b * p.K + i * 8, add, p.status, t0);
-                uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
+            // Two ranks: 8 elements per thread and step.  More ranks: 4 elements per step with all ranks
+            // polled together, so the number of dependent L2 round trips does not grow with the world.
+            if (!p.link.poll_all) {
+                for (int i = sub; i < nvec; i += nthr) {
+                    const uint4 raw = *reinterpret_cast<const uint4*>(xrow + i * 8);
+                    float add[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                    tp_gather<2, 8>(p.link, epoch, (long long)b * p.K + i * 8, add, p.status, t0);
+                    uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-                for (int e = 0; e < 4; ++e)
-                    w4[e] = pack_bf16(bf16_lo(w4[e]) + round_bf16(add[2 * e]), bf16_hi(w4[e]) + round_bf16(add[2 * e + 1]));
-                if (blockIdx.x == 0 && p.x_sum_out)
-                    *reinterpret_cast<uint4*>(p.x_sum_out + (long long)b * p.ldsum + i * 8) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+                    for (int e = 0; e < 4; ++e)
+                        w4[e] = pack_bf16(bf16_lo(w4[e]) + round_bf16(add[2 * e]), bf16_hi(w4[e]) + round_bf16(add[2 * e + 1]));
+                    if (blockIdx.x == 0 && p.x_sum_out)
+                        *reinterpret_cast<uint4*>(p.x_sum_out + (long long)b * p.ldsum + i * 8) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float lo = bf16_lo(w4[e]), hi = bf16_hi(w4[e]);
-                    ssq += lo * lo + hi * hi;
+                    for (int e = 0; e < 4; ++e) {
+                        const float lo = bf16_lo(w4[e]), hi = bf16_hi(w4[e]);
+                        ssq += lo * lo + hi * hi;
+                    }
+                    store_x8<PERMUTE32>(srow, i, w4);
                 }
-                store_x8<PERMUTE32>(srow, i, w4);
+            } else {
+                for (int h = sub; h < 2 * nvec; h += nthr) {  // h: half vector (4 elements)
+                    const uint2 raw = *reinterpret_cast<const uint2*>(xrow + h * 4);
+                    float add[4] = {0.f, 0.f, 0.f, 0.f};
+                    tp_gather<8, 4>(p.link, epoch, (long long)b * p.K + h * 4, add, p.status, t0);
+                    uint32_t w2[2] = {raw.x, raw.y};
+#pragma unroll
+                    for (int e = 0; e < 2; ++e)
+                        w2[e] = pack_bf16(bf16_lo(w2[e]) + round_bf16(add[2 * e]), bf16_hi(w2[e]) + round_bf16(add[2 * e + 1]));
+                    if (blockIdx.x == 0 && p.x_sum_out)
+                        *reinterpret_cast<uint2*>(p.x_sum_out + (long long)b * p.ldsum + h * 4) = make_uint2(w2[0], w2[1]);
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const float lo = bf16_lo(w2[e]), hi = bf16_hi(w2[e]);
+                        ssq += lo * lo + hi * hi;
+                    }
+                    store_x4<PERMUTE32>(srow, h, w2);
+                }
             }
         } else if (active) {
             for (int base = 0; base < nvec; base += U * nthr) {

@@ -92,7 +92,7 @@ __device__ __forceinline__ uint4 load_row8(const RowPrepParams& p, long long row
     if (p.link.world > 0 && p.link.gather_inbox >= 0) {
         // the term to add is the sum, in rank order, of the partials in this rank's inbox
         float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        tp_gather8(p.link, epoch, row * p.dim + i * 8, a, p.status, t0);
+        tp_gather<8, 8>(p.link, epoch, row * p.dim + i * 8, a, p.status, t0);
         raw.x = pack_bf16(bf16_lo(raw.x) + round_bf16(a[0]), bf16_hi(raw.x) + round_bf16(a[1]));
         raw.y = pack_bf16(bf16_lo(raw.y) + round_bf16(a[2]), bf16_hi(raw.y) + round_bf16(a[3]));
         raw.z = pack_bf16(bf16_lo(raw.z) + round_bf16(a[4]), bf16_hi(raw.z) + round_bf16(a[5]));

@@ -1,0 +1,67 @@
+"""One rank of the multi-GPU check of the tensor-parallel decode layer (launched by
+tests/test_tp_multi_gpu.py through torch.distributed.run, one process per GPU).
+
+Every rank runs the layer with the exchange fused into the kernels and with NCCL in between the
+three parts; rank 0 compares both with the CPU oracle on the unsharded weights.  Prints one line
+per case and exits 0 when every check held.
+"""
+
+import os
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+from ezops_b200 import _lib, tp as tpm, workloads as wl  # noqa: E402
+from oracle import ezops_oracle as orc  # noqa: E402
+
+
+def main() -> int:
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    ok = True
+    for sh, B, S in [(wl.QWEN3_VL_2B, 1, 700), (wl.QWEN3_8B, 3, 1025)]:
+        hidden, K0, V0, Wqkv, Wo, Wgu, Wd = wl.decode_layer_inputs(sh, B, S)
+        heads = (sh.num_heads, sh.num_kv_heads, sh.head_dim)
+        ref = orc.qwen3_dense_decode_ref(hidden, K0.clone(), V0.clone(), Wqkv, Wo, Wgu, Wd, *heads) if rank == 0 else None
+        args = (B, S, sh.hidden, sh.inter, sh.num_heads, sh.head_dim, sh.num_kv_heads)
+        nccl = tpm.TensorParallelDecodeLayer(*args)
+        fused = tpm.TensorParallelDecodeLayer(*args, exchange="fused")
+        shards = tuple(t.cuda() for t in tpm.shard_layer_weights(Wqkv, Wo, Wgu, Wd, *heads, world, rank))
+        Kl, Vl = tpm.shard_kv_cache(K0, world, rank).cuda(), tpm.shard_kv_cache(V0, world, rank).cuda()
+        hid = hidden.cuda()
+        a = nccl(hid, Kl.clone(), Vl.clone(), *shards)
+        torch.cuda.synchronize()
+        dist.barrier()
+        outs = [fused(hid, Kl, Vl, *shards) for _ in range(6)]  # several epochs of the exchange
+        torch.cuda.synchronize()
+        status = _lib.device_status()
+        gathered = [torch.empty_like(a) for _ in range(world)]
+        dist.all_gather(gathered, outs[-1])
+        same_on_all_ranks = all(torch.equal(g, outs[-1]) for g in gathered)
+        repeatable = all(torch.equal(o, outs[0]) for o in outs)
+        verdict = torch.tensor([int(same_on_all_ranks and repeatable and status == 0)], device="cuda")
+        if rank == 0:
+            err_fused = ((outs[0].cpu().float() - ref.float()).norm() / ref.float().norm()).item()
+            err_nccl = ((a.cpu().float() - ref.float()).norm() / ref.float().norm()).item()
+            good = err_fused < 1e-2 and err_nccl < 1e-2 and (world != 2 or torch.equal(a, outs[0]))
+            verdict *= int(good)
+            print(f"tp={world} {sh.name} B={B} S={S}: rel_fro fused {err_fused:.3e} nccl {err_nccl:.3e} "
+                  f"identical_across_ranks={same_on_all_ranks} repeatable={repeatable} status={status}", flush=True)
+        dist.all_reduce(verdict, op=dist.ReduceOp.MIN)
+        ok = ok and bool(verdict.item())
+        torch.cuda.synchronize()
+        dist.barrier()
+        fused.close()
+    dist.barrier()
+    sys.stdout.flush()
+    os._exit(0 if ok else 1)  # no NCCL teardown: see bench.py
+
+
+if __name__ == "__main__":
+    main()
