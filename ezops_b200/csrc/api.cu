@@ -722,44 +722,73 @@ int ezb_ipc_close(void* ptr) {
     return EZB_OK;
 }
 
-int ezb_qwen3_decode_layer_tp_fused(const void* hidden, void* K_cache, void* V_cache, const void* Wqkv_local,
-                                    const void* Wo_local, const void* Wgu_local, const void* Wd_local, void* out,
-                                    void* workspace, size_t workspace_bytes, void* const* comm_bases_host, int world,
-                                    int rank, int B, int S, int H, int I_local, int NH_local, int NKV_local, int D, float eps,
-                                    ezb_stream_t stream) {
-    EZB_REQUIRE(hidden && K_cache && V_cache && Wqkv_local && Wo_local && Wgu_local && Wd_local && out && comm_bases_host,
-                "null pointer");
+static int make_tp_link(TpLink& base, void* const* comm_bases_host, int world, int rank, int B, int H) {
+    EZB_REQUIRE(comm_bases_host, "null pointer");
     EZB_REQUIRE(world >= 1 && world <= kTpSlots && rank >= 0 && rank < world, "world must be 1..8 and rank inside it");
-    if (int rc = check_layer_args(B, S, H, I_local, NH_local, NKV_local, D)) return rc;
-    EZB_REQUIRE_SHAPE(gemv_small_batch_eligible(B, H) && gemv_small_batch_eligible(B, NH_local * D) &&
-                          gemv_small_batch_eligible(B, I_local),
-                      "the fused exchange needs a batch small enough for the resident-activation kernel");
-    EZB_REQUIRE(aligned16(hidden) && aligned16(K_cache) && aligned16(V_cache) && aligned16(Wqkv_local) &&
-                    aligned16(Wo_local) && aligned16(Wgu_local) && aligned16(Wd_local) && aligned16(out),
-                "pointers must be 16-byte aligned");
     for (int w = 0; w < world; ++w) EZB_REQUIRE(comm_bases_host[w] && aligned16(comm_bases_host[w]), "bad comm buffer pointer");
-    LayerWorkspace w = carve_layer_ws(workspace, B, S, H, I_local, NH_local, NKV_local, D);
-    if (!workspace || workspace_bytes < w.total) {
-        set_last_message("workspace missing or smaller than ezb_qwen3_decode_layer_workspace_bytes()");
-        return EZB_ERR_WORKSPACE;
-    }
     const int poll_mode = tuning(EZB_TUNE_TP_POLL_ALL);
-    TpLink base = {world, rank, {}, {}, (long long)B * H, -1, -1, -1, poll_mode == 1 || (poll_mode == 0 && world > 2) ? 1 : 0};
+    base = {world, rank, {}, {}, (long long)B * H, -1, -1, -1, poll_mode == 1 || (poll_mode == 0 && world > 2) ? 1 : 0};
     for (int r = 0; r < world; ++r) {
         base.ctrl_peer[r] = static_cast<unsigned int*>(comm_bases_host[r]);
         base.inbox_peer[r] = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(comm_bases_host[r]) + kTpCtrlBytes);
     }
-    const bf16* hid = static_cast<const bf16*>(hidden);
-    const bf16* wgu = static_cast<const bf16*>(Wgu_local);
-    const int Q = NH_local * D;
+    return EZB_OK;
+}
+
+static int check_tp_fused_shape(int B, int H, int I_local, int NH_local, int D) {
+    EZB_REQUIRE_SHAPE(gemv_small_batch_eligible(B, H) && gemv_small_batch_eligible(B, NH_local * D) &&
+                          gemv_small_batch_eligible(B, I_local),
+                      "the fused exchange needs a batch small enough for the resident-activation kernel");
+    return EZB_OK;
+}
+
+// One tensor-parallel layer with the sums over ranks inside the kernels (five launches).
+//   x_prev / gather_prev: the layer input is x_prev + sum(inbox 1) when gather_prev is set (the
+//   previous layer's down projection pushed there), and is written to layer_in by the QKV kernel;
+//   otherwise the layer input is x_prev itself and layer_in is not used.
+//   x2_out receives hidden + sum(inbox 0); the down projection pushes into inbox 1, so the caller
+//   finishes with x2_out + sum(inbox 1) (the next layer's QKV prologue, or a final row kernel).
+static int run_layer_tp_fused(const bf16* x_prev, bool gather_prev, bf16* layer_in, bf16* x2_out, bf16* Kc, bf16* Vc,
+                              const bf16* Wqkv, const bf16* Wo, const bf16* wgu, const bf16* Wd, const LayerWorkspace& w,
+                              const TpLink& base, int B, int S, int H, int I_local, int NH_local, int NKV_local, int D, float eps,
+                              const LayerExtras& ex, cudaStream_t stream) {
+    const int Q = NH_local * D, rows = (NH_local + 2 * NKV_local) * D;
     const int pf_kb = tuning(EZB_TUNE_L2_PREFETCH_KB);
-    chain_begin();
-    EZB_CUDA_TRY(launch_qkv_and_attention(hid, static_cast<bf16*>(K_cache), static_cast<bf16*>(V_cache),
-                                          static_cast<const bf16*>(Wqkv_local), w, B, S, H, NH_local, NKV_local, D, eps, stream,
-                                          static_cast<const bf16*>(Wo_local)));
-    {   // o_proj: partial -> inbox 0 of every rank; its last CTA also opens the next epoch of inbox 1
+    const bf16* hid = gather_prev ? layer_in : x_prev;
+    {   // QKV projection (norm prologue; gathers the previous layer's second sum when there is one)
         GemvArgs g;
-        g.W0 = static_cast<const bf16*>(Wo_local), g.ldw = Q, g.N = H, g.K = Q, g.B = B;
+        g.W0 = Wqkv, g.ldw = H, g.N = rows, g.K = H, g.B = B;
+        g.x = x_prev, g.ldx = H;
+        g.norm_w = ex.input_norm_w;
+        g.eps = eps, g.prologue = gather_prev ? PRO_ADD_RMSNORM : PRO_RMSNORM, g.epilogue = EPI_STORE;
+        g.out = w.qkv, g.ldout = rows;
+        g.xn_scratch = w.xn;
+        g.trace_id = 1;
+        if (gather_prev) {
+            g.x_sum_out = layer_in, g.ldsum = H;
+            g.link = base, g.link.gather_inbox = 1;
+        }
+        const size_t kv_bytes = (size_t)B * NKV_local * S * D * 2;
+        if (2 * kv_bytes <= ((size_t)48 << 20)) g.next = one_plan(prefetch_plan_flat(Kc, Vc, kv_bytes));
+        EZB_CUDA_TRY(launch_gemv(g, stream));
+    }
+    {
+        AttnArgs a;
+        a.K = Kc, a.V = Vc;
+        a.Out = w.attn_out, a.o_bstride = Q;
+        a.B = B, a.H = NH_local, a.NKV = NKV_local, a.S = S, a.D = D;
+        a.workspace = w.attn;
+        a.fuse_new_token = 1;
+        a.qkv = w.qkv, a.qkv_bstride = rows;
+        a.K_cache_w = Kc, a.V_cache_w = Vc;
+        a.eps = eps;
+        a.q_norm_w = ex.q_norm_w, a.k_norm_w = ex.k_norm_w, a.rope_cos = ex.rope_cos, a.rope_sin = ex.rope_sin;
+        if ((size_t)H * Q * 2 <= ((size_t)64 << 20)) a.next = one_plan(next_rows(Wo, nullptr, H, Q, 1 << 20));
+        EZB_CUDA_TRY(launch_attn_decode(a, stream));
+    }
+    {   // o_proj: partial -> inbox 0 of every rank; also opens the next epoch of inbox 1
+        GemvArgs g;
+        g.W0 = Wo, g.ldw = Q, g.N = H, g.K = Q, g.B = B;
         g.x = w.attn_out, g.ldx = Q;
         g.epilogue = EPI_PUSH_F32, g.ldout = H;
         g.link = base, g.link.push_inbox = 0, g.link.bump_inbox = 1;
@@ -767,36 +796,125 @@ int ezb_qwen3_decode_layer_tp_fused(const void* hidden, void* K_cache, void* V_c
         g.trace_id = 3;
         EZB_CUDA_TRY(launch_gemv(g, stream));
     }
-    {   // gate/up: x2 = hidden + sum(inbox 0), norm, SwiGLU
+    {   // gate/up: x2 = layer input + sum(inbox 0), norm, SwiGLU
         GemvArgs g;
         g.W0 = wgu, g.W1 = wgu + (size_t)I_local * H, g.ldw = H, g.N = I_local, g.K = H, g.B = B;
         g.x = hid, g.ldx = H;
-        g.x_sum_out = w.x2, g.ldsum = H;
+        g.x_sum_out = x2_out, g.ldsum = H;
+        g.norm_w = ex.post_norm_w;
         g.eps = eps, g.prologue = PRO_ADD_RMSNORM, g.epilogue = EPI_SWIGLU;
         g.out = w.h, g.ldout = I_local;
         g.link = base, g.link.gather_inbox = 0;
-        g.next = one_plan(next_rows(static_cast<const bf16*>(Wd_local), nullptr, H, I_local, pf_kb));
+        g.next = one_plan(next_rows(Wd, nullptr, H, I_local, pf_kb));
         g.trace_id = 4;
         EZB_CUDA_TRY(launch_gemv(g, stream));
     }
     {   // down: partial -> inbox 1 of every rank; opens the next epoch of inbox 0
         GemvArgs g;
-        g.W0 = static_cast<const bf16*>(Wd_local), g.ldw = I_local, g.N = H, g.K = I_local, g.B = B;
+        g.W0 = Wd, g.ldw = I_local, g.N = H, g.K = I_local, g.B = B;
         g.x = w.h, g.ldx = I_local;
         g.epilogue = EPI_PUSH_F32, g.ldout = H;
         g.link = base, g.link.push_inbox = 1, g.link.bump_inbox = 0;
+        if (ex.next_Wqkv) g.next = one_plan(next_rows(ex.next_Wqkv, nullptr, rows, H, pf_kb));
         g.trace_id = 5;
         EZB_CUDA_TRY(launch_gemv(g, stream));
     }
-    {   // out = x2 + sum(inbox 1)
-        RowPrepArgs a;
-        a.x = w.x2, a.ldx = H;
-        a.sum_out = static_cast<bf16*>(out), a.ldsum = H;
-        a.rows = B, a.dim = H, a.normalize = 0;
-        a.link = base, a.link.gather_inbox = 1;
-        EZB_CUDA_TRY(launch_row_prep(a, stream));
-    }
     return EZB_OK;
+}
+
+// out = x2 + sum(inbox 1): closes the last layer of a fused tensor-parallel chain
+static int finish_tp_fused(const bf16* x2, bf16* out, const TpLink& base, int B, int H, cudaStream_t stream) {
+    RowPrepArgs a;
+    a.x = x2, a.ldx = H;
+    a.sum_out = out, a.ldsum = H;
+    a.rows = B, a.dim = H, a.normalize = 0;
+    a.link = base, a.link.gather_inbox = 1;
+    EZB_CUDA_TRY(launch_row_prep(a, stream));
+    return EZB_OK;
+}
+
+int ezb_qwen3_decode_layer_tp_fused(const void* hidden, void* K_cache, void* V_cache, const void* Wqkv_local,
+                                    const void* Wo_local, const void* Wgu_local, const void* Wd_local, void* out,
+                                    void* workspace, size_t workspace_bytes, void* const* comm_bases_host, int world,
+                                    int rank, int B, int S, int H, int I_local, int NH_local, int NKV_local, int D, float eps,
+                                    ezb_stream_t stream) {
+    EZB_REQUIRE(hidden && K_cache && V_cache && Wqkv_local && Wo_local && Wgu_local && Wd_local && out, "null pointer");
+    TpLink base;
+    if (int rc = make_tp_link(base, comm_bases_host, world, rank, B, H)) return rc;
+    if (int rc = check_layer_args(B, S, H, I_local, NH_local, NKV_local, D)) return rc;
+    if (int rc = check_tp_fused_shape(B, H, I_local, NH_local, D)) return rc;
+    EZB_REQUIRE(aligned16(hidden) && aligned16(K_cache) && aligned16(V_cache) && aligned16(Wqkv_local) &&
+                    aligned16(Wo_local) && aligned16(Wgu_local) && aligned16(Wd_local) && aligned16(out),
+                "pointers must be 16-byte aligned");
+    LayerWorkspace w = carve_layer_ws(workspace, B, S, H, I_local, NH_local, NKV_local, D);
+    if (!workspace || workspace_bytes < w.total) {
+        set_last_message("workspace missing or smaller than ezb_qwen3_decode_layer_workspace_bytes()");
+        return EZB_ERR_WORKSPACE;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    chain_begin();
+    if (int rc = run_layer_tp_fused(static_cast<const bf16*>(hidden), false, nullptr, w.x2, static_cast<bf16*>(K_cache),
+                                    static_cast<bf16*>(V_cache), static_cast<const bf16*>(Wqkv_local),
+                                    static_cast<const bf16*>(Wo_local), static_cast<const bf16*>(Wgu_local),
+                                    static_cast<const bf16*>(Wd_local), w, base, B, S, H, I_local, NH_local, NKV_local, D, eps,
+                                    kPlainLayer, st))
+        return rc;
+    return finish_tp_fused(w.x2, static_cast<bf16*>(out), base, B, H, st);
+}
+
+size_t ezb_qwen3_decode_stack_tp_fused_workspace_bytes(int B, int S, int H, int I_local, int NH_local, int NKV_local, int D) {
+    if (check_layer_args(B, S, H, I_local, NH_local, NKV_local, D)) return 0;
+    return carve_layer_ws(nullptr, B, S, H, I_local, NH_local, NKV_local, D).total + 4 * round256((size_t)B * H * sizeof(bf16));
+}
+
+int ezb_qwen3_decode_stack_tp_fused(const void* hidden, void* out, const ezb_layer_t* layers_local, int n_layers,
+                                    const void* rope_cos, const void* rope_sin, int rope_position, void* workspace,
+                                    size_t workspace_bytes, void* const* comm_bases_host, int world, int rank, int B, int S,
+                                    int H, int I_local, int NH_local, int NKV_local, int D, float eps, ezb_stream_t stream) {
+    EZB_REQUIRE(hidden && out && layers_local && n_layers >= 1, "null pointer or no layers");
+    EZB_REQUIRE((rope_cos == nullptr) == (rope_sin == nullptr) && rope_position >= 0, "rotary tables come as a pair; position >= 0");
+    TpLink base;
+    if (int rc = make_tp_link(base, comm_bases_host, world, rank, B, H)) return rc;
+    if (int rc = check_layer_args(B, S, H, I_local, NH_local, NKV_local, D)) return rc;
+    if (int rc = check_tp_fused_shape(B, H, I_local, NH_local, D)) return rc;
+    EZB_REQUIRE(aligned16(hidden) && aligned16(out) && aligned16(rope_cos) && aligned16(rope_sin), "pointers must be 16-byte aligned");
+    for (int l = 0; l < n_layers; ++l) {
+        const ezb_layer_t& L = layers_local[l];
+        EZB_REQUIRE(L.K_cache && L.V_cache && L.Wqkv && L.Wo && L.Wgu && L.Wd, "null pointer in a layer");
+        EZB_REQUIRE(aligned16(L.K_cache) && aligned16(L.V_cache) && aligned16(L.Wqkv) && aligned16(L.Wo) && aligned16(L.Wgu) &&
+                        aligned16(L.Wd) && aligned16(L.input_norm_w) && aligned16(L.post_norm_w) && aligned16(L.q_norm_w) &&
+                        aligned16(L.k_norm_w),
+                    "layer pointers must be 16-byte aligned");
+    }
+    LayerWorkspace w = carve_layer_ws(workspace, B, S, H, I_local, NH_local, NKV_local, D);
+    const size_t hbytes = round256((size_t)B * H * sizeof(bf16));
+    if (!workspace || workspace_bytes < w.total + 4 * hbytes) {
+        set_last_message("workspace missing or smaller than ezb_qwen3_decode_stack_tp_fused_workspace_bytes()");
+        return EZB_ERR_WORKSPACE;
+    }
+    unsigned char* extra = static_cast<unsigned char*>(workspace) + w.total;
+    bf16* layer_in[2] = {reinterpret_cast<bf16*>(extra), reinterpret_cast<bf16*>(extra + hbytes)};
+    bf16* x2[2] = {reinterpret_cast<bf16*>(extra + 2 * hbytes), reinterpret_cast<bf16*>(extra + 3 * hbytes)};
+    const bf16* cos_row = rope_cos ? static_cast<const bf16*>(rope_cos) + (size_t)rope_position * D : nullptr;
+    const bf16* sin_row = rope_sin ? static_cast<const bf16*>(rope_sin) + (size_t)rope_position * D : nullptr;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    chain_begin();
+    for (int l = 0; l < n_layers; ++l) {
+        const ezb_layer_t& L = layers_local[l];
+        LayerExtras ex;
+        ex.input_norm_w = static_cast<const bf16*>(L.input_norm_w), ex.post_norm_w = static_cast<const bf16*>(L.post_norm_w);
+        ex.q_norm_w = static_cast<const bf16*>(L.q_norm_w), ex.k_norm_w = static_cast<const bf16*>(L.k_norm_w);
+        ex.rope_cos = cos_row, ex.rope_sin = sin_row;
+        ex.next_Wqkv = (l + 1 < n_layers) ? static_cast<const bf16*>(layers_local[l + 1].Wqkv) : nullptr;
+        // layer l > 0 reads x2 of layer l-1 and folds that layer's second sum into its own QKV prologue
+        const bf16* x_prev = l == 0 ? static_cast<const bf16*>(hidden) : x2[(l - 1) & 1];
+        if (int rc = run_layer_tp_fused(x_prev, l > 0, layer_in[l & 1], x2[l & 1], static_cast<bf16*>(L.K_cache),
+                                        static_cast<bf16*>(L.V_cache), static_cast<const bf16*>(L.Wqkv),
+                                        static_cast<const bf16*>(L.Wo), static_cast<const bf16*>(L.Wgu),
+                                        static_cast<const bf16*>(L.Wd), w, base, B, S, H, I_local, NH_local, NKV_local, D, eps, ex, st))
+            return rc;
+    }
+    return finish_tp_fused(x2[(n_layers - 1) & 1], static_cast<bf16*>(out), base, B, H, st);
 }
 
 int ezb_residual_add_f32(const void* x2, const float* summed_d, void* out, int B, int H, ezb_stream_t stream) {

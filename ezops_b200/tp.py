@@ -188,3 +188,64 @@ class TensorParallelDecodeLayer:
         self._sum_over_ranks(bufs["partial_d"])
         self._part_out(out, bufs)
         return out
+
+
+def shard_stack(layers, num_heads: int, num_kv_heads: int, head_dim: int, tp: int, rank: int):
+    """Per-rank copy of a stack's layers (dicts as ``Qwen3DecodeStackOp.gen_data`` returns them):
+    weights and caches sharded as for one layer, norm weights replicated."""
+    out = []
+    for L in layers:
+        Wqkv, Wo, Wgu, Wd = shard_layer_weights(L["Wqkv"], L["Wo"], L["Wgu"], L["Wd"], num_heads, num_kv_heads, head_dim, tp, rank)
+        local = {"K_cache": shard_kv_cache(L["K_cache"], tp, rank), "V_cache": shard_kv_cache(L["V_cache"], tp, rank),
+                 "Wqkv": Wqkv, "Wo": Wo, "Wgu": Wgu, "Wd": Wd}
+        for key in ("input_norm_w", "post_norm_w", "q_norm_w", "k_norm_w"):
+            local[key] = L.get(key)
+        out.append(local)
+    return out
+
+
+class TensorParallelDecodeStack(TensorParallelDecodeLayer):
+    """All layers of a decoder stack on this rank's shards in one call, the sums over ranks fused
+    into the kernels (``ezb_qwen3_decode_stack_tp_fused``).  ``__call__(hidden, layers_local, cos,
+    sin)``; every rank returns the same [B, H] output.  Batch <= 8 (the fused exchange's limit)."""
+
+    def __init__(self, batch, seq_len, hidden_size, intermediate_size, num_heads, head_dim, num_kv_heads, num_layers, group=None):
+        super().__init__(batch, seq_len, hidden_size, intermediate_size, num_heads, head_dim, num_kv_heads, group=group,
+                         exchange="fused")
+        self.L = num_layers
+        self._table, self._table_key, self._stack_ws = None, None, None
+
+    def _layer_table(self, layers):
+        names = ("K_cache", "V_cache", "Wqkv", "Wo", "Wgu", "Wd", "input_norm_w", "post_norm_w", "q_norm_w", "k_norm_w")
+        key = tuple(0 if L.get(n) is None else L[n].data_ptr() for L in layers for n in names)
+        if key != self._table_key:
+            table = (_lib.LayerStruct * len(layers))()
+            for i, L in enumerate(layers):
+                for n in names:
+                    t = L.get(n)
+                    if t is None and not n.endswith("_norm_w"):
+                        raise ValueError(f"layer {i}: {n} is required")
+                    if t is not None and (not t.is_cuda or t.dtype != torch.bfloat16 or not t.is_contiguous()):
+                        raise ValueError(f"layer {i}: {n} must be a contiguous bf16 CUDA tensor")
+                    setattr(table[i], n, None if t is None else t.data_ptr())
+            self._table, self._table_key = table, key
+        return self._table
+
+    def __call__(self, hidden, layers_local, cos=None, sin=None, out=None):
+        if len(layers_local) != self.L:
+            raise ValueError(f"expected {self.L} layers, got {len(layers_local)}")
+        lib = _lib.load()
+        if self._stack_ws is None or self._stack_ws.device != hidden.device:
+            need = lib.ezb_qwen3_decode_stack_tp_fused_workspace_bytes(self.B, self.S, self.H, self.I_l, self.NH_l, self.NKV_l, self.D)
+            self._stack_ws = torch.zeros(max(need, 256), dtype=torch.uint8, device=hidden.device)
+        comm = self._fused_comm(hidden.device)
+        table = self._layer_table(layers_local)
+        if out is None:
+            out = torch.empty_like(hidden)
+        _lib.check(lib.ezb_qwen3_decode_stack_tp_fused(
+            hidden.data_ptr(), out.data_ptr(), table, self.L, None if cos is None else cos.data_ptr(),
+            None if sin is None else sin.data_ptr(), self.S - 1, self._stack_ws.data_ptr(), self._stack_ws.numel(), comm["bases"],
+            self.tp, self.rank, self.B, self.S, self.H, self.I_l, self.NH_l, self.NKV_l, self.D, self.rms_eps,
+            torch.cuda.current_stream().cuda_stream))
+        return out
+

@@ -239,6 +239,18 @@ int ezb_qwen3_decode_stack(const void* hidden, void* out, const ezb_layer_t* lay
  * instead of a hand-kept constant. */
 unsigned long long ezb_launch_count(void);
 
+/* The stack of layers, tensor parallel with the exchange fused into the kernels:
+ * ezb_qwen3_decode_stack on this rank's shards (as ezb_qwen3_decode_layer_tp_fused
+ * takes them), one call for all layers.  A layer's second sum is folded into
+ * the next layer's QKV prologue, so a layer costs five launches and only the
+ * last one ends with the small kernel that adds the final sum.  Same rules for
+ * the communication buffers; no counterpart in the reference. */
+size_t ezb_qwen3_decode_stack_tp_fused_workspace_bytes(int B, int S, int H, int I_local, int NH_local, int NKV_local, int D);
+int ezb_qwen3_decode_stack_tp_fused(const void* hidden, void* out, const ezb_layer_t* layers_local, int n_layers,
+                                    const void* rope_cos, const void* rope_sin, int rope_position, void* workspace,
+                                    size_t workspace_bytes, void* const* comm_bases_host, int world, int rank, int B, int S,
+                                    int H, int I_local, int NH_local, int NKV_local, int D, float eps, ezb_stream_t stream);
+
 /* Bandwidth calibration for the roofline profile of a GPU: one pass of a
  * STREAM-style kernel over n_vec4 128-bit elements; op 0 reads b, 1 writes a, 2
  * copies b to a, 3 is the triad a = b + scalar*c.  Replaces the stand-alone

@@ -577,3 +577,27 @@ def test_decode_stack_of_one_plain_layer_is_the_layer_op(ez):
     stack_op = ez.Qwen3DecodeStackOp(B, S, sh.hidden, sh.inter, sh.num_heads, sh.head_dim, 1, backend="cuda", num_kv_heads=sh.num_kv_heads)
     got = stack_op(hid.cuda(), _stack_to_device(layers))
     assert torch.equal(got, want)
+
+
+def test_tp_fused_stack_world_one_matches_the_stack(ez):
+    """The tensor-parallel stack with one rank (its exchange pushes into its own inbox, the second
+    sum of a layer is gathered by the next layer's QKV kernel) reproduces the single-GPU stack bit for bit."""
+    from ezops_b200 import _lib
+    from ezops_b200 import tp as tpm
+    from ezops_b200 import workloads as wl
+
+    sh, B, S, NL = wl.QWEN3_VL_2B, 2, 260, 3
+    hid, layers, cos, sin = wl.decode_stack_inputs(sh, B, S, NL)
+    op = ez.Qwen3DecodeStackOp(B, S, sh.hidden, sh.inter, sh.num_heads, sh.head_dim, NL, backend="cuda", num_kv_heads=sh.num_kv_heads)
+    want = op(hid.cuda(), _stack_to_device(layers), cos.cuda(), sin.cuda())
+    stack = tpm.TensorParallelDecodeStack(B, S, sh.hidden, sh.inter, sh.num_heads, sh.head_dim, sh.num_kv_heads, NL)
+    try:
+        dl = _stack_to_device(layers)
+        for _ in range(2):
+            got = stack(hid.cuda(), dl, cos.cuda(), sin.cuda())
+            assert torch.equal(got, want)
+        assert _lib.device_status() == 0
+    finally:
+        torch.cuda.synchronize()
+        stack.close()
+

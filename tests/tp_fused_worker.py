@@ -58,6 +58,31 @@ def main() -> int:
         torch.cuda.synchronize()
         dist.barrier()
         fused.close()
+    # the whole stack: three layers with norm weights and RoPE, second sums folded into the next layer
+    sh, B, S, NL = wl.QWEN3_VL_2B, 2, 300, 3
+    hid, layers, cos, sin = wl.decode_stack_inputs(sh, B, S, NL)
+    import copy
+
+    ref = orc.qwen3_decode_stack_ref(hid, copy.deepcopy(layers), sh.num_heads, sh.num_kv_heads, sh.head_dim, cos, sin) if rank == 0 else None
+    local = [{k: (None if v is None else v.cuda()) for k, v in L.items()}
+             for L in tpm.shard_stack(layers, sh.num_heads, sh.num_kv_heads, sh.head_dim, world, rank)]
+    stack = tpm.TensorParallelDecodeStack(B, S, sh.hidden, sh.inter, sh.num_heads, sh.head_dim, sh.num_kv_heads, NL)
+    outs = [stack(hid.cuda(), local, cos.cuda(), sin.cuda()) for _ in range(3)]
+    torch.cuda.synchronize()
+    status = _lib.device_status()
+    gathered = [torch.empty_like(outs[0]) for _ in range(world)]
+    dist.all_gather(gathered, outs[-1])
+    good = all(torch.equal(g, outs[-1]) for g in gathered) and all(torch.equal(o, outs[0]) for o in outs) and status == 0
+    verdict = torch.tensor([int(good)], device="cuda")
+    if rank == 0:
+        err = ((outs[0].cpu().float() - ref.float()).norm() / ref.float().norm()).item()
+        verdict *= int(err < 1e-2)
+        print(f"tp={world} stack of {NL} layers B={B} S={S}: rel_fro {err:.3e} identical_across_ranks={good} status={status}", flush=True)
+    dist.all_reduce(verdict, op=dist.ReduceOp.MIN)
+    ok = ok and bool(verdict.item())
+    torch.cuda.synchronize()
+    dist.barrier()
+    stack.close()
     dist.barrier()
     sys.stdout.flush()
     os._exit(0 if ok else 1)  # no NCCL teardown: see bench.py
