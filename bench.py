@@ -58,6 +58,9 @@ def parse_args():
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a CUDA graph")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--stack", action="store_true",
+                    help="issue the timed steps as multi-layer calls (ezb_qwen3_decode_stack / ..._tp_fused): a step is still "
+                         "one layer; at N > 1 a layer's second sum is then folded into the next layer's first kernel")
     ap.add_argument("--roofline-only", action="store_true",
                     help="run only the roofline leg (a few launches of the dominant kernel): the command an ncu capture wraps")
     ap.add_argument("--no-cross-call-pdl", action="store_true",
@@ -204,6 +207,7 @@ def workload_config(args, shape, n):
         "parallelism": f"tp{n}",
         "cache_policy": f"inputs larger than L2: steps rotate over {NUM_WEIGHT_SETS * n} weight+KV sets per GPU",
         "pdl_across_calls": not getattr(args, "no_cross_call_pdl", False),
+        "calls": "one multi-layer call per graph" if getattr(args, "stack", False) else "one call per layer",
     }
 
 
@@ -352,6 +356,25 @@ def main():
             layer(h, sets[(first + i) % nsets], out)
             h = out
 
+    if args.stack:
+        names = ("K_cache", "V_cache", "Wqkv", "Wo", "Wgu", "Wd")
+        as_layers = [dict(zip(names, wset)) for wset in sets]
+        stacks = {}  # multi-layer executors by layer count (created in the same order on every rank)
+
+        def stack_for(n):
+            if n not in stacks:
+                if tp == 1:
+                    stacks[n] = ez.get_kernel("qwen3_decode_stack", "cuda")(B, S, H, I, NH, D, n, num_kv_heads=NKV)
+                else:
+                    stacks[n] = tpm.TensorParallelDecodeStack(B, S, H, I, NH, D, NKV, n)
+            return stacks[n]
+
+        def run_steps(n, first=0):  # noqa: F811 - the multi-layer form of the loop above
+            stack_for(n)(hidden0, [as_layers[(first + i) % nsets] for i in range(n)], None, None, out=bufs[0])
+
+        def layer(hidden, wset, out):  # noqa: F811 - one-layer stack call (self-check and e2e leg)
+            return stack_for(1)(hidden, [dict(zip(names, wset))], None, None, out=out)
+
     def sync_all():
         torch.cuda.synchronize()
         if world > 1:
@@ -373,8 +396,10 @@ def main():
         unroll = max(d for d in range(1, 65) if steps % d == 0)
         try:
             graph = torch.cuda.CUDAGraph()
+            n0 = lib_.ezb_launch_count()
             with torch.cuda.graph(graph):
                 run_steps(unroll)
+            launches_per_step = (lib_.ezb_launch_count() - n0) / unroll  # what one replay launches, per step
             graph.replay()  # untimed: first replay pays graph upload
             sync_all()
         except Exception as exc:  # pragma: no cover - depends on the runtime
@@ -454,7 +479,7 @@ def main():
             "algorithmic_bytes_per_step": total_bytes,
             "frac_of_8tbs": value / 8000.0, "frac_of_measured_hbm": value / peaks["hbm_gbs"],
             "timing": f"CUDA events around {steps} steps " + (f"replayed from a CUDA graph of {unroll} steps" if graph is not None else "launched eagerly") + ", max over ranks",
-            "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": steps * launches_per_step,
+            "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": int(round(steps * launches_per_step)),
             "roofline": roofline, "cpu_baseline": cpu, "check_vs_torch_ref": check, "device_status": status,
         }
         print(json.dumps(line), flush=True)
