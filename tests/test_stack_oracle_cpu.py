@@ -57,3 +57,20 @@ def test_operator_reference_matches_the_oracle():
     want = orc.qwen3_decode_stack_ref(hid, copy.deepcopy(layers), *HEADS, cos, sin)
     assert torch.equal(got, want)
     assert op.check(got, want)
+
+
+def test_shard_stack_splits_every_layer_like_one_layer():
+    from ezops_b200 import tp as tpm
+
+    _, layers, _, _ = wl.decode_stack_inputs(SH, 2, 12, 2)
+    world = 4
+    shards = [tpm.shard_stack(layers, *HEADS, world, r) for r in range(world)]
+    for l, L in enumerate(layers):
+        for r in range(world):
+            want = tpm.shard_layer_weights(L["Wqkv"], L["Wo"], L["Wgu"], L["Wd"], *HEADS, world, r)
+            got = shards[r][l]
+            for name, w in zip(("Wqkv", "Wo", "Wgu", "Wd"), want):
+                assert torch.equal(got[name], w)
+            assert got["input_norm_w"] is L["input_norm_w"] and got["q_norm_w"] is L["q_norm_w"]  # replicated
+        assert torch.equal(torch.cat([shards[r][l]["K_cache"] for r in range(world)], dim=1), L["K_cache"])
+        assert torch.equal(torch.cat([shards[r][l]["Wo"] for r in range(world)], dim=1), L["Wo"])
