@@ -394,6 +394,9 @@ def main():
     graph = None
     if not args.no_graph:
         unroll = max(d for d in range(1, 65) if steps % d == 0)
+        if args.stack:  # the executor for `unroll` layers allocates on first use: not inside a capture
+            run_steps(unroll)
+            sync_all()
         try:
             graph = torch.cuda.CUDAGraph()
             n0 = lib_.ezb_launch_count()
