@@ -58,9 +58,12 @@ def parse_args():
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a CUDA graph")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--skip-e2e", action="store_true")
-    ap.add_argument("--stack", action="store_true",
-                    help="issue the timed steps as multi-layer calls (ezb_qwen3_decode_stack / ..._tp_fused): a step is still "
-                         "one layer; at N > 1 a layer's second sum is then folded into the next layer's first kernel")
+    ap.add_argument("--calls", choices=["auto", "layer", "stack"], default="auto",
+                    help="layer: one C call per step (the reference operator's granularity).  stack: the timed steps are "
+                         "issued as multi-layer calls (ezb_qwen3_decode_stack / ..._tp_fused); a step is still one layer, "
+                         "but at N > 1 a layer's second sum is folded into the next layer's first kernel.  auto: layer at "
+                         "N = 1, stack at N > 1 when the fused exchange applies")
+    ap.add_argument("--stack", action="store_true", help="same as --calls stack")
     ap.add_argument("--roofline-only", action="store_true",
                     help="run only the roofline leg (a few launches of the dominant kernel): the command an ncu capture wraps")
     ap.add_argument("--no-cross-call-pdl", action="store_true",
@@ -356,6 +359,10 @@ def main():
             layer(h, sets[(first + i) % nsets], out)
             h = out
 
+    if args.calls == "stack":
+        args.stack = True
+    elif args.calls == "auto" and tp > 1 and exchange == "fused":
+        args.stack = True
     if args.stack:
         names = ("K_cache", "V_cache", "Wqkv", "Wo", "Wgu", "Wd")
         as_layers = [dict(zip(names, wset)) for wset in sets]
