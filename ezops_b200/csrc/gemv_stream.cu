@@ -138,7 +138,8 @@ __device__ __forceinline__ void load_x8(const bf16* srow, int i, uint32_t (&w)[4
 template <bool PERMUTE32, bool LINK, bool SINGLE>
 __device__ __forceinline__ void stage_activations(const GemvParams& p, bf16* xs, int xs_stride, float* scratch, int ct,
                                                   int cw, int lane) {
-    constexpr int U = 8;  // independent 16-byte loads in flight per thread
+    // independent 16-byte loads in flight per thread (16 spilled registers in the multi-row instances and was slower)
+    constexpr int U = 8;
     const int nvec = p.K / 8;
     // Rows are staged side by side: the consumer warps are split into groups of `wpr` warps, one
     // group per batch row, so a batch of 8 rows costs the same number of L2 round trips and
@@ -201,37 +202,55 @@ __device__ __forceinline__ void stage_activations(const GemvParams& p, bf16* xs,
                     store_x4<PERMUTE32>(srow, h, w2);
                 }
             }
+        } else if (active && p.prologue == PRO_ADD_RMSNORM) {
+            constexpr int UA = 8;  // the fp32 term triples the registers per vector
+            for (int base = 0; base < nvec; base += UA * nthr) {
+                uint4 raw[UA];
+                float4 add0[UA], add1[UA];
+#pragma unroll
+                for (int u = 0; u < UA; ++u) {
+                    const int i = base + u * nthr + sub;
+                    if (i < nvec) {
+                        raw[u] = *reinterpret_cast<const uint4*>(xrow + i * 8);
+                        add0[u] = *reinterpret_cast<const float4*>(p.x_add + (long long)b * p.ldadd + i * 8);
+                        add1[u] = *reinterpret_cast<const float4*>(p.x_add + (long long)b * p.ldadd + i * 8 + 4);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < UA; ++u) {
+                    const int i = base + u * nthr + sub;
+                    if (i < nvec) {
+                        uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+                        const float add[8] = {add0[u].x, add0[u].y, add0[u].z, add0[u].w, add1[u].x, add1[u].y, add1[u].z, add1[u].w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            w[e] = pack_bf16(bf16_lo(w[e]) + round_bf16(add[2 * e]), bf16_hi(w[e]) + round_bf16(add[2 * e + 1]));
+                        if (blockIdx.x == 0 && p.x_sum_out)
+                            *reinterpret_cast<uint4*>(p.x_sum_out + (long long)b * p.ldsum + i * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float lo = bf16_lo(w[e]), hi = bf16_hi(w[e]);
+                            ssq += lo * lo + hi * hi;
+                        }
+                        store_x8<PERMUTE32>(srow, i, w);
+                    }
+                }
+            }
         } else if (active) {
             for (int base = 0; base < nvec; base += U * nthr) {
                 // all loads of the batch are issued before any of them is used, so the
                 // L2 latency is paid once per batch and not once per vector
                 uint4 raw[U];
-                float4 add0[U], add1[U];
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
                     const int i = base + u * nthr + sub;
-                    if (i < nvec) {
-                        raw[u] = *reinterpret_cast<const uint4*>(xrow + i * 8);
-                        if (p.prologue == PRO_ADD_RMSNORM) {
-                            add0[u] = *reinterpret_cast<const float4*>(p.x_add + (long long)b * p.ldadd + i * 8);
-                            add1[u] = *reinterpret_cast<const float4*>(p.x_add + (long long)b * p.ldadd + i * 8 + 4);
-                        }
-                    }
+                    if (i < nvec) raw[u] = *reinterpret_cast<const uint4*>(xrow + i * 8);
                 }
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
                     const int i = base + u * nthr + sub;
                     if (i < nvec) {
-                        uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
-                        if (p.prologue == PRO_ADD_RMSNORM) {
-                            const float add[8] = {add0[u].x, add0[u].y, add0[u].z, add0[u].w,
-                                                  add1[u].x, add1[u].y, add1[u].z, add1[u].w};
-#pragma unroll
-                            for (int e = 0; e < 4; ++e)
-                                w[e] = pack_bf16(bf16_lo(w[e]) + round_bf16(add[2 * e]), bf16_hi(w[e]) + round_bf16(add[2 * e + 1]));
-                            if (blockIdx.x == 0 && p.x_sum_out)
-                                *reinterpret_cast<uint4*>(p.x_sum_out + (long long)b * p.ldsum + i * 8) = make_uint4(w[0], w[1], w[2], w[3]);
-                        }
+                        const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
                             const float lo = bf16_lo(w[e]), hi = bf16_hi(w[e]);
