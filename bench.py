@@ -333,8 +333,7 @@ def main():
         # batch allows it, NCCL all-reduce between the three local parts otherwise.
         exchange = args.exchange
         if exchange == "auto":
-            fits = all(B * (k + 32) * 2 <= 72 * 1024 for k in (H, NH // tp * D, I // tp))
-            exchange = "fused" if B <= 8 and fits else "nccl"
+            exchange = "fused"  # batch <= 8: inside the small-batch kernel; up to 64: row kernel + tensor-core kernel
         lay = tpm.TensorParallelDecodeLayer(B, S, H, I, NH, D, NKV, exchange=exchange)
         launches_per_step = 6 if exchange == "fused" else 7
 

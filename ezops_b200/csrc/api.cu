@@ -735,10 +735,15 @@ static int make_tp_link(TpLink& base, void* const* comm_bases_host, int world, i
     return EZB_OK;
 }
 
-static int check_tp_fused_shape(int B, int H, int I_local, int NH_local, int D) {
-    EZB_REQUIRE_SHAPE(gemv_small_batch_eligible(B, H) && gemv_small_batch_eligible(B, NH_local * D) &&
-                          gemv_small_batch_eligible(B, I_local),
-                      "the fused exchange needs a batch small enough for the resident-activation kernel");
+static int check_tp_fused_shape(int B, int H, int I_local, int NH_local, int NKV_local, int D) {
+    // every projection must run a kernel that knows the exchange: the small-batch kernel, or (batch >= 2)
+    // the tensor-core kernel with the row kernel in front
+    auto covered = [&](int K, int N, bool pair) {
+        return gemv_small_batch_eligible(B, K) || (tuning(EZB_TUNE_TC) != 0 && gemm_tc_supported(B, K) && gemm_tc_fits(N, pair));
+    };
+    EZB_REQUIRE_SHAPE(covered(H, (NH_local + 2 * NKV_local) * D, false) && covered(NH_local * D, H, false) &&
+                          covered(H, I_local, true) && covered(I_local, H, false),
+                      "no kernel with the fused exchange covers this batch and these sizes");
     return EZB_OK;
 }
 
@@ -757,12 +762,12 @@ static int run_layer_tp_fused(const bf16* x_prev, bool gather_prev, bf16* layer_
     const bf16* hid = gather_prev ? layer_in : x_prev;
     {   // QKV projection (norm prologue; gathers the previous layer's second sum when there is one)
         GemvArgs g;
+        g.tc_workspace = w.tc, g.xn_scratch = w.xn;
         g.W0 = Wqkv, g.ldw = H, g.N = rows, g.K = H, g.B = B;
         g.x = x_prev, g.ldx = H;
         g.norm_w = ex.input_norm_w;
         g.eps = eps, g.prologue = gather_prev ? PRO_ADD_RMSNORM : PRO_RMSNORM, g.epilogue = EPI_STORE;
         g.out = w.qkv, g.ldout = rows;
-        g.xn_scratch = w.xn;
         g.trace_id = 1;
         if (gather_prev) {
             g.x_sum_out = layer_in, g.ldsum = H;
@@ -788,6 +793,7 @@ static int run_layer_tp_fused(const bf16* x_prev, bool gather_prev, bf16* layer_
     }
     {   // o_proj: partial -> inbox 0 of every rank; also opens the next epoch of inbox 1
         GemvArgs g;
+        g.tc_workspace = w.tc, g.xn_scratch = w.xn;
         g.W0 = Wo, g.ldw = Q, g.N = H, g.K = Q, g.B = B;
         g.x = w.attn_out, g.ldx = Q;
         g.epilogue = EPI_PUSH_F32, g.ldout = H;
@@ -798,6 +804,7 @@ static int run_layer_tp_fused(const bf16* x_prev, bool gather_prev, bf16* layer_
     }
     {   // gate/up: x2 = layer input + sum(inbox 0), norm, SwiGLU
         GemvArgs g;
+        g.tc_workspace = w.tc, g.xn_scratch = w.xn;
         g.W0 = wgu, g.W1 = wgu + (size_t)I_local * H, g.ldw = H, g.N = I_local, g.K = H, g.B = B;
         g.x = hid, g.ldx = H;
         g.x_sum_out = x2_out, g.ldsum = H;
@@ -811,6 +818,7 @@ static int run_layer_tp_fused(const bf16* x_prev, bool gather_prev, bf16* layer_
     }
     {   // down: partial -> inbox 1 of every rank; opens the next epoch of inbox 0
         GemvArgs g;
+        g.tc_workspace = w.tc, g.xn_scratch = w.xn;
         g.W0 = Wd, g.ldw = I_local, g.N = H, g.K = I_local, g.B = B;
         g.x = w.h, g.ldx = I_local;
         g.epilogue = EPI_PUSH_F32, g.ldout = H;
@@ -842,7 +850,7 @@ int ezb_qwen3_decode_layer_tp_fused(const void* hidden, void* K_cache, void* V_c
     TpLink base;
     if (int rc = make_tp_link(base, comm_bases_host, world, rank, B, H)) return rc;
     if (int rc = check_layer_args(B, S, H, I_local, NH_local, NKV_local, D)) return rc;
-    if (int rc = check_tp_fused_shape(B, H, I_local, NH_local, D)) return rc;
+    if (int rc = check_tp_fused_shape(B, H, I_local, NH_local, NKV_local, D)) return rc;
     EZB_REQUIRE(aligned16(hidden) && aligned16(K_cache) && aligned16(V_cache) && aligned16(Wqkv_local) &&
                     aligned16(Wo_local) && aligned16(Wgu_local) && aligned16(Wd_local) && aligned16(out),
                 "pointers must be 16-byte aligned");
@@ -876,7 +884,7 @@ int ezb_qwen3_decode_stack_tp_fused(const void* hidden, void* out, const ezb_lay
     TpLink base;
     if (int rc = make_tp_link(base, comm_bases_host, world, rank, B, H)) return rc;
     if (int rc = check_layer_args(B, S, H, I_local, NH_local, NKV_local, D)) return rc;
-    if (int rc = check_tp_fused_shape(B, H, I_local, NH_local, D)) return rc;
+    if (int rc = check_tp_fused_shape(B, H, I_local, NH_local, NKV_local, D)) return rc;
     EZB_REQUIRE(aligned16(hidden) && aligned16(out) && aligned16(rope_cos) && aligned16(rope_sin), "pointers must be 16-byte aligned");
     for (int l = 0; l < n_layers; ++l) {
         const ezb_layer_t& L = layers_local[l];

@@ -58,6 +58,7 @@ struct TcParams {
     unsigned int* status;
     Trace trace;
     int trace_id;
+    TpLink link;  // fused tensor-parallel exchange (world 0: none); only the push side lives in this kernel
 };
 
 // ---- tcgen05 / TMA wrappers -------------------------------------------------
@@ -130,7 +131,8 @@ __device__ __forceinline__ int tc_owner(long long T, int G, long long u) {
     return c;
 }
 
-template <int NB>
+// LINK: the instance whose epilogue pushes its fp32 results into the peers' inboxes (see TpLink).
+template <int NB, bool LINK>
 __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap mapW0, const __grid_constant__ CUtensorMap mapW1,
                const __grid_constant__ CUtensorMap mapX, const TcParams p) {
@@ -312,6 +314,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapW0, const __grid_constant_
         const int et = (warp - 2) * 32 + lane;
         pdl_wait();
         trace_mark(trec, 3);
+        const unsigned int push_epoch = (LINK && p.link.world > 0 && p.link.push_inbox >= 0) ? tp_next_epoch(p.link, p.link.push_inbox) : 0u;
         const int nseg = *nseg_s;
         for (int seg = 0; seg < nseg; ++seg) {
             const int tile = segs[4 * seg], kb0 = segs[4 * seg + 1], kb1 = segs[4 * seg + 2];
@@ -388,6 +391,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapW0, const __grid_constant_
                                     *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(p.out) + (long long)(b0 + j) * p.ldout + n) =
                                         make_uint2(pack_bf16(bf16_lo(res[j].x) + round_bf16(acc[j].x), bf16_hi(res[j].x) + round_bf16(acc[j].y)),
                                                    pack_bf16(bf16_lo(res[j].y) + round_bf16(acc[j].z), bf16_hi(res[j].y) + round_bf16(acc[j].w)));
+                        } else if (LINK && p.epilogue == EPI_PUSH_F32) {
+#pragma unroll
+                            for (int j = 0; j < NBG; ++j)
+                                if (b0 + j < p.B) {
+                                    const long long e = (long long)(b0 + j) * p.ldout + n;
+                                    tp_push(p.link, e, acc[j].x, push_epoch), tp_push(p.link, e + 1, acc[j].y, push_epoch);
+                                    tp_push(p.link, e + 2, acc[j].z, push_epoch), tp_push(p.link, e + 3, acc[j].w, push_epoch);
+                                }
                         } else if (p.epilogue == EPI_STORE_F32) {
 #pragma unroll
                             for (int j = 0; j < NBG; ++j)
@@ -437,6 +448,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapW0, const __grid_constant_
                             if (b < p.B)
                                 reinterpret_cast<bf16*>(p.out)[(long long)b * p.ldout + n] =
                                     __float2bfloat16_rn(res[b] + round_bf16(v[b]));
+                    } else if (LINK && p.epilogue == EPI_PUSH_F32) {
+#pragma unroll
+                        for (int b = 0; b < NB; ++b)
+                            if (b < p.B) tp_push(p.link, (long long)b * p.ldout + n, v[b], push_epoch);
                     } else if (p.epilogue == EPI_STORE_F32) {
 #pragma unroll
                         for (int b = 0; b < NB; ++b)
@@ -470,6 +485,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapW0, const __grid_constant_
             }
         }
         trace_mark(trec, 5);
+        if (LINK && p.link.world > 0 && p.link.bump_inbox >= 0 && blockIdx.x == 0 && et == 0) tp_bump(p.link);
     }
 
     tc_fence_before();
@@ -524,10 +540,10 @@ size_t gemm_tc_workspace_bytes(int B, int N, bool pair) {
     return kTcCounterBytes + (size_t)sm_count() * 2 * NB * kTcRows * sizeof(float);
 }
 
-template <int NB>
+template <int NB, bool LINK>
 static cudaError_t launch_tc_instance(const CUtensorMap& m0, const CUtensorMap& m1, const CUtensorMap& mx, TcParams& p,
                                       int grid, cudaStream_t stream) {
-    auto kernel = gemm_tc_kernel<NB>;
+    auto kernel = gemm_tc_kernel<NB, LINK>;
     constexpr size_t stage = kTcABytes + (size_t)NB * kTcBlockK * 2;
     const size_t tail = 256 + (size_t)64 * (NB + 1) * sizeof(float) + (4 * kTcMaxSegs + 4) * sizeof(int);
     const size_t cap = (size_t)max_smem_optin();
@@ -565,6 +581,8 @@ cudaError_t launch_gemm_tc(const GemvArgs& a, const bf16* x, long long ldx, void
     if (!p.status) return cudaErrorUnknown;
     p.trace = trace_handle();
     p.trace_id = a.trace_id;
+    p.link = a.link;
+    if (a.link.world > 0 && (a.link.gather_inbox >= 0 || pair)) return cudaErrorNotSupported;  // only the push side lives here
 
     alignas(64) CUtensorMap m0, m1, mx;
     const int box_rows = pair ? 64 : 128;
@@ -575,10 +593,17 @@ cudaError_t launch_gemm_tc(const GemvArgs& a, const bf16* x, long long ldx, void
     long long T = (long long)p.tiles * p.kblocks;
     int grid = sm_count();
     if (grid > T) grid = (int)T;
+    if (a.link.world > 0) {
+        switch (NB) {
+            case 16: return launch_tc_instance<16, true>(m0, m1, mx, p, grid, stream);
+            case 32: return launch_tc_instance<32, true>(m0, m1, mx, p, grid, stream);
+            default: return launch_tc_instance<64, true>(m0, m1, mx, p, grid, stream);
+        }
+    }
     switch (NB) {
-        case 16: return launch_tc_instance<16>(m0, m1, mx, p, grid, stream);
-        case 32: return launch_tc_instance<32>(m0, m1, mx, p, grid, stream);
-        default: return launch_tc_instance<64>(m0, m1, mx, p, grid, stream);
+        case 16: return launch_tc_instance<16, false>(m0, m1, mx, p, grid, stream);
+        case 32: return launch_tc_instance<32, false>(m0, m1, mx, p, grid, stream);
+        default: return launch_tc_instance<64, false>(m0, m1, mx, p, grid, stream);
     }
 }
 

@@ -877,15 +877,25 @@ cudaError_t launch_gemv(const GemvArgs& a, cudaStream_t stream) {
     p.trace_id = a.trace_id;
     p.link = a.link;
 
-    if (a.link.world > 0 && !rows8) return cudaErrorNotSupported;  // the fused exchange lives in the small-batch kernel
     const bool use_tc = !rows8 && a.tc_workspace && tuning(EZB_TUNE_TC) != 0 && gemm_tc_supported(a.B, a.K) && gemm_tc_fits(a.N, pair);
+    // The fused tensor-parallel exchange lives in the small-batch kernel (gather and push) and, for larger
+    // batches, in the row kernel (gather) and the tensor-core kernel (push); the general fallback has none.
+    const bool linked = a.link.world > 0;
+    const bool gathers = linked && a.link.gather_inbox >= 0;
+    if (linked && !rows8 && !use_tc) return cudaErrorNotSupported;
+    GemvArgs tc_args = a;
     if ((use_tc || !pl.xres) && a.prologue != PRO_NONE) {
         // The activation block is not resident in this path: run the prologue as
         // its own (tiny) kernel into the scratch rows, then stream those.
         RowPrepArgs rp;
         rp.x = a.x, rp.ldx = a.ldx;
-        rp.add = (a.prologue == PRO_ADD_RMSNORM) ? a.x_add : nullptr, rp.ldadd = a.ldadd;
+        rp.add = (a.prologue == PRO_ADD_RMSNORM && !gathers) ? a.x_add : nullptr, rp.ldadd = a.ldadd;
         rp.sum_out = (a.prologue == PRO_ADD_RMSNORM) ? a.x_sum_out : nullptr, rp.ldsum = a.ldsum;
+        if (gathers) {  // the term to add comes from the inbox; the projection itself then has nothing to gather
+            rp.link = a.link, rp.link.push_inbox = -1, rp.link.bump_inbox = -1;
+            tc_args.link.gather_inbox = -1;
+            if (tc_args.link.push_inbox < 0 && tc_args.link.bump_inbox < 0) tc_args.link.world = 0;
+        }
         rp.w = a.norm_w;
         rp.y = a.xn_scratch, rp.ldy = a.K;
         rp.rows = a.B, rp.dim = a.K, rp.eps = a.eps, rp.normalize = 1;
@@ -894,7 +904,7 @@ cudaError_t launch_gemv(const GemvArgs& a, cudaStream_t stream) {
         p.x = a.xn_scratch, p.ldx = a.K;
         p.prologue = PRO_NONE;
     }
-    if (use_tc) return launch_gemm_tc(a, p.x, p.ldx, a.tc_workspace, stream);
+    if (use_tc) return launch_gemm_tc(tc_args, p.x, p.ldx, a.tc_workspace, stream);
 
     if (rows8) {
         const int which = (pair ? 4 : 0) | (a.link.world > 0 ? 2 : 0) | (a.B == 1 ? 1 : 0);

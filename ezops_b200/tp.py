@@ -207,7 +207,7 @@ def shard_stack(layers, num_heads: int, num_kv_heads: int, head_dim: int, tp: in
 class TensorParallelDecodeStack(TensorParallelDecodeLayer):
     """All layers of a decoder stack on this rank's shards in one call, the sums over ranks fused
     into the kernels (``ezb_qwen3_decode_stack_tp_fused``).  ``__call__(hidden, layers_local, cos,
-    sin)``; every rank returns the same [B, H] output.  Batch <= 8 (the fused exchange's limit)."""
+    sin)``; every rank returns the same [B, H] output."""
 
     def __init__(self, batch, seq_len, hidden_size, intermediate_size, num_heads, head_dim, num_kv_heads, num_layers, group=None):
         super().__init__(batch, seq_len, hidden_size, intermediate_size, num_heads, head_dim, num_kv_heads, group=group,

@@ -273,9 +273,11 @@ int ezb_hbm_stream(int op, const void* b, const void* c, void* a, long long n_ve
  * its own inbox (bounded, about one second, then records a device fault) until
  * every word carries the expected epoch and adds the slots in rank order, so
  * all ranks get identical bits.  Ranks must make the same sequence of calls; a
- * buffer serves one stream.  Limited to batches for which every projection
- * runs the resident-activation kernel (EZB_ERR_UNSUPPORTED_SHAPE
- * otherwise; use the three-part form with NCCL then). */
+ * buffer serves one stream.  Up to batch 8 the gather and the push live in the
+ * resident-activation kernel; for larger batches the row kernel in front of a
+ * projection gathers and the tensor-core kernel's epilogue pushes.  Shapes that
+ * neither covers return EZB_ERR_UNSUPPORTED_SHAPE (use the three-part form with
+ * NCCL then). */
 size_t ezb_tp_comm_bytes(int B, int H);
 int ezb_tp_comm_alloc(size_t bytes, void** out_host);
 int ezb_tp_comm_free(void* buffer);

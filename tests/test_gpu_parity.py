@@ -472,7 +472,7 @@ def test_tp_parts_sum_to_the_layer(ez, tp, batch):
 
 
 @pytest.mark.parametrize("poll_all", [0, 1])
-@pytest.mark.parametrize("batch", [1, 4])
+@pytest.mark.parametrize("batch", [1, 4, 8, 16, 40])
 def test_tp_fused_exchange_world_one_matches_the_layer(ez, batch, poll_all):
     """The fused exchange with one rank pushes into its own inbox: same bits as the
     single-GPU layer, on every one of several calls in a row (the epochs advance)."""
@@ -501,7 +501,7 @@ def test_tp_fused_exchange_rejects_large_batches(ez):
     from ezops_b200 import tp as tpm
     from ezops_b200 import workloads as wl
 
-    sh, S, batch = wl.QWEN3_VL_2B, 300, 16
+    sh, S, batch = wl.QWEN3_VL_2B, 300, 65
     data = wl.decode_layer_inputs(sh, batch, S)
     lay = tpm.TensorParallelDecodeLayer(batch, S, sh.hidden, sh.inter, sh.num_heads, sh.head_dim, sh.num_kv_heads, exchange="fused")
     try:

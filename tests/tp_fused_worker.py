@@ -25,7 +25,8 @@ def main() -> int:
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     ok = True
-    for sh, B, S in [(wl.QWEN3_VL_2B, 1, 700), (wl.QWEN3_8B, 3, 1025)]:
+    # batch 1 and 3: gather and push inside the small-batch kernel; batch 16: row kernel + tensor-core kernel
+    for sh, B, S in [(wl.QWEN3_VL_2B, 1, 700), (wl.QWEN3_8B, 3, 1025), (wl.QWEN3_VL_2B, 16, 400)]:
         hidden, K0, V0, Wqkv, Wo, Wgu, Wd = wl.decode_layer_inputs(sh, B, S)
         heads = (sh.num_heads, sh.num_kv_heads, sh.head_dim)
         ref = orc.qwen3_dense_decode_ref(hidden, K0.clone(), V0.clone(), Wqkv, Wo, Wgu, Wd, *heads) if rank == 0 else None
