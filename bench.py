@@ -333,7 +333,9 @@ def main():
         # batch allows it, NCCL all-reduce between the three local parts otherwise.
         exchange = args.exchange
         if exchange == "auto":
-            exchange = "fused"  # batch <= 8: inside the small-batch kernel; up to 64: row kernel + tensor-core kernel
+            # the fused exchange wins where a layer is latency-bound (batch <= 8); above that the peer stores of
+            # the tensor-core epilogue were measured slower than NCCL's all-reduce
+            exchange = "fused" if B <= 8 else "nccl"
         lay = tpm.TensorParallelDecodeLayer(B, S, H, I, NH, D, NKV, exchange=exchange)
         launches_per_step = 6 if exchange == "fused" else 7
 

@@ -36,7 +36,7 @@ TUNE = {
     "l2_prefetch_kb": 10,
     "gemv_window": 11,
     "l2_prefetch_attn_kb": 12,
-    "tc": 13, "attn_waves_uniform": 14, "tp_poll_all": 15,
+    "tc": 13, "attn_waves_uniform": 14, "tp_poll_all": 15, "tp_pull": 16,
 }
 
 # name -> (restype, argtypes); every symbol include/ezb200.h declares

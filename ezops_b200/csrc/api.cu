@@ -97,11 +97,12 @@ static const int kTuningDefaults[EZB_TUNE_COUNT] = {
     1,    // EZB_TUNE_TC
     3,    // EZB_TUNE_ATTN_WAVES_UNIFORM
     0,    // EZB_TUNE_TP_POLL_ALL
+    0,    // EZB_TUNE_TP_PULL
 };
 static const char* kTuningEnv[EZB_TUNE_COUNT] = {
     "EZB_TUNE_PDL",          "EZB_TUNE_GEMV_SMEM_KB",   "EZB_TUNE_GEMV_PREFETCH", "EZB_TUNE_GEMV_CTAS_PER_SM",
     "EZB_TUNE_ATTN_MIN_CHUNK", "EZB_TUNE_ATTN_WAVES", "EZB_TUNE_GEMV_KC", "EZB_TUNE_GEMV_ROWS8", "EZB_TUNE_PDL_ACROSS_CALLS", "EZB_TUNE_L2_PREFETCH", "EZB_TUNE_L2_PREFETCH_KB", "EZB_TUNE_GEMV_WINDOW", "EZB_TUNE_L2_PREFETCH_ATTN_KB", "EZB_TUNE_TC",
-    "EZB_TUNE_ATTN_WAVES_UNIFORM", "EZB_TUNE_TP_POLL_ALL",
+    "EZB_TUNE_ATTN_WAVES_UNIFORM", "EZB_TUNE_TP_POLL_ALL", "EZB_TUNE_TP_PULL",
 };
 
 static void tuning_init() {
@@ -727,7 +728,9 @@ static int make_tp_link(TpLink& base, void* const* comm_bases_host, int world, i
     EZB_REQUIRE(world >= 1 && world <= kTpSlots && rank >= 0 && rank < world, "world must be 1..8 and rank inside it");
     for (int w = 0; w < world; ++w) EZB_REQUIRE(comm_bases_host[w] && aligned16(comm_bases_host[w]), "bad comm buffer pointer");
     const int poll_mode = tuning(EZB_TUNE_TP_POLL_ALL);
-    base = {world, rank, {}, {}, (long long)B * H, -1, -1, -1, poll_mode == 1 || (poll_mode == 0 && world > 2) ? 1 : 0};
+    const int pull_mode = tuning(EZB_TUNE_TP_PULL);
+    base = {world, rank, {}, {}, (long long)B * H, -1, -1, -1, poll_mode == 1 || (poll_mode == 0 && world > 2) ? 1 : 0,
+            pull_mode == 1 ? 1 : 0};
     for (int r = 0; r < world; ++r) {
         base.ctrl_peer[r] = static_cast<unsigned int*>(comm_bases_host[r]);
         base.inbox_peer[r] = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(comm_bases_host[r]) + kTpCtrlBytes);

@@ -47,15 +47,18 @@ static constexpr long long kWaitLimitCycles = 2000000000LL;
 //   holds the partial [B, H] that rank r pushed, every cell = {fp32 value in
 //   the low half, epoch in the high half}.
 // A producer stores each fp32 output, tagged with epoch+1, into slot `rank` of
-// the chosen inbox of EVERY rank: one 64-bit peer store per value over NVLink,
+// the chosen inbox of EVERY rank: one plain 64-bit peer store per value over NVLink,
 // single-copy atomic, no fence and no flag behind it.  A consumer polls the cells
 // of its own inbox (bounded) until their tag shows epoch+1 and adds the values
 // in rank order, so every rank computes the same bits; a value is usable the
 // moment its own store lands.  Epochs live on the device and are advanced by a
-// later kernel of the chain, so a captured CUDA graph can be replayed.  Two
-// inboxes alternate (after o_proj / after down_proj); a rank can only push to an
-// inbox again after every peer has consumed its previous content, because the
-// pushes and polls of the other inbox lie in between.
+// later kernel of the chain, so a captured CUDA graph can be replayed.
+// Two directions.  Push (the default): the producer stores into slot `rank` on every rank and
+// consumers poll their own memory, so a value crosses NVLink once per peer however many CTAs
+// read it.  Pull (EZB_TUNE_TP_PULL): the producer writes slot `rank` of its OWN buffer only and
+// consumers poll slot w of rank w's buffer with peer loads.  Measured on two GPUs at batch 32-64
+// pull was slower than push, and both slower than NCCL there (see the tensor-parallel notes of
+// the design document); at batch <= 8 push is the fast one.
 // ---------------------------------------------------------------------------
 struct TpLink {
     int world;  // 0: no fused exchange
@@ -67,6 +70,7 @@ struct TpLink {
     int gather_inbox;  // -1 or the inbox whose slots this kernel's prologue sums
     int bump_inbox;    // -1 or the inbox whose epoch this kernel advances
     int poll_all;      // 1: the gathering prologue polls all ranks together, 4 elements per thread and step
+    int pull;          // 1: a producer writes only its own buffer and consumers read every rank's buffer over NVLink
 };
 static constexpr int kTpEpoch = 0;
 static constexpr int kTpCtrlBytes = 256;
@@ -79,10 +83,23 @@ __device__ __forceinline__ unsigned long long* tp_slot(const TpLink& l, int on_r
 __device__ __forceinline__ unsigned int tp_next_epoch(const TpLink& l, int inbox) {
     return l.ctrl_peer[l.rank][kTpEpoch + inbox] + 1u;
 }
+// The store is a plain (weak) 64-bit store: value and tag travel in one naturally aligned word, so
+// nothing has to be ordered around it, and a weak store is posted - a thread can have many in flight.
+// (Measured: with st.relaxed.sys a thread's stores to a peer went out one NVLink round trip at a time,
+// 64 of them cost the tensor-core epilogue 30 us.)  The consumer polls with strong system-scope loads.
 __device__ __forceinline__ void tp_push(const TpLink& l, long long elem, float v, unsigned int epoch) {
     const unsigned long long cell = ((unsigned long long)epoch << 32) | (unsigned long long)__float_as_uint(v);
     for (int w = 0; w < l.world; ++w)
-        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(tp_slot(l, w, l.push_inbox, l.rank) + elem), "l"(cell) : "memory");
+        if (!l.pull || w == l.rank)
+            asm volatile("st.weak.global.u64 [%0], %1;" ::"l"(tp_slot(l, w, l.push_inbox, l.rank) + elem), "l"(cell) : "memory");
+}
+// Two neighbouring cells (elem even) in one 16-byte store; each 64-bit half is a cell of its own.
+__device__ __forceinline__ void tp_push2(const TpLink& l, long long elem, float v0, float v1, unsigned int epoch) {
+    const unsigned long long c0 = ((unsigned long long)epoch << 32) | (unsigned long long)__float_as_uint(v0);
+    const unsigned long long c1 = ((unsigned long long)epoch << 32) | (unsigned long long)__float_as_uint(v1);
+    for (int w = 0; w < l.world; ++w)
+        if (!l.pull || w == l.rank)
+            asm volatile("st.weak.global.v2.u64 [%0], {%1, %2};" ::"l"(tp_slot(l, w, l.push_inbox, l.rank) + elem), "l"(c0), "l"(c1) : "memory");
 }
 // Called by exactly one thread of the grid, anywhere in the kernel.
 __device__ __forceinline__ void tp_bump(const TpLink& l) { l.ctrl_peer[l.rank][kTpEpoch + l.bump_inbox] += 1u; }
@@ -104,7 +121,7 @@ __device__ __forceinline__ bool tp_gather(const TpLink& l, unsigned int epoch, l
 #pragma unroll
             for (int g = 0; g < G; ++g)
                 if (pending & (1u << g)) {
-                    const unsigned long long* src = tp_slot(l, l.rank, l.gather_inbox, w0 + g) + elem;
+                    const unsigned long long* src = tp_slot(l, l.pull ? w0 + g : l.rank, l.gather_inbox, w0 + g) + elem;
 #pragma unroll
                     for (int q = 0; q < E / 2; ++q)
                         asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];"

@@ -376,6 +376,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapW0, const __grid_constant_
                         acc[j].x += t.x, acc[j].y += t.y, acc[j].z += t.z, acc[j].w += t.w;
                     }
                 }
+                if (LINK && !p.pair && p.epilogue == EPI_PUSH_F32) {
+                    // A lane holds 4 consecutive rows; stored as they are, a warp's 64-bit peer stores would
+                    // be 32 bytes apart (one NVLink transaction each: measured 30 us per tile).  Shuffle so
+                    // that lane L owns rows 2L, 2L+1 (then 64+2L, 64+2L+1): 512 contiguous bytes per store.
+                    const int src = lane >> 1;
+                    const bool odd = lane & 1;
+#pragma unroll
+                    for (int j = 0; j < NBG; ++j) {
+#pragma unroll
+                        for (int half = 0; half < 2; ++half) {
+                            const int s2 = src + half * 16;
+                            const float ax = __shfl_sync(0xffffffffu, acc[j].x, s2), ay = __shfl_sync(0xffffffffu, acc[j].y, s2);
+                            const float az = __shfl_sync(0xffffffffu, acc[j].z, s2), aw = __shfl_sync(0xffffffffu, acc[j].w, s2);
+                            if (b0 + j < p.B && tile * kTcRows + half * 64 + 2 * lane < p.N)
+                                tp_push2(p.link, (long long)(b0 + j) * p.ldout + tile * kTcRows + half * 64 + 2 * lane,
+                                         odd ? az : ax, odd ? aw : ay, push_epoch);
+                        }
+                    }
+                    continue;
+                }
                 if (!p.pair) {
                     const int n = tile * kTcRows + r4;
                     if (n < p.N) {
@@ -391,14 +411,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapW0, const __grid_constant_
                                     *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(p.out) + (long long)(b0 + j) * p.ldout + n) =
                                         make_uint2(pack_bf16(bf16_lo(res[j].x) + round_bf16(acc[j].x), bf16_hi(res[j].x) + round_bf16(acc[j].y)),
                                                    pack_bf16(bf16_lo(res[j].y) + round_bf16(acc[j].z), bf16_hi(res[j].y) + round_bf16(acc[j].w)));
-                        } else if (LINK && p.epilogue == EPI_PUSH_F32) {
-#pragma unroll
-                            for (int j = 0; j < NBG; ++j)
-                                if (b0 + j < p.B) {
-                                    const long long e = (long long)(b0 + j) * p.ldout + n;
-                                    tp_push(p.link, e, acc[j].x, push_epoch), tp_push(p.link, e + 1, acc[j].y, push_epoch);
-                                    tp_push(p.link, e + 2, acc[j].z, push_epoch), tp_push(p.link, e + 3, acc[j].w, push_epoch);
-                                }
                         } else if (p.epilogue == EPI_STORE_F32) {
 #pragma unroll
                             for (int j = 0; j < NBG; ++j)

@@ -65,7 +65,8 @@ typedef struct CUstream_st* ezb_stream_t; /* same type as cudaStream_t */
 #define EZB_TUNE_TC 13              /* 1: batched projections run on tcgen05 tensor cores (default 1)                   */
 #define EZB_TUNE_ATTN_WAVES_UNIFORM 14 /* as ATTN_WAVES, used when all rows have the same length (default 3)    */
 #define EZB_TUNE_TP_POLL_ALL 15       /* fused exchange prologue: 0 = by world size (all ranks at once when > 2), 1 = always, 2 = never */
-#define EZB_TUNE_COUNT 16
+#define EZB_TUNE_TP_PULL 16           /* fused exchange direction: 0 = push (default), 1 = pull (consumers read the peers' buffers) */
+#define EZB_TUNE_COUNT 17
 
 int ezb_version(void);
 const char* ezb_strerror(int code);
