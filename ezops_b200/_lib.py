@@ -65,11 +65,11 @@ SIGNATURES = {
     "ezb_qwen3_decode_layer_tp_ffn": (c_int, [c_void_p] * 7 + [c_size_t] + [c_int] * 3 + [c_float, c_void_p]),
     "ezb_residual_add_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "ezb_qwen3_decode_stack_workspace_bytes": (c_size_t, [c_int] * 7),
-    "ezb_qwen3_decode_stack": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_size_t]
+    "ezb_qwen3_decode_stack": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_size_t]
                                + [c_int] * 7 + [c_float, c_void_p]),
     "ezb_qwen3_decode_stack_tp_fused_workspace_bytes": (c_size_t, [c_int] * 7),
-    "ezb_qwen3_decode_stack_tp_fused": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_size_t,
-                                                POINTER(c_void_p)] + [c_int] * 9 + [c_float, c_void_p]),
+    "ezb_qwen3_decode_stack_tp_fused": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                                c_size_t, POINTER(c_void_p)] + [c_int] * 9 + [c_float, c_void_p]),
     "ezb_launch_count": (ctypes.c_ulonglong, []),
     "ezb_hbm_stream": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_float, c_int, c_int, c_void_p]),
     "ezb_tp_comm_bytes": (c_size_t, [c_int, c_int]),

@@ -274,6 +274,8 @@ struct LayerExtras {
     const bf16* rope_cos = nullptr;
     const bf16* rope_sin = nullptr;
     const bf16* next_Wqkv = nullptr;
+    const int* seq_lens = nullptr;  // per-row valid lengths (device); the new token goes to slot len-1
+    int rope_by_len = 0;            // rope_cos / rope_sin are table bases indexed by that slot
 };
 static const LayerExtras kPlainLayer = {};
 
@@ -307,6 +309,7 @@ static cudaError_t launch_qkv_and_attention(const bf16* hidden, bf16* Kc, bf16* 
     a.K_cache_w = Kc, a.V_cache_w = Vc;
     a.eps = eps;
     a.q_norm_w = ex.q_norm_w, a.k_norm_w = ex.k_norm_w, a.rope_cos = ex.rope_cos, a.rope_sin = ex.rope_sin;
+    a.seq_lens = ex.seq_lens, a.rope_by_len = ex.rope_by_len;
     // attention is latency-bound at small batch: let HBM stream the output projection meanwhile
     if ((size_t)H * NH * D * 2 <= ((size_t)64 << 20)) {
         a.next = one_plan(next_rows(Wo, nullptr, H, NH * D, 1 << 20));
@@ -568,8 +571,9 @@ size_t ezb_qwen3_decode_stack_workspace_bytes(int B, int S, int H, int I, int NH
 }
 
 int ezb_qwen3_decode_stack(const void* hidden, void* out, const ezb_layer_t* layers, int n_layers, const void* rope_cos,
-                           const void* rope_sin, int rope_position, void* workspace, size_t workspace_bytes, int B, int S,
-                           int H, int I, int NH, int NKV, int D, float eps, ezb_stream_t stream) {
+                           const void* rope_sin, int rope_position, const int* seq_lens, void* workspace,
+                           size_t workspace_bytes, int B, int S, int H, int I, int NH, int NKV, int D, float eps,
+                           ezb_stream_t stream) {
     EZB_REQUIRE(hidden && out && layers && n_layers >= 1, "null pointer or no layers");
     EZB_REQUIRE((rope_cos == nullptr) == (rope_sin == nullptr) && rope_position >= 0, "rotary tables come as a pair; position >= 0");
     if (int rc = check_layer_args(B, S, H, I, NH, NKV, D)) return rc;
@@ -590,8 +594,10 @@ int ezb_qwen3_decode_stack(const void* hidden, void* out, const ezb_layer_t* lay
     }
     bf16* pp[2] = {reinterpret_cast<bf16*>(static_cast<unsigned char*>(workspace) + w.total),
                    reinterpret_cast<bf16*>(static_cast<unsigned char*>(workspace) + w.total + hbytes)};
-    const bf16* cos_row = rope_cos ? static_cast<const bf16*>(rope_cos) + (size_t)rope_position * D : nullptr;
-    const bf16* sin_row = rope_sin ? static_cast<const bf16*>(rope_sin) + (size_t)rope_position * D : nullptr;
+    // one position for all rows: hand the kernel that table row; per-row lengths: the table base, indexed by len-1
+    const size_t row_off = seq_lens ? 0 : (size_t)rope_position * D;
+    const bf16* cos_row = rope_cos ? static_cast<const bf16*>(rope_cos) + row_off : nullptr;
+    const bf16* sin_row = rope_sin ? static_cast<const bf16*>(rope_sin) + row_off : nullptr;
     chain_begin();  // one dependency chain through all layers
     const bf16* x = static_cast<const bf16*>(hidden);
     for (int l = 0; l < n_layers; ++l) {
@@ -600,6 +606,7 @@ int ezb_qwen3_decode_stack(const void* hidden, void* out, const ezb_layer_t* lay
         ex.input_norm_w = static_cast<const bf16*>(L.input_norm_w), ex.post_norm_w = static_cast<const bf16*>(L.post_norm_w);
         ex.q_norm_w = static_cast<const bf16*>(L.q_norm_w), ex.k_norm_w = static_cast<const bf16*>(L.k_norm_w);
         ex.rope_cos = cos_row, ex.rope_sin = sin_row;
+        ex.seq_lens = seq_lens, ex.rope_by_len = seq_lens ? 1 : 0;
         ex.next_Wqkv = (l + 1 < n_layers) ? static_cast<const bf16*>(layers[l + 1].Wqkv) : nullptr;
         bf16* y = (l + 1 == n_layers) ? static_cast<bf16*>(out) : pp[l & 1];
         if (int rc = run_layer(x, static_cast<bf16*>(L.K_cache), static_cast<bf16*>(L.V_cache), static_cast<const bf16*>(L.Wqkv),
@@ -791,6 +798,7 @@ static int run_layer_tp_fused(const bf16* x_prev, bool gather_prev, bf16* layer_
         a.K_cache_w = Kc, a.V_cache_w = Vc;
         a.eps = eps;
         a.q_norm_w = ex.q_norm_w, a.k_norm_w = ex.k_norm_w, a.rope_cos = ex.rope_cos, a.rope_sin = ex.rope_sin;
+        a.seq_lens = ex.seq_lens, a.rope_by_len = ex.rope_by_len;
         if ((size_t)H * Q * 2 <= ((size_t)64 << 20)) a.next = one_plan(next_rows(Wo, nullptr, H, Q, 1 << 20));
         EZB_CUDA_TRY(launch_attn_decode(a, stream));
     }
@@ -879,9 +887,10 @@ size_t ezb_qwen3_decode_stack_tp_fused_workspace_bytes(int B, int S, int H, int 
 }
 
 int ezb_qwen3_decode_stack_tp_fused(const void* hidden, void* out, const ezb_layer_t* layers_local, int n_layers,
-                                    const void* rope_cos, const void* rope_sin, int rope_position, void* workspace,
-                                    size_t workspace_bytes, void* const* comm_bases_host, int world, int rank, int B, int S,
-                                    int H, int I_local, int NH_local, int NKV_local, int D, float eps, ezb_stream_t stream) {
+                                    const void* rope_cos, const void* rope_sin, int rope_position, const int* seq_lens,
+                                    void* workspace, size_t workspace_bytes, void* const* comm_bases_host, int world, int rank,
+                                    int B, int S, int H, int I_local, int NH_local, int NKV_local, int D, float eps,
+                                    ezb_stream_t stream) {
     EZB_REQUIRE(hidden && out && layers_local && n_layers >= 1, "null pointer or no layers");
     EZB_REQUIRE((rope_cos == nullptr) == (rope_sin == nullptr) && rope_position >= 0, "rotary tables come as a pair; position >= 0");
     TpLink base;
@@ -906,8 +915,10 @@ int ezb_qwen3_decode_stack_tp_fused(const void* hidden, void* out, const ezb_lay
     unsigned char* extra = static_cast<unsigned char*>(workspace) + w.total;
     bf16* layer_in[2] = {reinterpret_cast<bf16*>(extra), reinterpret_cast<bf16*>(extra + hbytes)};
     bf16* x2[2] = {reinterpret_cast<bf16*>(extra + 2 * hbytes), reinterpret_cast<bf16*>(extra + 3 * hbytes)};
-    const bf16* cos_row = rope_cos ? static_cast<const bf16*>(rope_cos) + (size_t)rope_position * D : nullptr;
-    const bf16* sin_row = rope_sin ? static_cast<const bf16*>(rope_sin) + (size_t)rope_position * D : nullptr;
+    // one position for all rows: hand the kernel that table row; per-row lengths: the table base, indexed by len-1
+    const size_t row_off = seq_lens ? 0 : (size_t)rope_position * D;
+    const bf16* cos_row = rope_cos ? static_cast<const bf16*>(rope_cos) + row_off : nullptr;
+    const bf16* sin_row = rope_sin ? static_cast<const bf16*>(rope_sin) + row_off : nullptr;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     chain_begin();
     for (int l = 0; l < n_layers; ++l) {
@@ -916,6 +927,7 @@ int ezb_qwen3_decode_stack_tp_fused(const void* hidden, void* out, const ezb_lay
         ex.input_norm_w = static_cast<const bf16*>(L.input_norm_w), ex.post_norm_w = static_cast<const bf16*>(L.post_norm_w);
         ex.q_norm_w = static_cast<const bf16*>(L.q_norm_w), ex.k_norm_w = static_cast<const bf16*>(L.k_norm_w);
         ex.rope_cos = cos_row, ex.rope_sin = sin_row;
+        ex.seq_lens = seq_lens, ex.rope_by_len = seq_lens ? 1 : 0;
         ex.next_Wqkv = (l + 1 < n_layers) ? static_cast<const bf16*>(layers_local[l + 1].Wqkv) : nullptr;
         // layer l > 0 reads x2 of layer l-1 and folds that layer's second sum into its own QKV prologue
         const bf16* x_prev = l == 0 ? static_cast<const bf16*>(hidden) : x2[(l - 1) & 1];

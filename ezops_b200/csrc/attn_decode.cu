@@ -51,6 +51,7 @@ struct AttnParams {
     const bf16* k_norm_w;
     const bf16* rope_cos;
     const bf16* rope_sin;
+    int rope_by_len;  // 1: rope_cos / rope_sin are table bases, the row used is the token's slot (len-1)
     PrefetchList next;
     Trace trace;
 };
@@ -123,12 +124,17 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
     // The first tiles are requested right away, so that their latency overlaps
     // the query prologue below.
     int len = p.S;
-    if (p.seq_lens) len = max(0, min(p.S, p.seq_lens[b]));
+    if (p.seq_lens) len = max(p.fuse_new_token ? 1 : 0, min(p.S, p.seq_lens[b]));
+    // decode-layer mode: the token being decoded is the last valid key of the row (slot len-1;
+    // with one length for all rows that is slot S-1, the reference layer's convention)
+    const int new_slot = len - 1;
+    const bf16* rope_cos = p.rope_cos ? p.rope_cos + (p.rope_by_len ? (long long)new_slot * D : 0) : nullptr;
+    const bf16* rope_sin = p.rope_sin ? p.rope_sin + (p.rope_by_len ? (long long)new_slot * D : 0) : nullptr;
     const int c0 = chunk_id * p.chunk;
     const int c1 = min(len, c0 + p.chunk);
     const int nkeys = max(0, c1 - c0);
     const int ntiles = (nkeys + kTileKeys - 1) / kTileKeys;
-    const bool owns_new_slot = p.fuse_new_token && c0 <= p.S - 1 && p.S - 1 < c1;
+    const bool owns_new_slot = p.fuse_new_token && c0 <= new_slot && new_slot < c1;
 
     auto load_tile = [&](int t) {
         unsigned char* st = stages + (t % kAttnStages) * STAGE_BYTES;
@@ -182,20 +188,20 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
                 float x[D / 32];
 #pragma unroll
                 for (int j = 0; j < D / 32; ++j) x[j] = __bfloat162float(q_s[row * QS + lane + j * 32]);
-                head_norm_rope<D>(x, p.eps, p.q_norm_w, p.rope_cos, p.rope_sin, lane);
+                head_norm_rope<D>(x, p.eps, p.q_norm_w, rope_cos, rope_sin, lane);
 #pragma unroll
                 for (int j = 0; j < D / 32; ++j) q_s[row * QS + lane + j * 32] = __float2bfloat16_rn(x[j]);
             }
             // new token's k (normalised) and v: kept in shared memory for the patch below and
             // written to cache slot S-1 (nobody reads that slot from memory in this kernel)
             if (owns_new_slot) {
-                const long long slot = (kv_row0 + p.S - 1) * D;
+                const long long slot = (kv_row0 + new_slot) * D;
                 if (warp == 0) {
                     const bf16* ksrc = p.qkv + (long long)b * p.qkv_bstride + p.q_rows + kvh * D;
                     float x[D / 32];
 #pragma unroll
                     for (int j = 0; j < D / 32; ++j) x[j] = __bfloat162float(ksrc[lane + j * 32]);
-                    head_norm_rope<D>(x, p.eps, p.k_norm_w, p.rope_cos, p.rope_sin, lane);
+                    head_norm_rope<D>(x, p.eps, p.k_norm_w, rope_cos, rope_sin, lane);
 #pragma unroll
                     for (int j = 0; j < D / 32; ++j) {
                         const bf16 kn = __float2bfloat16_rn(x[j]);
@@ -245,7 +251,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
         cp_async_commit();
         if (owns_new_slot && t == ntiles - 1) {
             // overwrite the stale row of slot S-1 in this tile with the new token's k and v
-            const int r = p.S - 1 - (c0 + t * kTileKeys);
+            const int r = new_slot - (c0 + t * kTileKeys);
             if (tid < 2 * CPR) {
                 const int which = tid / CPR, c = tid % CPR;
                 unsigned char* dst = stages + (t % kAttnStages) * STAGE_BYTES + which * TILE_BYTES + r * ROW_BYTES + ((c ^ (r & 7)) << 4);
@@ -560,6 +566,7 @@ cudaError_t launch_attn_decode(const AttnArgs& a, cudaStream_t stream) {
     p.K_cache_w = a.K_cache_w, p.V_cache_w = a.V_cache_w;
     p.eps = a.eps;
     p.q_norm_w = a.q_norm_w, p.k_norm_w = a.k_norm_w, p.rope_cos = a.rope_cos, p.rope_sin = a.rope_sin;
+    p.rope_by_len = a.rope_by_len;
     p.next = a.next;
     if (!tuning(EZB_TUNE_L2_PREFETCH)) p.next.plan[0].units = p.next.plan[1].units = 0;
     p.trace = trace_handle();

@@ -121,6 +121,10 @@ struct AttnArgs {
     const bf16* k_norm_w = nullptr;
     const bf16* rope_cos = nullptr;
     const bf16* rope_sin = nullptr;
+    // with seq_lens in decode-layer mode the new token of row b sits in slot seq_lens[b]-1 and only
+    // seq_lens[b] keys are attended; rope_by_len = 1 then makes rope_cos / rope_sin table bases
+    // ([>= S, D]) indexed by that slot
+    int rope_by_len = 0;
     PrefetchList next = {};
 };
 size_t attn_workspace_bytes(int B, int H, int NKV, int S, int D);

@@ -296,12 +296,16 @@ class Qwen3DecodeStackSm100Kernel(BaseKernel):
             self._table, self._table_key = table, key
         return self._table
 
-    def __call__(self, hidden, layers, cos=None, sin=None, out=None):
+    def __call__(self, hidden, layers, cos=None, sin=None, out=None, seq_lens=None):
+        """``seq_lens`` (optional int32 CUDA tensor [B], values 1..S): row b's new token goes to slot
+        ``seq_lens[b] - 1``, attends to its first ``seq_lens[b]`` keys and is rotated with that slot's table row."""
         if len(layers) != self.L:
             raise ValueError(f"expected {self.L} layers, got {len(layers)}")
         _require(hidden, "hidden", (self.B, self.H))
         if (cos is None) != (sin is None):
             raise ValueError("cos and sin come as a pair")
+        if seq_lens is not None:
+            _require(seq_lens, "seq_lens", (self.B,), dtype=torch.int32)
         position = self.S - 1
         if cos is not None:
             for name, t in (("cos", cos), ("sin", sin)):
@@ -315,8 +319,8 @@ class Qwen3DecodeStackSm100Kernel(BaseKernel):
         _lib.check(
             self._lib.ezb_qwen3_decode_stack(
                 hidden.data_ptr(), out.data_ptr(), table, self.L, cos.data_ptr() if cos is not None else None,
-                sin.data_ptr() if sin is not None else None, position, ws.data_ptr(), ws.numel(), self.B, self.S, self.H, self.I,
-                self.NH, self.NKV, self.D, self.rms_eps, _stream(),
+                sin.data_ptr() if sin is not None else None, position, None if seq_lens is None else seq_lens.data_ptr(),
+                ws.data_ptr(), ws.numel(), self.B, self.S, self.H, self.I, self.NH, self.NKV, self.D, self.rms_eps, _stream(),
             )
         )
         return out

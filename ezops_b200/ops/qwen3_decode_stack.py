@@ -12,6 +12,11 @@ with, optionally,
   operator does (ezops/ops/fused_qk_norm_rope.py:138-147: head norm, weight and
   rotate-half in fp32, one bf16 rounding) with the table row of ``position``;
 
+* per-row lengths (``seq_lens``, each in 1..seq_len): row b's new token goes to cache slot
+  ``seq_lens[b] - 1``, attends to its first ``seq_lens[b]`` keys and is rotated with the table
+  row of that slot - the per-row position of sequences of different lengths in one batch
+  (the reference's attention and RoPE operators each take one length / position for all rows);
+
 and feeds layer ``l + 1``.  ``gen_data`` returns ``(hidden, layers, cos, sin)``
 where ``layers`` is a list of dicts of bf16 tensors: ``K_cache``, ``V_cache``
 [B, NKV, S, D] (slot S-1 receives the new k / v), ``Wqkv``, ``Wo``, ``Wgu``,
@@ -47,13 +52,14 @@ class Qwen3DecodeStackOp(Op):
         "num_kv_heads": "Number of KV heads for GQA (default: num_heads)",
         "rope": "1 = rotary embedding at position seq_len - 1 (default), 0 = none",
         "norm_weights": "1 = random norm weights 1 + N(0, 0.1) (default), 0 = unit weights",
+        "seq_lens": "optional list of per-row lengths in 1..seq_len (default: every row has seq_len)",
     }
     _rtol = 1e-2
     rms_eps = 1e-6
     rope_theta = 1e6
 
     def __init__(self, batch, seq_len, hidden_size, intermediate_size, num_heads, head_dim, num_layers, backend="ref",
-                 num_kv_heads=None, rope=1, norm_weights=1):
+                 num_kv_heads=None, rope=1, norm_weights=1, seq_lens=None):
         if seq_len < 1 or num_layers < 1:
             raise ValueError(f"seq_len ({seq_len}) and num_layers ({num_layers}) must be >= 1")
         self.batch, self.seq_len, self.num_layers = batch, seq_len, num_layers
@@ -64,6 +70,12 @@ class Qwen3DecodeStackOp(Op):
             raise ValueError(f"num_heads ({num_heads}) must be divisible by num_kv_heads ({self.num_kv_heads})")
         self.rope, self.norm_weights = bool(rope), bool(norm_weights)
         self.position = seq_len - 1
+        if seq_lens is not None:
+            seq_lens = [int(v) for v in seq_lens]
+            if len(seq_lens) != batch or any(v < 1 or v > seq_len for v in seq_lens):
+                raise ValueError(f"seq_lens must hold {batch} values in [1, {seq_len}]")
+        self.seq_lens = seq_lens
+        self._lens_dev = None
         self.q_rows, self.kv_rows = num_heads * head_dim, self.num_kv_heads * head_dim
         self._backend = backend
         if backend == "ref":
@@ -77,7 +89,11 @@ class Qwen3DecodeStackOp(Op):
         return actual.shape == expected.shape and rel_frobenius(actual, expected) < bound
 
     def forward(self, hidden, layers, cos=None, sin=None):
-        return self._kernel(hidden, layers, cos, sin)
+        if self._backend == "ref" or self.seq_lens is None:
+            return self._kernel(hidden, layers, cos, sin)
+        if self._lens_dev is None or self._lens_dev.device != hidden.device:
+            self._lens_dev = torch.tensor(self.seq_lens, dtype=torch.int32, device=hidden.device)
+        return self._kernel(hidden, layers, cos, sin, seq_lens=self._lens_dev)
 
     def rope_tables(self, device):
         """ezops/ops/fused_qk_norm_rope.py:119-125."""
@@ -123,16 +139,24 @@ class Qwen3DecodeStackOp(Op):
     def _ref_forward(self, hidden, layers, cos=None, sin=None):
         B, D, I = hidden.shape[0], self.head_dim, self.intermediate_size
         q_end, k_end = self.q_rows, self.q_rows + self.kv_rows
-        c = cos[self.position].to(torch.float32) if cos is not None else None
-        s = sin[self.position].to(torch.float32) if sin is not None else None
+        lens = self.seq_lens if self.seq_lens is not None else [self.seq_len] * B
+        pos = torch.tensor([n - 1 for n in lens], device=hidden.device)
+        c = cos[pos].to(torch.float32)[:, None, :] if cos is not None else None  # [B, 1, D]: one table row per batch row
+        s = sin[pos].to(torch.float32)[:, None, :] if sin is not None else None
+        rows = torch.arange(B, device=hidden.device)
         x_in = hidden
         for L in layers:
             qkv = self._rmsnorm(x_in, L.get("input_norm_w")) @ L["Wqkv"].T
             q = self._head(qkv[:, :q_end].view(B, self.num_heads, D), L.get("q_norm_w"), c, s)
             k = self._head(qkv[:, q_end:k_end].view(B, self.num_kv_heads, D), L.get("k_norm_w"), c, s)
-            L["K_cache"][:, :, -1, :] = k
-            L["V_cache"][:, :, -1, :] = qkv[:, k_end:].view(B, self.num_kv_heads, D)
-            attn = F.scaled_dot_product_attention(q.unsqueeze(2), L["K_cache"], L["V_cache"], enable_gqa=True).squeeze(2)
+            L["K_cache"][rows, :, pos, :] = k
+            L["V_cache"][rows, :, pos, :] = qkv[:, k_end:].view(B, self.num_kv_heads, D)
+            if self.seq_lens is None:
+                attn = F.scaled_dot_product_attention(q.unsqueeze(2), L["K_cache"], L["V_cache"], enable_gqa=True).squeeze(2)
+            else:  # every row attends to its own prefix
+                attn = torch.cat([F.scaled_dot_product_attention(q[b : b + 1].unsqueeze(2), L["K_cache"][b : b + 1, :, :n],
+                                                                 L["V_cache"][b : b + 1, :, :n], enable_gqa=True).squeeze(2)
+                                  for b, n in enumerate(lens)], dim=0)
             x2 = x_in + attn.reshape(B, self.q_rows) @ L["Wo"].T
             gu = self._rmsnorm(x2, L.get("post_norm_w")) @ L["Wgu"].T
             x_in = x2 + (F.silu(gu[:, :I]) * gu[:, I:]) @ L["Wd"].T

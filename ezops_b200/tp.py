@@ -231,7 +231,7 @@ class TensorParallelDecodeStack(TensorParallelDecodeLayer):
             self._table, self._table_key = table, key
         return self._table
 
-    def __call__(self, hidden, layers_local, cos=None, sin=None, out=None):
+    def __call__(self, hidden, layers_local, cos=None, sin=None, out=None, seq_lens=None):
         if len(layers_local) != self.L:
             raise ValueError(f"expected {self.L} layers, got {len(layers_local)}")
         lib = _lib.load()
@@ -244,7 +244,8 @@ class TensorParallelDecodeStack(TensorParallelDecodeLayer):
             out = torch.empty_like(hidden)
         _lib.check(lib.ezb_qwen3_decode_stack_tp_fused(
             hidden.data_ptr(), out.data_ptr(), table, self.L, None if cos is None else cos.data_ptr(),
-            None if sin is None else sin.data_ptr(), self.S - 1, self._stack_ws.data_ptr(), self._stack_ws.numel(), comm["bases"],
+            None if sin is None else sin.data_ptr(), self.S - 1, None if seq_lens is None else seq_lens.data_ptr(),
+            self._stack_ws.data_ptr(), self._stack_ws.numel(), comm["bases"],
             self.tp, self.rank, self.B, self.S, self.H, self.I_l, self.NH_l, self.NKV_l, self.D, self.rms_eps,
             torch.cuda.current_stream().cuda_stream))
         return out

@@ -216,7 +216,12 @@ int ezb_residual_add_f32(const void* x2, const float* summed_d, void* out, int B
  * may be NULL (unit weight); rope_cos / rope_sin are [>= rope_position + 1, D]
  * bf16 tables in the reference's layout (halves repeated) or both NULL (no
  * rotation).  As in the layer operator every cache has S slots and the new
- * token goes to slot S - 1.  `layers` is a host array, read during the call. */
+ * token goes to slot S - 1 - unless seq_lens (device, [B] int32, each 1..S) is
+ * given: then row b's token goes to slot seq_lens[b] - 1, attends to its
+ * first seq_lens[b] keys and is rotated with the table row of that slot
+ * (rope_position is ignored; the tables must have S rows).  That is the
+ * per-row position a serving loop with sequences of different lengths needs.
+ * `layers` is a host array, read during the call. */
 typedef struct ezb_layer_t {
     void* K_cache;
     void* V_cache;
@@ -231,8 +236,9 @@ typedef struct ezb_layer_t {
 } ezb_layer_t;
 size_t ezb_qwen3_decode_stack_workspace_bytes(int B, int S, int H, int I, int NH, int NKV, int D);
 int ezb_qwen3_decode_stack(const void* hidden, void* out, const ezb_layer_t* layers, int n_layers, const void* rope_cos,
-                           const void* rope_sin, int rope_position, void* workspace, size_t workspace_bytes, int B, int S,
-                           int H, int I, int NH, int NKV, int D, float eps, ezb_stream_t stream);
+                           const void* rope_sin, int rope_position, const int* seq_lens, void* workspace,
+                           size_t workspace_bytes, int B, int S, int H, int I, int NH, int NKV, int D, float eps,
+                           ezb_stream_t stream);
 
 /* Kernel launches issued by the library in this process so far (every kernel of
  * the library goes through one launch helper).  A diagnostic with no
@@ -248,9 +254,10 @@ unsigned long long ezb_launch_count(void);
  * the communication buffers; no counterpart in the reference. */
 size_t ezb_qwen3_decode_stack_tp_fused_workspace_bytes(int B, int S, int H, int I_local, int NH_local, int NKV_local, int D);
 int ezb_qwen3_decode_stack_tp_fused(const void* hidden, void* out, const ezb_layer_t* layers_local, int n_layers,
-                                    const void* rope_cos, const void* rope_sin, int rope_position, void* workspace,
-                                    size_t workspace_bytes, void* const* comm_bases_host, int world, int rank, int B, int S,
-                                    int H, int I_local, int NH_local, int NKV_local, int D, float eps, ezb_stream_t stream);
+                                    const void* rope_cos, const void* rope_sin, int rope_position, const int* seq_lens,
+                                    void* workspace, size_t workspace_bytes, void* const* comm_bases_host, int world, int rank,
+                                    int B, int S, int H, int I_local, int NH_local, int NKV_local, int D, float eps,
+                                    ezb_stream_t stream);
 
 /* Bandwidth calibration for the roofline profile of a GPU: one pass of a
  * STREAM-style kernel over n_vec4 128-bit elements; op 0 reads b, 1 writes a, 2

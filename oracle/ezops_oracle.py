@@ -217,21 +217,28 @@ def qwen3_dense_decode_fp64(hidden, K_cache, V_cache, Wqkv, Wo, Wgu, Wd, num_hea
 
 # ------------------------------------------------ tensor-parallel sharding ---
 def qwen3_decode_stack_ref(hidden, layers, num_heads, num_kv_heads, head_dim, cos=None, sin=None, position=None,
-                           eps: float = RMS_EPS) -> torch.Tensor:
+                           eps: float = RMS_EPS, seq_lens=None) -> torch.Tensor:
     """A stack of decode layers: the layer formula above (ezops/ops/qwen3_dense_decode.py:142-176)
     per layer, each feeding the next.  Optional per-layer norm weights (``None`` = unit; weighted
     RMSNorm as ezops/ops/fused_o_proj_ffn.py:107-110) and, when ``cos`` / ``sin`` are given, the
     new token's q and k go through the stand-alone operator's formula (``_head_norm_f32`` +
     ``_rotate_half_f32``, ezops/ops/fused_qk_norm_rope.py:138-147) with the table row of
     ``position`` (default S-1).  ``layers``: dicts with K_cache, V_cache (slot S-1 is written),
-    Wqkv, Wo, Wgu, Wd and optionally input_norm_w, post_norm_w, q_norm_w, k_norm_w.  No single
-    reference function covers this composition; each piece is pinned by its own fixtures."""
+    Wqkv, Wo, Wgu, Wd and optionally input_norm_w, post_norm_w, q_norm_w, k_norm_w.
+    ``seq_lens`` (one int per batch row, 1..S): row b's token goes to slot seq_lens[b]-1, attends to
+    its first seq_lens[b] keys (per-row SDPA over the prefix, as ``attn_decode_ref`` does for ragged
+    batches) and is rotated with that slot's table row (per-row positions, as ``qk_norm_rope_ref``).
+    No single reference function covers this composition; each piece is pinned by its own fixtures."""
     B = hidden.shape[0]
     q_rows, kv_rows = num_heads * head_dim, num_kv_heads * head_dim
     x_in = hidden
     for L in layers:
         S = L["K_cache"].shape[2]
-        pos = S - 1 if position is None else position
+        if seq_lens is not None:
+            slots = [int(n) - 1 for n in seq_lens]
+        else:
+            slots = [S - 1 if position is None else position] * B
+        lens = [int(n) for n in seq_lens] if seq_lens is not None else [S] * B
         inter = L["Wgu"].shape[0] // 2
         qkv = rmsnorm_bf16_ref(x_in, L.get("input_norm_w"), eps) @ L["Wqkv"].T
         q = qkv[:, :q_rows].view(B, num_heads, head_dim)
@@ -242,14 +249,21 @@ def qwen3_decode_stack_ref(hidden, layers, num_heads, num_kv_heads, head_dim, co
             k = rmsnorm_bf16_ref(k, L.get("k_norm_w"), eps)
         else:
             ones = torch.ones(head_dim, dtype=torch.bfloat16)
-            c, s = cos[pos].to(torch.float32), sin[pos].to(torch.float32)
+            idx = torch.tensor(slots)
+            c, s = cos[idx].to(torch.float32)[:, None, :], sin[idx].to(torch.float32)[:, None, :]
             qw = ones if L.get("q_norm_w") is None else L["q_norm_w"]
             kw = ones if L.get("k_norm_w") is None else L["k_norm_w"]
             q = _rotate_half_f32(_head_norm_f32(q, qw, eps), c, s)
             k = _rotate_half_f32(_head_norm_f32(k, kw, eps), c, s)
-        L["K_cache"][:, :, -1, :] = k
-        L["V_cache"][:, :, -1, :] = v
-        attn = F.scaled_dot_product_attention(q.unsqueeze(2), L["K_cache"], L["V_cache"], enable_gqa=True).squeeze(2)
+        for b, slot in enumerate(slots):
+            L["K_cache"][b, :, slot, :] = k[b]
+            L["V_cache"][b, :, slot, :] = v[b]
+        if seq_lens is None:
+            attn = F.scaled_dot_product_attention(q.unsqueeze(2), L["K_cache"], L["V_cache"], enable_gqa=True).squeeze(2)
+        else:
+            attn = torch.cat([F.scaled_dot_product_attention(q[b : b + 1].unsqueeze(2), L["K_cache"][b : b + 1, :, :n],
+                                                             L["V_cache"][b : b + 1, :, :n], enable_gqa=True).squeeze(2)
+                              for b, n in enumerate(lens)], dim=0)
         x2 = x_in + attn.reshape(B, q_rows) @ L["Wo"].T
         gu = rmsnorm_bf16_ref(x2, L.get("post_norm_w"), eps) @ L["Wgu"].T
         x_in = x2 + (F.silu(gu[:, :inter]) * gu[:, inter:]) @ L["Wd"].T

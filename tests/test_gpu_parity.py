@@ -601,3 +601,30 @@ def test_tp_fused_stack_world_one_matches_the_stack(ez):
         torch.cuda.synchronize()
         stack.close()
 
+
+
+@pytest.mark.parametrize("batch,lens", [(4, [333, 17, 128, 65]), (1, [200]), (16, [333, 1, 64, 65, 129, 300, 2, 77, 333, 200, 100, 50, 25, 12, 6, 3])])
+def test_decode_stack_with_per_row_lengths(ez, batch, lens):
+    """Rows of different lengths in one batch: the new token of row b goes to slot lens[b]-1, the row
+    attends to its own prefix and RoPE uses that slot's table row; everything else in the caches stays."""
+    import copy
+
+    from ezops_b200 import workloads as wl
+
+    sh, S, NL = wl.QWEN3_VL_2B, 333, 2
+    hid, layers, cos, sin = wl.decode_stack_inputs(sh, batch, S, NL)
+    ref_layers = copy.deepcopy(layers)
+    ref = orc.qwen3_decode_stack_ref(hid, ref_layers, sh.num_heads, sh.num_kv_heads, sh.head_dim, cos, sin, seq_lens=lens)
+    op = ez.Qwen3DecodeStackOp(batch, S, sh.hidden, sh.inter, sh.num_heads, sh.head_dim, NL, backend="cuda",
+                               num_kv_heads=sh.num_kv_heads, seq_lens=lens)
+    dl = _stack_to_device(layers)
+    got = op(hid.cuda(), dl, cos.cuda(), sin.cuda())
+    assert rel_fro(got, ref) < 1e-2, rel_fro(got, ref)
+    for L, R, L0 in zip(dl, ref_layers, layers):
+        for b, n in enumerate(lens):
+            keep = [i for i in range(S) if i != n - 1]
+            assert torch.equal(L["K_cache"][b][:, keep].cpu(), L0["K_cache"][b][:, keep])
+            assert torch.equal(L["V_cache"][b][:, keep].cpu(), L0["V_cache"][b][:, keep])
+            assert torch.allclose(L["K_cache"][b][:, n - 1].cpu().float(), R["K_cache"][b][:, n - 1].float(), atol=6e-2, rtol=2e-2)
+    again = op(hid.cuda(), dl, cos.cuda(), sin.cuda())
+    assert torch.equal(again, got)

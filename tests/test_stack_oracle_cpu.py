@@ -74,3 +74,36 @@ def test_shard_stack_splits_every_layer_like_one_layer():
             assert got["input_norm_w"] is L["input_norm_w"] and got["q_norm_w"] is L["q_norm_w"]  # replicated
         assert torch.equal(torch.cat([shards[r][l]["K_cache"] for r in range(world)], dim=1), L["K_cache"])
         assert torch.equal(torch.cat([shards[r][l]["Wo"] for r in range(world)], dim=1), L["Wo"])
+
+
+def test_per_row_lengths_reduce_to_the_uniform_case_and_match_the_operator_reference():
+    import ezops_b200 as ez
+
+    B, S, NL = 3, 21, 2
+    hid, layers, cos, sin = wl.decode_stack_inputs(SH, B, S, NL)
+    full = orc.qwen3_decode_stack_ref(hid, copy.deepcopy(layers), *HEADS, cos, sin)
+    same = orc.qwen3_decode_stack_ref(hid, copy.deepcopy(layers), *HEADS, cos, sin, seq_lens=[S] * B)
+    assert torch.equal(full, same)
+    lens = [S, 5, 13]
+    la, lb = copy.deepcopy(layers), copy.deepcopy(layers)
+    want = orc.qwen3_decode_stack_ref(hid, la, *HEADS, cos, sin, seq_lens=lens)
+    op = ez.Qwen3DecodeStackOp(B, S, SH.hidden, SH.inter, SH.num_heads, SH.head_dim, NL, backend="ref",
+                               num_kv_heads=SH.num_kv_heads, seq_lens=lens)
+    got = op(hid, lb, cos, sin)
+    assert torch.equal(got, want)
+    for L0, L1 in zip(layers, la):
+        for b, n in enumerate(lens):  # only slot len-1 of each row changed
+            keep = [i for i in range(S) if i != n - 1]
+            assert torch.equal(L1["K_cache"][b][:, keep], L0["K_cache"][b][:, keep])
+            assert not torch.equal(L1["K_cache"][b][:, n - 1], L0["K_cache"][b][:, n - 1])
+    # a row with a shorter prefix must not depend on the keys behind it
+    lc = copy.deepcopy(layers)
+    for L in lc:
+        L["K_cache"][1, :, 5:] = 7.0
+        L["V_cache"][1, :, 5:] = -3.0
+    again = orc.qwen3_decode_stack_ref(hid, lc, *HEADS, cos, sin, seq_lens=lens)
+    assert torch.equal(again[1], want[1])
+    import pytest
+
+    with pytest.raises(ValueError):
+        ez.Qwen3DecodeStackOp(B, S, SH.hidden, SH.inter, SH.num_heads, SH.head_dim, NL, seq_lens=[S, 0, 3])
