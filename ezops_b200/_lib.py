@@ -64,6 +64,10 @@ SIGNATURES = {
     "ezb_qwen3_decode_layer_tp_attn": (c_int, [c_void_p] * 7 + [c_size_t] + [c_int] * 6 + [c_float, c_void_p]),
     "ezb_qwen3_decode_layer_tp_ffn": (c_int, [c_void_p] * 7 + [c_size_t] + [c_int] * 3 + [c_float, c_void_p]),
     "ezb_residual_add_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "ezb_attn_decode_paged": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t] + [c_int] * 6
+                              + [c_void_p, c_void_p]),
+    "ezb_qwen3_decode_stack_paged": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                             c_void_p, c_size_t] + [c_int] * 6 + [c_float, c_void_p]),
     "ezb_qwen3_decode_stack_workspace_bytes": (c_size_t, [c_int] * 7),
     "ezb_qwen3_decode_stack": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_size_t]
                                + [c_int] * 7 + [c_float, c_void_p]),

@@ -276,6 +276,8 @@ struct LayerExtras {
     const bf16* next_Wqkv = nullptr;
     const int* seq_lens = nullptr;  // per-row valid lengths (device); the new token goes to slot len-1
     int rope_by_len = 0;            // rope_cos / rope_sin are table bases indexed by that slot
+    const int* page_table = nullptr;  // paged caches (see AttnArgs)
+    int page_shift = 0, max_pages = 0;
 };
 static const LayerExtras kPlainLayer = {};
 
@@ -295,7 +297,7 @@ static cudaError_t launch_qkv_and_attention(const bf16* hidden, bf16* Kc, bf16* 
     g.trace_id = 1;
     // while the projection drains, start pulling the KV cache (if it is small enough to sit in L2)
     const size_t kv_bytes = (size_t)B * NKV * S * D * 2;
-    if (2 * kv_bytes <= ((size_t)48 << 20)) g.next = one_plan(prefetch_plan_flat(Kc, Vc, kv_bytes));
+    if (!ex.page_table && 2 * kv_bytes <= ((size_t)48 << 20)) g.next = one_plan(prefetch_plan_flat(Kc, Vc, kv_bytes));
     cudaError_t e = launch_gemv(g, stream);
     if (e != cudaSuccess) return e;
 
@@ -310,6 +312,7 @@ static cudaError_t launch_qkv_and_attention(const bf16* hidden, bf16* Kc, bf16* 
     a.eps = eps;
     a.q_norm_w = ex.q_norm_w, a.k_norm_w = ex.k_norm_w, a.rope_cos = ex.rope_cos, a.rope_sin = ex.rope_sin;
     a.seq_lens = ex.seq_lens, a.rope_by_len = ex.rope_by_len;
+    a.page_table = ex.page_table, a.page_shift = ex.page_shift, a.max_pages = ex.max_pages;
     // attention is latency-bound at small batch: let HBM stream the output projection meanwhile
     if ((size_t)H * NH * D * 2 <= ((size_t)64 << 20)) {
         a.next = one_plan(next_rows(Wo, nullptr, H, NH * D, 1 << 20));
@@ -491,6 +494,40 @@ int ezb_attn_decode(const void* Q, const void* K, const void* V, void* Out, void
     return EZB_OK;
 }
 
+static int page_shift_of(int page_size) {
+    int sh = 0;
+    while ((1 << sh) < page_size) ++sh;
+    return ((1 << sh) == page_size && page_size >= 64) ? sh : -1;
+}
+
+int ezb_attn_decode_paged(const void* Q, const void* K_pool, const void* V_pool, const int* page_table, void* Out,
+                          void* workspace, size_t workspace_bytes, int B, int H, int NKV, int max_pages, int page_size, int D,
+                          const int* seq_lens, ezb_stream_t stream) {
+    EZB_REQUIRE(Q && K_pool && V_pool && page_table && Out && seq_lens, "null pointer");
+    EZB_REQUIRE(B >= 1 && H >= 1 && NKV >= 1 && max_pages >= 1, "sizes must be positive");
+    EZB_REQUIRE_SHAPE(page_shift_of(page_size) >= 0, "page_size must be a power of two >= 64");
+    EZB_REQUIRE_SHAPE(D == 64 || D == 128, "head_dim must be 64 or 128");
+    EZB_REQUIRE_SHAPE(H % NKV == 0, "num_heads must be divisible by num_kv_heads");
+    EZB_REQUIRE_SHAPE(B <= 65535 && NKV <= 65535, "batch and kv heads are limited to 65535");
+    EZB_REQUIRE(aligned16(Q) && aligned16(K_pool) && aligned16(V_pool), "Q and the page pools must be 16-byte aligned");
+    const int S = max_pages * page_size;
+    if (!workspace || workspace_bytes < attn_workspace_bytes(B, H, NKV, S, D)) {
+        set_last_message("attention workspace missing or smaller than ezb_attn_decode_workspace_bytes(B, H, NKV, max_pages * page_size, D)");
+        return EZB_ERR_WORKSPACE;
+    }
+    AttnArgs a;
+    a.Q = static_cast<const bf16*>(Q), a.q_bstride = (long long)H * D;
+    a.K = static_cast<const bf16*>(K_pool), a.V = static_cast<const bf16*>(V_pool);
+    a.Out = static_cast<bf16*>(Out), a.o_bstride = (long long)H * D;
+    a.seq_lens = seq_lens;
+    a.B = B, a.H = H, a.NKV = NKV, a.S = S, a.D = D;
+    a.page_table = page_table, a.page_shift = page_shift_of(page_size), a.max_pages = max_pages;
+    a.workspace = workspace;
+    chain_begin();
+    EZB_CUDA_TRY(launch_attn_decode(a, stream));
+    return EZB_OK;
+}
+
 size_t ezb_o_proj_ffn_workspace_bytes(int B, int H, int I, int Q) {
     if (B < 1 || H < 1 || I < 1 || Q < 1) return 0;
     return carve_ffn_ws(nullptr, B, H, I).total;
@@ -570,10 +607,10 @@ size_t ezb_qwen3_decode_stack_workspace_bytes(int B, int S, int H, int I, int NH
     return carve_layer_ws(nullptr, B, S, H, I, NH, NKV, D).total + 2 * round256((size_t)B * H * sizeof(bf16));
 }
 
-int ezb_qwen3_decode_stack(const void* hidden, void* out, const ezb_layer_t* layers, int n_layers, const void* rope_cos,
-                           const void* rope_sin, int rope_position, const int* seq_lens, void* workspace,
-                           size_t workspace_bytes, int B, int S, int H, int I, int NH, int NKV, int D, float eps,
-                           ezb_stream_t stream) {
+static int run_stack(const void* hidden, void* out, const ezb_layer_t* layers, int n_layers, const void* rope_cos,
+                     const void* rope_sin, int rope_position, const int* seq_lens, const int* page_table, int page_shift,
+                     int max_pages, void* workspace, size_t workspace_bytes, int B, int S, int H, int I, int NH, int NKV, int D,
+                     float eps, ezb_stream_t stream) {
     EZB_REQUIRE(hidden && out && layers && n_layers >= 1, "null pointer or no layers");
     EZB_REQUIRE((rope_cos == nullptr) == (rope_sin == nullptr) && rope_position >= 0, "rotary tables come as a pair; position >= 0");
     if (int rc = check_layer_args(B, S, H, I, NH, NKV, D)) return rc;
@@ -607,6 +644,7 @@ int ezb_qwen3_decode_stack(const void* hidden, void* out, const ezb_layer_t* lay
         ex.q_norm_w = static_cast<const bf16*>(L.q_norm_w), ex.k_norm_w = static_cast<const bf16*>(L.k_norm_w);
         ex.rope_cos = cos_row, ex.rope_sin = sin_row;
         ex.seq_lens = seq_lens, ex.rope_by_len = seq_lens ? 1 : 0;
+        ex.page_table = page_table, ex.page_shift = page_shift, ex.max_pages = max_pages;
         ex.next_Wqkv = (l + 1 < n_layers) ? static_cast<const bf16*>(layers[l + 1].Wqkv) : nullptr;
         bf16* y = (l + 1 == n_layers) ? static_cast<bf16*>(out) : pp[l & 1];
         if (int rc = run_layer(x, static_cast<bf16*>(L.K_cache), static_cast<bf16*>(L.V_cache), static_cast<const bf16*>(L.Wqkv),
@@ -879,6 +917,24 @@ int ezb_qwen3_decode_layer_tp_fused(const void* hidden, void* K_cache, void* V_c
                                     kPlainLayer, st))
         return rc;
     return finish_tp_fused(w.x2, static_cast<bf16*>(out), base, B, H, st);
+}
+
+int ezb_qwen3_decode_stack(const void* hidden, void* out, const ezb_layer_t* layers, int n_layers, const void* rope_cos,
+                           const void* rope_sin, int rope_position, const int* seq_lens, void* workspace,
+                           size_t workspace_bytes, int B, int S, int H, int I, int NH, int NKV, int D, float eps,
+                           ezb_stream_t stream) {
+    return run_stack(hidden, out, layers, n_layers, rope_cos, rope_sin, rope_position, seq_lens, nullptr, 0, 0, workspace,
+                     workspace_bytes, B, S, H, I, NH, NKV, D, eps, stream);
+}
+
+int ezb_qwen3_decode_stack_paged(const void* hidden, void* out, const ezb_layer_t* layers, int n_layers, const void* rope_cos,
+                                 const void* rope_sin, const int* seq_lens, const int* page_table, int page_size,
+                                 int max_pages, void* workspace, size_t workspace_bytes, int B, int H, int I, int NH, int NKV,
+                                 int D, float eps, ezb_stream_t stream) {
+    EZB_REQUIRE(seq_lens && page_table && max_pages >= 1, "paged caches need seq_lens and a page table");
+    EZB_REQUIRE_SHAPE(page_shift_of(page_size) >= 0, "page_size must be a power of two >= 64");
+    return run_stack(hidden, out, layers, n_layers, rope_cos, rope_sin, 0, seq_lens, page_table, page_shift_of(page_size),
+                     max_pages, workspace, workspace_bytes, B, max_pages * page_size, H, I, NH, NKV, D, eps, stream);
 }
 
 size_t ezb_qwen3_decode_stack_tp_fused_workspace_bytes(int B, int S, int H, int I_local, int NH_local, int NKV_local, int D) {

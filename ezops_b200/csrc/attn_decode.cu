@@ -52,6 +52,9 @@ struct AttnParams {
     const bf16* rope_cos;
     const bf16* rope_sin;
     int rope_by_len;  // 1: rope_cos / rope_sin are table bases, the row used is the token's slot (len-1)
+    const int* page_table;  // null: contiguous caches [B, NKV, S, D]; else [B, max_pages] page ids into pools [pages, NKV, P, D]
+    int page_shift;         // log2 of the page size P (a power of two >= 64, so a 64-key tile never straddles pages)
+    int max_pages;
     PrefetchList next;
     Trace trace;
 };
@@ -109,6 +112,12 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
     const int kvh = blockIdx.y, b = blockIdx.z;
     const int G = p.G, g0 = qt * 16, gn = min(16, G - g0);
     const long long kv_row0 = ((long long)b * p.NKV + kvh) * p.S;
+    // Row (in units of D elements) of this (batch row, kv head)'s key `key` in the cache.
+    auto cache_row = [&](int key) -> long long {
+        if (!p.page_table) return kv_row0 + key;
+        const long long page = __ldg(p.page_table + (long long)b * p.max_pages + (key >> p.page_shift));
+        return ((page * p.NKV + kvh) << p.page_shift) + (key & ((1 << p.page_shift) - 1));
+    };
 
     unsigned long long* trec = (tid == 0) ? trace_open(p.trace, 9u, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) : nullptr;
     pdl_trigger();
@@ -139,6 +148,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
     auto load_tile = [&](int t) {
         unsigned char* st = stages + (t % kAttnStages) * STAGE_BYTES;
         const int key0 = c0 + t * kTileKeys;
+        const long long tile_row0 = cache_row(key0);  // the tile lies inside one page
 #pragma unroll
         for (int i = 0; i < (2 * kTileKeys * CPR) / kAttnThreads; ++i) {
             const int idx = tid + i * kAttnThreads;
@@ -147,7 +157,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
             const int r = rem / CPR, c = rem % CPR;
             const int key = key0 + r;
             const bool valid = key < c1;
-            const bf16* src = (which ? p.V : p.K) + (kv_row0 + (valid ? key : 0)) * D + c * 8;
+            const bf16* src = (which ? p.V : p.K) + (tile_row0 + (valid ? r : 0)) * D + c * 8;
             const uint32_t dst = smem_u32(st) + which * TILE_BYTES + r * ROW_BYTES + ((c ^ (r & 7)) << 4);
             cp_async16(dst, src, valid);
         }
@@ -195,7 +205,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
             // new token's k (normalised) and v: kept in shared memory for the patch below and
             // written to cache slot S-1 (nobody reads that slot from memory in this kernel)
             if (owns_new_slot) {
-                const long long slot = (kv_row0 + new_slot) * D;
+                const long long slot = cache_row(new_slot) * D;
                 if (warp == 0) {
                     const bf16* ksrc = p.qkv + (long long)b * p.qkv_bstride + p.q_rows + kvh * D;
                     float x[D / 32];
@@ -567,6 +577,7 @@ cudaError_t launch_attn_decode(const AttnArgs& a, cudaStream_t stream) {
     p.eps = a.eps;
     p.q_norm_w = a.q_norm_w, p.k_norm_w = a.k_norm_w, p.rope_cos = a.rope_cos, p.rope_sin = a.rope_sin;
     p.rope_by_len = a.rope_by_len;
+    p.page_table = a.page_table, p.page_shift = a.page_shift, p.max_pages = a.max_pages;
     p.next = a.next;
     if (!tuning(EZB_TUNE_L2_PREFETCH)) p.next.plan[0].units = p.next.plan[1].units = 0;
     p.trace = trace_handle();

@@ -125,6 +125,11 @@ struct AttnArgs {
     // seq_lens[b] keys are attended; rope_by_len = 1 then makes rope_cos / rope_sin table bases
     // ([>= S, D]) indexed by that slot
     int rope_by_len = 0;
+    // paged caches: K / V (and K_cache_w / V_cache_w) are page pools [pages, NKV, P, D], page_table is
+    // [B, max_pages] int32 on the device, P = 1 << page_shift >= 64, S = max_pages * P
+    const int* page_table = nullptr;
+    int page_shift = 0;
+    int max_pages = 0;
     PrefetchList next = {};
 };
 size_t attn_workspace_bytes(int B, int H, int NKV, int S, int D);

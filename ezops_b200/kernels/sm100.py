@@ -169,6 +169,29 @@ class AttnDecodeSm100Kernel(BaseKernel):
         )
         return out
 
+    def call_paged(self, Q, K_pool, V_pool, page_table, seq_lens, page_size):
+        """The same attention over paged caches: ``K_pool`` / ``V_pool`` [pages, NKV, page_size, D],
+        ``page_table`` [B, max_pages] int32 and ``seq_lens`` [B] int32 on the device; the constructor's
+        ``seq_len`` must equal ``max_pages * page_size``."""
+        B, H, NKV, D = self.B, self.H, self.NKV, self.D
+        _require(Q, "Q", (B, H, 1, D))
+        max_pages = page_table.shape[1]
+        if self.S != max_pages * page_size:
+            raise ValueError(f"seq_len ({self.S}) must equal max_pages * page_size ({max_pages} * {page_size})")
+        _require(page_table, "page_table", (B, max_pages), dtype=torch.int32)
+        _require(seq_lens, "seq_lens", (B,), dtype=torch.int32)
+        for name, t in (("K_pool", K_pool), ("V_pool", V_pool)):
+            _require(t, name, (t.shape[0], NKV, page_size, D))
+        out = torch.empty_like(Q)
+        ws = self._workspace(Q.device)
+        _lib.check(
+            self._lib.ezb_attn_decode_paged(
+                Q.data_ptr(), K_pool.data_ptr(), V_pool.data_ptr(), page_table.data_ptr(), out.data_ptr(), ws.data_ptr(),
+                ws.numel(), B, H, NKV, max_pages, page_size, D, seq_lens.data_ptr(), _stream(),
+            )
+        )
+        return out
+
 
 @register_kernel("fused_o_proj_ffn", "cuda")
 class FusedOProjFfnSm100Kernel(BaseKernel):
@@ -276,9 +299,10 @@ class Qwen3DecodeStackSm100Kernel(BaseKernel):
             self._ws = _zeros_bytes(need, device)
         return self._ws
 
-    def _layer_table(self, layers):
+    def _layer_table(self, layers, page_size=None):
         B, S, H, I, NH, NKV, D = self.B, self.S, self.H, self.I, self.NH, self.NKV, self.D
-        shapes = {"K_cache": (B, NKV, S, D), "V_cache": (B, NKV, S, D), "Wqkv": ((NH + 2 * NKV) * D, H), "Wo": (H, NH * D),
+        cache = (B, NKV, S, D) if page_size is None else (layers[0]["K_cache"].shape[0], NKV, page_size, D)  # pools when paged
+        shapes = {"K_cache": cache, "V_cache": cache, "Wqkv": ((NH + 2 * NKV) * D, H), "Wo": (H, NH * D),
                   "Wgu": (2 * I, H), "Wd": (H, I), "input_norm_w": (H,), "post_norm_w": (H,), "q_norm_w": (D,), "k_norm_w": (D,)}
         key = tuple(0 if L.get(n) is None else L[n].data_ptr() for L in layers for n in shapes)
         if key != self._table_key:
@@ -296,9 +320,11 @@ class Qwen3DecodeStackSm100Kernel(BaseKernel):
             self._table, self._table_key = table, key
         return self._table
 
-    def __call__(self, hidden, layers, cos=None, sin=None, out=None, seq_lens=None):
+    def __call__(self, hidden, layers, cos=None, sin=None, out=None, seq_lens=None, page_table=None, page_size=None):
         """``seq_lens`` (optional int32 CUDA tensor [B], values 1..S): row b's new token goes to slot
-        ``seq_lens[b] - 1``, attends to its first ``seq_lens[b]`` keys and is rotated with that slot's table row."""
+        ``seq_lens[b] - 1``, attends to its first ``seq_lens[b]`` keys and is rotated with that slot's table row.
+        ``page_table`` ([B, max_pages] int32) + ``page_size``: the layers' K_cache / V_cache are page pools
+        [pages, NKV, page_size, D]; needs ``seq_lens`` and ``S == max_pages * page_size``."""
         if len(layers) != self.L:
             raise ValueError(f"expected {self.L} layers, got {len(layers)}")
         _require(hidden, "hidden", (self.B, self.H))
@@ -312,6 +338,25 @@ class Qwen3DecodeStackSm100Kernel(BaseKernel):
                 if t.dim() != 2 or t.shape[1] != self.D or t.shape[0] <= position:
                     raise ValueError(f"{name} must be [> {position}, {self.D}], got {tuple(t.shape)}")
                 _require(t, name, t.shape)
+        if page_table is not None:
+            if seq_lens is None or page_size is None:
+                raise ValueError("paged caches need seq_lens and page_size")
+            _require(page_table, "page_table", (self.B, page_table.shape[1]), dtype=torch.int32)
+            if self.S != page_table.shape[1] * page_size:
+                raise ValueError(f"seq_len ({self.S}) must equal max_pages * page_size")
+            table = self._layer_table(layers, page_size)
+            ws = self.workspace(hidden.device)
+            if out is None:
+                out = torch.empty_like(hidden)
+            _lib.check(
+                self._lib.ezb_qwen3_decode_stack_paged(
+                    hidden.data_ptr(), out.data_ptr(), table, self.L, cos.data_ptr() if cos is not None else None,
+                    sin.data_ptr() if sin is not None else None, seq_lens.data_ptr(), page_table.data_ptr(), page_size,
+                    page_table.shape[1], ws.data_ptr(), ws.numel(), self.B, self.H, self.I, self.NH, self.NKV, self.D,
+                    self.rms_eps, _stream(),
+                )
+            )
+            return out
         table = self._layer_table(layers)
         ws = self.workspace(hidden.device)
         if out is None:

@@ -246,6 +246,24 @@ int ezb_qwen3_decode_stack(const void* hidden, void* out, const ezb_layer_t* lay
  * instead of a hand-kept constant. */
 unsigned long long ezb_launch_count(void);
 
+/* Paged KV caches (the format a serving stack hands over; the reference's caches
+ * are contiguous [B, NKV, S, D], ezops/ops/attn_decode.py:52-56): K and V live
+ * in page pools [pages, NKV, page_size, D]; page_table [B, max_pages] (device
+ * int32) names the pool page of every page_size keys of a row, seq_lens [B]
+ * the valid lengths.  page_size is a power of two >= 64, so a 64-key tile of
+ * the kernel never straddles pages and paging costs one table lookup per tile.
+ * Workspace as for S = max_pages * page_size.  The stack form takes the pools
+ * through ezb_layer_t.K_cache / V_cache (one pool pair per layer, one page
+ * table for all layers); the new token of row b goes to the page slot of
+ * position seq_lens[b] - 1, which the caller has mapped. */
+int ezb_attn_decode_paged(const void* Q, const void* K_pool, const void* V_pool, const int* page_table, void* Out,
+                          void* workspace, size_t workspace_bytes, int B, int H, int NKV, int max_pages, int page_size, int D,
+                          const int* seq_lens, ezb_stream_t stream);
+int ezb_qwen3_decode_stack_paged(const void* hidden, void* out, const ezb_layer_t* layers, int n_layers, const void* rope_cos,
+                                 const void* rope_sin, const int* seq_lens, const int* page_table, int page_size,
+                                 int max_pages, void* workspace, size_t workspace_bytes, int B, int H, int I, int NH, int NKV,
+                                 int D, float eps, ezb_stream_t stream);
+
 /* The stack of layers, tensor parallel with the exchange fused into the kernels:
  * ezb_qwen3_decode_stack on this rank's shards (as ezb_qwen3_decode_layer_tp_fused
  * takes them), one call for all layers.  A layer's second sum is folded into

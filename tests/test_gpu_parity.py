@@ -628,3 +628,70 @@ def test_decode_stack_with_per_row_lengths(ez, batch, lens):
             assert torch.allclose(L["K_cache"][b][:, n - 1].cpu().float(), R["K_cache"][b][:, n - 1].float(), atol=6e-2, rtol=2e-2)
     again = op(hid.cuda(), dl, cos.cuda(), sin.cuda())
     assert torch.equal(again, got)
+
+
+# ------------------------------------------------------------------ paged KV caches ---
+def _to_pages(cache, page_size, perm, extra_pages=3):
+    """Contiguous cache [B, NKV, S, D] -> (pool [pages, NKV, P, D], page_table [B, S/P]) with shuffled page ids."""
+    B, NKV, S, D = cache.shape
+    n = S // page_size
+    pool = torch.randn(B * n + extra_pages, NKV, page_size, D, dtype=cache.dtype)  # unmapped pages hold noise
+    table = perm[: B * n].view(B, n).to(torch.int32)
+    for b in range(B):
+        for i in range(n):
+            pool[table[b, i]] = cache[b, :, i * page_size:(i + 1) * page_size]
+    return pool, table
+
+
+def _from_pages(pool, table, page_size):
+    B, n = table.shape
+    return torch.stack([torch.cat([pool[table[b, i]] for i in range(n)], dim=1) for b in range(B)])
+
+
+@pytest.mark.parametrize("page_size", [64, 256])
+def test_paged_attention_matches_contiguous(ez, page_size):
+    from ezops_b200 import workloads as wl
+
+    B, H, NKV, D, S = 5, 16, 4, 128, 1024
+    (Q, K, V), _ = wl.attn_decode_inputs(batch=B, num_heads=H, num_kv_heads=NKV, head_dim=D, max_len=S, min_len=1)
+    lens = [1024, 1, 65, 700, 256]
+    perm = torch.randperm(B * (S // page_size) + 3, generator=torch.Generator().manual_seed(3))
+    Kp, table = _to_pages(K, page_size, perm)
+    Vp, _ = _to_pages(V, page_size, perm)
+    op = ez.AttnDecodeOp(B, H, S, D, backend="cuda", num_kv_heads=NKV, seq_lens=lens)
+    want = op(*dev(Q, K, V))
+    lens_d = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    got = op._kernel.call_paged(Q.cuda(), Kp.cuda(), Vp.cuda(), table.cuda(), lens_d, page_size)
+    assert torch.equal(got, want)  # same kernel, same tiles, only the addresses differ
+    assert torch.allclose(got.cpu().float(), orc.attn_decode_ref(Q, K, V, seq_lens=lens).float(), atol=1e-2, rtol=1e-2)
+
+
+def test_paged_decode_stack_matches_the_contiguous_stack(ez):
+    import copy
+
+    from ezops_b200 import workloads as wl
+
+    sh, B, S, NL, P = wl.QWEN3_VL_2B, 3, 512, 2, 128
+    lens = [512, 130, 7]
+    hid, layers, cos, sin = wl.decode_stack_inputs(sh, B, S, NL)
+    ref_layers = copy.deepcopy(layers)
+    ref = orc.qwen3_decode_stack_ref(hid, ref_layers, sh.num_heads, sh.num_kv_heads, sh.head_dim, cos, sin, seq_lens=lens)
+    perm = torch.randperm(B * (S // P) + 3, generator=torch.Generator().manual_seed(5))
+    paged, table = [], None
+    for L in layers:
+        Kp, table = _to_pages(L["K_cache"], P, perm)
+        Vp, _ = _to_pages(L["V_cache"], P, perm)
+        paged.append({**L, "K_cache": Kp, "V_cache": Vp})
+    op = ez.Qwen3DecodeStackOp(B, S, sh.hidden, sh.inter, sh.num_heads, sh.head_dim, NL, backend="cuda", num_kv_heads=sh.num_kv_heads)
+    dl = _stack_to_device(paged)
+    lens_d = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    got = op._kernel(hid.cuda(), dl, cos.cuda(), sin.cuda(), seq_lens=lens_d, page_table=table.cuda(), page_size=P)
+    assert rel_fro(got, ref) < 1e-2, rel_fro(got, ref)
+    contiguous = ez.Qwen3DecodeStackOp(B, S, sh.hidden, sh.inter, sh.num_heads, sh.head_dim, NL, backend="cuda",
+                                       num_kv_heads=sh.num_kv_heads, seq_lens=lens)
+    cl = _stack_to_device(layers)
+    assert torch.equal(got, contiguous(hid.cuda(), cl, cos.cuda(), sin.cuda()))
+    for Lp, Lc in zip(dl, cl):  # the new tokens landed in the right pages, nothing else moved
+        assert torch.equal(_from_pages(Lp["K_cache"].cpu(), table, P), Lc["K_cache"].cpu())
+        assert torch.equal(_from_pages(Lp["V_cache"].cpu(), table, P), Lc["V_cache"].cpu())
+
