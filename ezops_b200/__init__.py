@@ -10,8 +10,11 @@ from .ops import (
     Op,
     Qwen3DecodeStackOp,
     Qwen3DenseDecodeOp,
+    ReduceOp,
     RmsNormOp,
     RooflineResult,
+    SoftmaxOp,
+    VectorAddOp,
 )
 from .registry import get_kernel, list_backends, list_ops, register_kernel
 
@@ -23,8 +26,11 @@ __all__ = [
     "Op",
     "Qwen3DecodeStackOp",
     "Qwen3DenseDecodeOp",
+    "ReduceOp",
     "RmsNormOp",
     "RooflineResult",
+    "SoftmaxOp",
+    "VectorAddOp",
     "get_kernel",
     "list_backends",
     "list_ops",

@@ -74,6 +74,10 @@ SIGNATURES = {
     "ezb_qwen3_decode_stack_tp_fused_workspace_bytes": (c_size_t, [c_int] * 7),
     "ezb_qwen3_decode_stack_tp_fused": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                                 c_size_t, POINTER(c_void_p)] + [c_int] * 9 + [c_float, c_void_p]),
+    "ezb_vector_add_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p]),
+    "ezb_softmax_f32": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "ezb_reduce_workspace_bytes": (c_size_t, []),
+    "ezb_reduce_sum_f32": (c_int, [c_void_p, c_void_p, c_longlong, c_void_p, c_size_t, c_void_p]),
     "ezb_launch_count": (ctypes.c_ulonglong, []),
     "ezb_hbm_stream": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_float, c_int, c_int, c_void_p]),
     "ezb_tp_comm_bytes": (c_size_t, [c_int, c_int]),

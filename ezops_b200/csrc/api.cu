@@ -703,6 +703,30 @@ int ezb_qwen3_decode_layer_tp_ffn(const void* hidden, const float* summed_o, con
     return EZB_OK;
 }
 
+int ezb_vector_add_f32(const float* A, const float* B, float* C, long long n, ezb_stream_t stream) {
+    EZB_REQUIRE(A && B && C && n >= 1, "null pointer or empty vector");
+    EZB_CUDA_TRY(launch_vector_add_f32(A, B, C, n, static_cast<cudaStream_t>(stream)));
+    return EZB_OK;
+}
+
+int ezb_softmax_f32(const float* X, float* Out, int rows, int dim, ezb_stream_t stream) {
+    EZB_REQUIRE(X && Out && rows >= 1 && dim >= 1, "null pointer or empty matrix");
+    EZB_CUDA_TRY(launch_softmax_f32(X, Out, rows, dim, static_cast<cudaStream_t>(stream)));
+    return EZB_OK;
+}
+
+size_t ezb_reduce_workspace_bytes(void) { return reduce_workspace_bytes(); }
+
+int ezb_reduce_sum_f32(const float* A, float* Out, long long n, void* workspace, size_t workspace_bytes, ezb_stream_t stream) {
+    EZB_REQUIRE(A && Out && n >= 1, "null pointer or empty vector");
+    if (!workspace || workspace_bytes < reduce_workspace_bytes()) {
+        set_last_message("workspace missing or smaller than ezb_reduce_workspace_bytes()");
+        return EZB_ERR_WORKSPACE;
+    }
+    EZB_CUDA_TRY(launch_reduce_sum_f32(A, Out, n, workspace, static_cast<cudaStream_t>(stream)));
+    return EZB_OK;
+}
+
 unsigned long long ezb_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int ezb_hbm_stream(int op, const void* b, const void* c, void* a, long long n_vec4, float scalar, int block_size,

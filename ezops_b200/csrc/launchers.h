@@ -141,5 +141,11 @@ cudaError_t launch_attn_decode(const AttnArgs& a, cudaStream_t stream);
 cudaError_t launch_hbm_stream(int op, const void* b, const void* c, void* a, long long n_vec4, float s, int block,
                               int blocks_per_sm, float* sink, cudaStream_t stream);
 
+// The reference's teaching operators (tutorial_ops.cu).
+cudaError_t launch_vector_add_f32(const float* A, const float* B, float* C, long long n, cudaStream_t stream);
+cudaError_t launch_softmax_f32(const float* X, float* Out, int rows, int dim, cudaStream_t stream);
+size_t reduce_workspace_bytes();  // zero-filled once by the caller
+cudaError_t launch_reduce_sum_f32(const float* A, float* Out, long long n, void* workspace, cudaStream_t stream);
+
 }  // namespace ezb
 

@@ -370,3 +370,53 @@ class Qwen3DecodeStackSm100Kernel(BaseKernel):
         )
         return out
 
+
+# ------------------------------------------------------------ teaching operators ---
+def _require_f32(t: torch.Tensor, name: str, shape) -> None:
+    _require(t, name, shape, dtype=torch.float32)
+
+
+@register_kernel("vector_add", "cuda")
+class VectorAddSm100Kernel(BaseKernel):
+    """C = A + B, fp32 (constructor contract: ezops/ops/vector_add.py:14-15)."""
+
+    def __init__(self, n: int):
+        if n < 1:
+            raise ValueError(f"n ({n}) must be positive")
+        self.n, self._lib = n, _lib.load()
+
+    def __call__(self, A, B, C) -> None:
+        for name, t in (("A", A), ("B", B), ("C", C)):
+            _require_f32(t, name, (self.n,))
+        _lib.check(self._lib.ezb_vector_add_f32(A.data_ptr(), B.data_ptr(), C.data_ptr(), self.n, _stream()))
+
+
+@register_kernel("softmax", "cuda")
+class SoftmaxSm100Kernel(BaseKernel):
+    """Row softmax, fp32 (constructor contract: ezops/ops/softmax.py:19-20)."""
+
+    def __init__(self, batch_size: int, dim: int):
+        if batch_size < 1 or dim < 1:
+            raise ValueError("batch_size and dim must be positive")
+        self.rows, self.dim, self._lib = batch_size, dim, _lib.load()
+
+    def __call__(self, X, Out) -> None:
+        _require_f32(X, "X", (self.rows, self.dim)); _require_f32(Out, "Out", (self.rows, self.dim))
+        _lib.check(self._lib.ezb_softmax_f32(X.data_ptr(), Out.data_ptr(), self.rows, self.dim, _stream()))
+
+
+@register_kernel("reduce", "cuda")
+class ReduceSm100Kernel(BaseKernel):
+    """Sum of an fp32 vector into Out[0], bit-reproducible (constructor contract: ezops/ops/reduce.py:17-18)."""
+
+    def __init__(self, n: int):
+        if n < 1:
+            raise ValueError(f"n ({n}) must be positive")
+        self.n, self._lib, self._ws = n, _lib.load(), None
+
+    def __call__(self, A, Out) -> None:
+        _require_f32(A, "A", (self.n,)); _require_f32(Out, "Out", (1,))
+        if self._ws is None or self._ws.device != A.device:
+            self._ws = _zeros_bytes(self._lib.ezb_reduce_workspace_bytes(), A.device)
+        _lib.check(self._lib.ezb_reduce_sum_f32(A.data_ptr(), Out.data_ptr(), self.n, self._ws.data_ptr(), self._ws.numel(), _stream()))
+

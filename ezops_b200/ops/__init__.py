@@ -6,6 +6,7 @@ from .gemv import GemvOp
 from .qwen3_decode_stack import Qwen3DecodeStackOp
 from .qwen3_dense_decode import Qwen3DenseDecodeOp
 from .rmsnorm import RmsNormOp
+from .tutorial import ReduceOp, SoftmaxOp, VectorAddOp
 from .utils.roofline import RooflineResult
 
 __all__ = [
@@ -16,6 +17,9 @@ __all__ = [
     "Op",
     "Qwen3DecodeStackOp",
     "Qwen3DenseDecodeOp",
+    "ReduceOp",
     "RmsNormOp",
     "RooflineResult",
+    "SoftmaxOp",
+    "VectorAddOp",
 ]

@@ -240,6 +240,19 @@ int ezb_qwen3_decode_stack(const void* hidden, void* out, const ezb_layer_t* lay
                            size_t workspace_bytes, int B, int S, int H, int I, int NH, int NKV, int D, float eps,
                            ezb_stream_t stream);
 
+/* The reference's three teaching operators, for API completeness.
+ * C = A + B over n fp32 elements (ezops/ops/vector_add.py:19-30;
+ * kernels/vector_add/vector_add_cu.cu).  Softmax over the last dimension of an
+ * fp32 [rows, dim] matrix (ezops/ops/softmax.py:24-36): one CTA per row, the
+ * row staged in shared memory when dim <= 12288.  Sum of n fp32 elements into
+ * Out[0] (ezops/ops/reduce.py:23-33): per-CTA partial sums, added in CTA order
+ * by the last CTA to finish, so two calls give the same bits; the workspace
+ * (ezb_reduce_workspace_bytes(), zero-filled once) holds the partials. */
+int ezb_vector_add_f32(const float* A, const float* B, float* C, long long n, ezb_stream_t stream);
+int ezb_softmax_f32(const float* X, float* Out, int rows, int dim, ezb_stream_t stream);
+size_t ezb_reduce_workspace_bytes(void);
+int ezb_reduce_sum_f32(const float* A, float* Out, long long n, void* workspace, size_t workspace_bytes, ezb_stream_t stream);
+
 /* Kernel launches issued by the library in this process so far (every kernel of
  * the library goes through one launch helper).  A diagnostic with no
  * counterpart in the reference: benchmarks report launches per step from it
