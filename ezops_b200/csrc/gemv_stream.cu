@@ -10,7 +10,7 @@
 //     rows padded by 16 bytes so that ldmatrix is bank-conflict free), completion
 //     counted on an mbarrier per stage; consumers hand stages back through a
 //     second mbarrier per stage;
-//   * four consumer warps split the k range of every stage between them and
+//   * eight consumer warps split the k range of every stage between them and
 //     feed mma.sync m16n8k16 (weights as the 16-row A operand, activations as
 //     the 8-wide B operand, batch padded to a multiple of 8), then combine
 //     their partial tiles through shared memory in a fixed order, which keeps
@@ -18,9 +18,10 @@
 //   * the activation block stays resident in shared memory when it fits (and
 //     can then be RMS-normalised in the prologue); otherwise its k-chunks ride
 //     along in every stage;
-//   * programmatic dependent launch: the first weight stages are requested
+//   * programmatic dependent launch: the first weight stage is requested
 //     before griddepcontrol.wait, because weights never depend on the kernel in
-//     front; only then are activations read.
+//     front; only then are activations read; once its own requests are out the
+//     producer asks L2 for the head of the next kernel's weights.
 // Every mbarrier wait is bounded (see mbar_wait_bounded).
 //
 // Two kernels share this structure:
@@ -28,7 +29,9 @@
 //                       the 8-wide B operand, so a stage is 8 whole weight rows
 //                       (up to 4096 elements = 8 KB per bulk copy, the size at
 //                       which the TMA unit reaches its streaming rate) and the
-//                       batch rows form the A operand;
+//                       batch rows form the A operand; template flags compile in
+//                       the tensor-parallel exchange (LINK) and fix the batch-1
+//                       activation staging at compile time (SINGLE);
 //   gemv_stream_kernel  every other case (batch up to 64, activations streamed
 //                       or resident): weights are the 16-row A operand, stages
 //                       are [16 rows x kc].
