@@ -15,9 +15,14 @@
 // and writes the bf16 output.  No spin waits anywhere.
 //
 // Decode-layer mode (fuse_new_token): q, k, v of the token being decoded come
-// straight from the fused QKV projection output; q and k get their unit-weight
-// RMSNorm over the head here, and the CTA whose split holds cache slot S-1
-// writes the new k and v into the cache before it streams that slot.
+// straight from the fused QKV projection output; q and k get their RMSNorm over
+// the head here (optionally with a weight and the rotary embedding, fp32 with one
+// rounding), and the CTA whose split holds the token's cache slot (S-1, or the
+// row's own length - 1 when per-row lengths are given) writes the new k and v
+// into the cache and patches them into its shared-memory tile.
+// The caches are contiguous [B, NKV, S, D] or page pools addressed through a page
+// table (pages of a power-of-two number of keys >= 64, so a tile never straddles
+// pages).
 #include "launchers.h"
 
 namespace ezb {

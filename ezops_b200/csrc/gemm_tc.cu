@@ -21,7 +21,10 @@
 //     32 tiles for 148 SMs).  A CTA that covers only part of a tile's K range
 //     stores its fp32 partial tile in the workspace; the last contributor of the
 //     tile (one atomic ticket, no waiting) adds the partials in CTA order, so
-//     results are bit-reproducible.
+//     results are bit-reproducible.  A CTA works through its shared tiles first
+//     and its whole tiles after them, so that fix-up overlaps their streaming.
+//   * the LINK instance pushes its fp32 results into the tensor-parallel peers'
+//     inboxes instead of storing them (see TpLink).
 // Every mbarrier wait is bounded; on a time-out the CTA records a fault, stops
 // issuing work, waits (bounded) for copies in flight, frees its tensor memory
 // and returns.
