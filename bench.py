@@ -93,7 +93,7 @@ class ClockSampler:
     }
     NOTED = {0x0000000000000004: "sw_power_cap"}
 
-    def __init__(self, index: int, period_s: float = 0.004):
+    def __init__(self, index: int, period_s: float = 0.0004):
         self.index, self.period = index, period_s
         self.samples, self.reasons = [], set()
         self.max_mhz = None
@@ -203,6 +203,19 @@ def run_reference_arm(args, shape, total_bytes):
     print(json.dumps(line), flush=True)
 
 
+def resolve_calls(args, n):
+    """How the timed steps are issued: 'layer' (one C call per step) or 'stack' (multi-layer calls).  The rule is
+    shared by both arms so that their ``config`` objects are equal."""
+    if getattr(args, "stack", False) or args.calls == "stack":
+        return "stack"
+    if args.calls == "layer":
+        return "layer"
+    exchange = args.exchange
+    if exchange == "auto":
+        exchange = "fused" if args.batch <= 8 else "nccl"
+    return "stack" if n > 1 and exchange == "fused" else "layer"
+
+
 def workload_config(args, shape, n):
     return {
         "workload": f"{shape.name} dense decode layer, batch {args.batch}, kv_len {args.seq_len}, bf16, tp{n}",
@@ -210,14 +223,29 @@ def workload_config(args, shape, n):
         "parallelism": f"tp{n}",
         "cache_policy": f"inputs larger than L2: steps rotate over {NUM_WEIGHT_SETS * n} weight+KV sets per GPU",
         "pdl_across_calls": not getattr(args, "no_cross_call_pdl", False),
-        "calls": "one multi-layer call per graph" if getattr(args, "stack", False) else "one call per layer",
+        "calls": "one multi-layer call per graph" if resolve_calls(args, n) == "stack" else "one call per layer",
     }
 
 
-# DRAM traffic of one launch of the roofline leg's kernel (dram__bytes_read.sum + dram__bytes_write.sum)
-# from the ncu capture summarised in profiles/gemv_rows8_gate_up_sized_b1_ncu_full.md; the key is
-# (weight rows, weight columns, batch).
-NCU_TRAFFIC_BYTES = {(24576, 4096, 1): 201_408_512 + 3_995_648}
+def ncu_traffic(kernel: str, rows: int, cols: int, batch: int):
+    """DRAM bytes (read + write) of one launch, from the ncu captures summarised under profiles/ (the table
+    profiles/ncu_dram_traffic.json names the summary each entry comes from).  An entry for the same kernel, batch
+    and row length but another number of rows is scaled by the rows (traffic is the weight stream: it grows in
+    proportion); returns (bytes or None, how)."""
+    path = ROOT / "profiles" / "ncu_dram_traffic.json"
+    try:
+        table = json.loads(path.read_text())["entries"]
+    except Exception:
+        return None, "no table"
+    same = [e for e in table if e["kernel"] == kernel and e["cols"] == cols and e["batch"] == batch]
+    for e in same:
+        if e["rows"] == rows:
+            return e["dram_read_bytes"] + e["dram_write_bytes"], f"ncu capture ({e['summary']})"
+    if same:
+        e = same[0]
+        scaled = (e["dram_read_bytes"] + e["dram_write_bytes"]) * rows / e["rows"]
+        return int(scaled), f"scaled by rows from the ncu capture at {e['rows']} rows ({e['summary']})"
+    return None, "no capture of this shape"
 
 
 def roofline_leg(sets, nsets, hidden0, B, H, device, n_roof):
@@ -250,10 +278,11 @@ def roofline_leg(sets, nsets, hidden0, B, H, device, n_roof):
     launch_s = r0.elapsed_time(r1) * 1e-3 / n_roof
     kernel_bytes = 2 * (rows_local * H + B * H + B * rows_local)
     achieved = kernel_bytes / launch_s / 1e9
+    traffic, traffic_how = ncu_traffic("gemv_rows8_kernel" if B <= 8 else "gemm_tc_kernel", rows_local, H, B)
     roofline = {
         "bound": "hbm", "kernel": "gemv_rows8_kernel" if B <= 8 else "gemm_tc_kernel", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
         "frac": achieved / peaks["hbm_gbs"], "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs, burst copy)",
-        "traffic": NCU_TRAFFIC_BYTES.get((rows_local, H, B)), "bytes_per_launch": kernel_bytes, "us_per_launch": launch_s * 1e6,
+        "traffic": traffic, "traffic_source": traffic_how, "bytes_per_launch": kernel_bytes, "us_per_launch": launch_s * 1e6,
         "workload": f"W [{rows_local}, {H}] bf16 (gate/up-sized), batch {B}, {n_roof} back-to-back launches over {nsets} weights",
     }
     return roofline
@@ -302,7 +331,7 @@ def main():
     # always rotates over more than four times the L2 capacity) ----
     nsets = NUM_WEIGHT_SETS * tp
     gen = torch.Generator(device=device)
-    sets = []
+    sets, full0 = [], None
     for i in range(nsets):
         gen.manual_seed(1000 + i)  # same seed on every rank: consistent shards
         rn = lambda *s, std=1.0: (torch.randn(*s, generator=gen, device=device, dtype=torch.float32) * std).to(torch.bfloat16)
@@ -310,6 +339,8 @@ def main():
         Wgu, Wd = rn(2 * I, H, std=0.02), rn(H, I, std=0.02)
         Kc, Vc = rn(B, NKV, S, D), rn(B, NKV, S, D)
         if tp > 1:
+            if i == 0 and rank == 0:
+                full0 = (Kc, Vc, Wqkv, Wo, Wgu, Wd)  # the unsharded layer, for the check against the torch reference
             Wqkv, Wo, Wgu, Wd = tpm.shard_layer_weights(Wqkv, Wo, Wgu, Wd, NH, NKV, D, tp, rank)
             Kc, Vc = tpm.shard_kv_cache(Kc, tp, rank), tpm.shard_kv_cache(Vc, tp, rank)
         sets.append((Kc, Vc, Wqkv, Wo, Wgu, Wd))
@@ -319,8 +350,9 @@ def main():
 
     if args.roofline_only:
         print(json.dumps({"roofline": roofline_leg(sets, nsets, hidden0, B, H, device, 4)}), flush=True)
-        os._exit(0)
+        return
 
+    lay, stacks, e2e_graphs = None, {}, None
     if tp == 1:
         op = ez.Qwen3DenseDecodeOp(B, S, H, I, NH, D, backend="cuda", num_kv_heads=NKV)
         kernel = op._kernel
@@ -342,15 +374,6 @@ def main():
         def layer(hidden, wset, out):
             return lay(hidden, *wset, out=out)
 
-    # quick self-check of one step against the torch reference on this GPU (tp=1)
-    check = None
-    if tp == 1:
-        ref_op = ez.Qwen3DenseDecodeOp(B, S, H, I, NH, D, backend="ref", num_kv_heads=NKV)
-        Kc, Vc = sets[0][0].clone(), sets[0][1].clone()
-        ref = ref_op._ref_forward(hidden0, Kc, Vc, *sets[0][2:])
-        got = layer(hidden0, (sets[0][0].clone(), sets[0][1].clone()) + sets[0][2:], torch.empty_like(hidden0))
-        check = bool(op.check(got, ref))
-
     bufs = [torch.empty_like(hidden0) for _ in range(2)]
 
     def run_steps(n, first=0):
@@ -367,7 +390,7 @@ def main():
     if args.stack:
         names = ("K_cache", "V_cache", "Wqkv", "Wo", "Wgu", "Wd")
         as_layers = [dict(zip(names, wset)) for wset in sets]
-        stacks = {}  # multi-layer executors by layer count (created in the same order on every rank)
+        # `stacks`: multi-layer executors by layer count (created in the same order on every rank)
 
         def stack_for(n):
             if n not in stacks:
@@ -388,6 +411,20 @@ def main():
         if world > 1:
             dist.barrier()
             torch.cuda.synchronize()
+
+    # One step checked against the torch reference on the unsharded weights (every rank takes part in the step,
+    # rank 0 holds the reference): the correctness bit of this line, at every N.
+    ref_op = ez.Qwen3DenseDecodeOp(B, S, H, I, NH, D, backend="ref", num_kv_heads=NKV)
+    got = layer(hidden0, (sets[0][0].clone(), sets[0][1].clone()) + sets[0][2:], torch.empty_like(hidden0))
+    sync_all()
+    check = None
+    if rank == 0:
+        ref_set = sets[0] if tp == 1 else full0
+        ref = ref_op._ref_forward(hidden0, ref_set[0].clone(), ref_set[1].clone(), *ref_set[2:])
+        check = bool(ref_op.check(got, ref))
+        del ref
+    full0 = None
+    torch.cuda.empty_cache()
 
     run_steps(warmup)
     sync_all()
@@ -419,16 +456,27 @@ def main():
             torch.cuda.synchronize()
 
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sync_all()
-    with ClockSampler(local_rank) as clocks:
-        t0.record()
+
+    def issue_steps(n):
         if graph is not None:
-            for _ in range(steps // unroll):
+            for _ in range(n // unroll):
                 graph.replay()
         else:
-            run_steps(steps)
+            run_steps(n)
+
+    # The timed steps follow untimed steps of the same kind on the stream with no host synchronisation in between:
+    # the ranks are then coupled on the device (by the exchange inside the steps) before t0, so host launch skew
+    # between the processes is not charged to the first timed step; the clock sampler sees the same load before
+    # and during the timed region (a 20-step region alone is shorter than one NVML query).
+    lead_in = max(unroll, (max(200, warmup) + unroll - 1) // unroll * unroll)
+    sync_all()
+    with ClockSampler(local_rank) as clocks:
+        issue_steps(lead_in)
+        t0.record()
+        issue_steps(steps)
         t1.record()
-        sync_all()
+        torch.cuda.synchronize()
+    sync_all()
     elapsed_ms = torch.tensor([t0.elapsed_time(t1)], device=device)
     if world > 1:
         dist.all_reduce(elapsed_ms, op=dist.ReduceOp.MAX)
@@ -455,7 +503,6 @@ def main():
 
         # One CUDA graph per weight set holding the whole step (copy in, the operator call, copy out), as a
         # serving loop would keep it: a step then costs one graph launch and one stream synchronisation.
-        e2e_graphs = None
         if not args.no_graph:
             try:
                 for i in range(nsets):
@@ -500,8 +547,19 @@ def main():
                "launch": "one CUDA graph per step (copy in, operator call, copy out)" if e2e_graphs is not None else "eager",
                "note": "weights and KV cache are resident device state; per-step input/output cross PCIe"}
 
-    roofline = roofline_leg(sets, nsets, hidden0, B, H, device, 200)
-    peaks, _ = measured_peaks()
+    peaks, peak_kind = measured_peaks()
+    gemv_leg = roofline_leg(sets, nsets, hidden0, B, H, device, 200)
+    if tp == 1 and launches_per_step == 1:
+        # One launch is the whole step: the dominant kernel's duration is the step time measured above.
+        traffic, traffic_how = ncu_traffic("decode_layer_b1_kernel", S, H, B)
+        roofline = {
+            "bound": "hbm", "kernel": "decode_layer_b1_kernel", "achieved": value, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+            "frac": value / peaks["hbm_gbs"], "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs, burst copy)",
+            "traffic": traffic, "traffic_source": traffic_how, "bytes_per_launch": total_bytes, "us_per_launch": ms_per_step * 1e3,
+            "workload": f"the whole layer in one launch (weights + KV once), {steps} launches of the timed region",
+        }
+    else:
+        roofline = gemv_leg
 
     # ---- CPU oracle beside it (rank 0, single-GPU run only) ----
     cpu = None
@@ -519,19 +577,29 @@ def main():
             "config": workload_config(args, shape, world),
             "algorithmic_bytes_per_step": total_bytes,
             "frac_of_8tbs": value / 8000.0, "frac_of_measured_hbm": value / peaks["hbm_gbs"],
-            "timing": f"CUDA events around {steps} steps " + (f"replayed from a CUDA graph of {unroll} steps" if graph is not None else "launched eagerly") + ", max over ranks",
+            "timing": f"CUDA events around {steps} steps " + (f"replayed from a CUDA graph of {unroll} steps" if graph is not None else "launched eagerly")
+                      + f", directly behind {lead_in} untimed steps on the same stream; max over ranks",
             "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": int(round(steps * launches_per_step)),
-            "roofline": roofline, "cpu_baseline": cpu, "check_vs_torch_ref": check, "device_status": status,
+            "roofline": roofline, "weight_streaming_leg": gemv_leg, "cpu_baseline": cpu, "check_vs_torch_ref": check, "device_status": status,
         }
         print(json.dumps(line), flush=True)
     sys.stdout.flush()
     sys.stderr.flush()
+    # Leave the normal way (interpreter exit hooks run).  With several ranks, first drop everything that holds NCCL
+    # kernels or peer mappings, then destroy the process group; a guard ends the process if that teardown blocks.
+    graph = e2e_graphs = None
+    torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
         torch.cuda.synchronize()
-    # Leave without tearing NCCL down: destroying the communicator while CUDA graphs that captured
-    # its kernels are still alive was seen to block for minutes.  Everything is already printed.
-    os._exit(0)
+        for obj in [lay] + list(stacks.values()):
+            if obj is not None and hasattr(obj, "close"):
+                obj.close()
+        guard = threading.Timer(90.0, lambda: (sys.stderr.write("[bench] process-group teardown blocked; leaving\n"), os._exit(0)))
+        guard.daemon = True
+        guard.start()
+        dist.destroy_process_group()
+        guard.cancel()
 
 
 def _watchdog(signum, frame):  # a benchmark must never sit in a hang until the caller's limit
@@ -543,3 +611,4 @@ if __name__ == "__main__":
     signal.signal(signal.SIGALRM, _watchdog)
     signal.alarm(int(os.environ.get("EZB_BENCH_LIMIT_S", "900")))
     main()
+    signal.alarm(0)

@@ -37,6 +37,7 @@ TUNE = {
     "gemv_window": 11,
     "l2_prefetch_attn_kb": 12,
     "tc": 13, "attn_waves_uniform": 14, "tp_poll_all": 15, "tp_pull": 16,
+    "mega": 17, "mega_l2_stages": 18, "wait_limit_ms": 19,
 }
 
 # name -> (restype, argtypes); every symbol include/ezb200.h declares

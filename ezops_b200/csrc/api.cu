@@ -98,11 +98,15 @@ static const int kTuningDefaults[EZB_TUNE_COUNT] = {
     3,    // EZB_TUNE_ATTN_WAVES_UNIFORM
     0,    // EZB_TUNE_TP_POLL_ALL
     0,    // EZB_TUNE_TP_PULL
+    1,    // EZB_TUNE_MEGA
+    6,    // EZB_TUNE_MEGA_L2_STAGES
+    1000, // EZB_TUNE_WAIT_LIMIT_MS
 };
 static const char* kTuningEnv[EZB_TUNE_COUNT] = {
     "EZB_TUNE_PDL",          "EZB_TUNE_GEMV_SMEM_KB",   "EZB_TUNE_GEMV_PREFETCH", "EZB_TUNE_GEMV_CTAS_PER_SM",
     "EZB_TUNE_ATTN_MIN_CHUNK", "EZB_TUNE_ATTN_WAVES", "EZB_TUNE_GEMV_KC", "EZB_TUNE_GEMV_ROWS8", "EZB_TUNE_PDL_ACROSS_CALLS", "EZB_TUNE_L2_PREFETCH", "EZB_TUNE_L2_PREFETCH_KB", "EZB_TUNE_GEMV_WINDOW", "EZB_TUNE_L2_PREFETCH_ATTN_KB", "EZB_TUNE_TC",
-    "EZB_TUNE_ATTN_WAVES_UNIFORM", "EZB_TUNE_TP_POLL_ALL", "EZB_TUNE_TP_PULL",
+    "EZB_TUNE_ATTN_WAVES_UNIFORM", "EZB_TUNE_TP_POLL_ALL", "EZB_TUNE_TP_PULL", "EZB_TUNE_MEGA", "EZB_TUNE_MEGA_L2_STAGES",
+    "EZB_TUNE_WAIT_LIMIT_MS",
 };
 
 static void tuning_init() {
@@ -120,6 +124,12 @@ int tuning(int key) {
     return (key >= 0 && key < EZB_TUNE_COUNT) ? g_tuning[key].load() : 0;
 }
 
+long long wait_limit_cycles() {
+    long long ms = tuning(EZB_TUNE_WAIT_LIMIT_MS);
+    if (ms < 1) ms = 1;
+    return ms * 2000000LL;
+}
+
 static size_t round256(size_t v) { return (v + 255) / 256 * 256; }
 
 // Carves the layer workspace.  The attention part comes first because it holds
@@ -128,6 +138,7 @@ struct LayerWorkspace {
     void* attn;
     void* tc;  // tensor-core path: split counters (zero between calls) and partial tiles; null at batch 1
     bf16 *qkv, *attn_out, *x2, *h, *xn;
+    void* mega;  // batch 1: barrier counters and slice records of the single-kernel layer (zero before first use)
     size_t total;
 };
 
@@ -159,6 +170,7 @@ static LayerWorkspace carve_layer_ws(void* base, int B, int S, int H, int I, int
     w.x2 = reinterpret_cast<bf16*>(take((size_t)B * H * 2));
     w.h = reinterpret_cast<bf16*>(take((size_t)B * I * 2));
     w.xn = reinterpret_cast<bf16*>(take((size_t)B * H * 2));
+    w.mega = (B == 1) ? take(decode_mega_workspace_bytes(NKV, D)) : nullptr;
     w.total = off;
     return w;
 }
@@ -567,6 +579,21 @@ size_t ezb_qwen3_decode_layer_workspace_bytes(int B, int S, int H, int I, int NH
 static int run_layer(const bf16* hid, bf16* Kc, bf16* Vc, const bf16* Wqkv, const bf16* Wo, const bf16* wgu, const bf16* Wd,
                      bf16* out, const LayerWorkspace& w, int B, int S, int H, int I, int NH, int NKV, int D, float eps,
                      const LayerExtras& ex, cudaStream_t stream) {
+    if (B == 1 && !ex.seq_lens && !ex.page_table && w.mega) {
+        // batch 1 on contiguous caches: the whole layer as one persistent kernel
+        MegaArgs m;
+        m.hidden = hid, m.out = out, m.Kc = Kc, m.Vc = Vc;
+        m.Wqkv = Wqkv, m.Wo = Wo, m.Wgu = wgu, m.Wd = Wd;
+        m.input_norm_w = ex.input_norm_w, m.post_norm_w = ex.post_norm_w, m.q_norm_w = ex.q_norm_w, m.k_norm_w = ex.k_norm_w;
+        m.rope_cos = ex.rope_cos, m.rope_sin = ex.rope_sin;
+        m.qkv = w.qkv, m.attn_out = w.attn_out, m.x2 = w.x2, m.h = w.h;
+        m.mega_workspace = w.mega;
+        m.S = S, m.H = H, m.I = I, m.NH = NH, m.NKV = NKV, m.D = D, m.eps = eps;
+        if (decode_mega_supported(m)) {
+            EZB_CUDA_TRY(launch_decode_mega(m, stream));
+            return EZB_OK;
+        }
+    }
     const int pf_kb = tuning(EZB_TUNE_L2_PREFETCH_KB);
     const int pf_attn_kb = tuning(EZB_TUNE_L2_PREFETCH_ATTN_KB);
     // attention is latency-bound: besides Wo it can pull the head of the gate/up rows; o_proj then pulls the rows after those

@@ -28,6 +28,7 @@ enum DeviceFault : unsigned int {
     FAULT_GEMV_DRAIN = 0x103,       // copies still in flight at exit
     FAULT_TC_ACC_WAIT = 0x104,      // tensor-memory accumulator hand-over never happened
     FAULT_AR_FLAG_WAIT = 0x201,     // a peer's partial result never arrived in the inbox
+    FAULT_MEGA_GRID_BARRIER = 0x400,  // + barrier index: a grid-wide barrier of the single-kernel layer never filled
 };
 
 __device__ __forceinline__ void report_fault(unsigned int* status, unsigned int code) {
@@ -209,6 +210,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Non-blocking probe of the phase with the given parity (try_wait may suspend the thread for a while).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
         : "r"(bar), "r"(parity)
@@ -408,6 +422,7 @@ void set_last_message(const char* msg);
 int sm_count();               // SMs of the current device (cached per device)
 int max_smem_optin();         // opt-in shared memory per block of the current device
 int tuning(int key);          // value of a tuning knob (see EZB_TUNE_* in ezb200.h)
+long long wait_limit_cycles();  // cycle budget of one device-side wait in the kernels that take it as a parameter
 unsigned int* status_ptr();   // device address of the status word on the current device (null on error)
 Trace trace_handle();         // tracing buffers of the current device (buf == null when disabled)
 void chain_begin();           // marks the next launch_pdl() of this thread as the first kernel of a call

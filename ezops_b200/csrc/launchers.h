@@ -137,6 +137,27 @@ size_t attn_counters_bytes(int B, int H, int NKV);  // leading part of the works
 int attn_chunk_keys(int B, int NKV, int S, bool ragged);  // keys per KV split chosen for this shape
 cudaError_t launch_attn_decode(const AttnArgs& a, cudaStream_t stream);
 
+// ------------------------------------------------- whole layer, batch 1 ---
+// The decode layer at batch 1 as one persistent kernel (decode_mega.cu).  `qkv`, `attn_out`, `x2`, `h` are the
+// activation rows of the layer workspace; `mega_workspace` (decode_mega_workspace_bytes(), zero before first use)
+// holds the grid-barrier counters and the attention slices' records.
+struct MegaArgs {
+    const bf16* hidden = nullptr;
+    bf16* out = nullptr;
+    bf16* Kc = nullptr;  // [1, NKV, S, D] contiguous; slot S-1 receives the new token
+    bf16* Vc = nullptr;
+    const bf16 *Wqkv = nullptr, *Wo = nullptr, *Wgu = nullptr, *Wd = nullptr;
+    const bf16 *input_norm_w = nullptr, *post_norm_w = nullptr, *q_norm_w = nullptr, *k_norm_w = nullptr;
+    const bf16 *rope_cos = nullptr, *rope_sin = nullptr;  // rows of the rotary tables for the token's position
+    bf16 *qkv = nullptr, *attn_out = nullptr, *x2 = nullptr, *h = nullptr;
+    void* mega_workspace = nullptr;
+    int S = 0, H = 0, I = 0, NH = 0, NKV = 0, D = 0;
+    float eps = 1e-6f;
+};
+bool decode_mega_supported(const MegaArgs& a);  // shape inside what the kernel covers on the current device (and switched on)
+size_t decode_mega_workspace_bytes(int NKV, int D);
+cudaError_t launch_decode_mega(const MegaArgs& a, cudaStream_t stream);
+
 // STREAM-style calibration kernels (hbm_stream.cu): op 0 read b, 1 write a, 2 copy b->a, 3 triad a = b + s*c.
 cudaError_t launch_hbm_stream(int op, const void* b, const void* c, void* a, long long n_vec4, float s, int block,
                               int blocks_per_sm, float* sink, cudaStream_t stream);
