@@ -37,7 +37,8 @@ TUNE = {
     "gemv_window": 11,
     "l2_prefetch_attn_kb": 12,
     "tc": 13, "attn_waves_uniform": 14, "tp_poll_all": 15, "tp_pull": 16,
-    "mega": 17, "mega_l2_stages": 18, "wait_limit_ms": 19,
+    "mega": 17, "mega_l2_stages": 18, "wait_limit_ms": 19, "mega_stages": 20, "mega_inflight": 21, "mega_gate": 22,
+    "tp_wait_limit_ms": 23,
 }
 
 # name -> (restype, argtypes); every symbol include/ezb200.h declares
@@ -65,10 +66,10 @@ SIGNATURES = {
     "ezb_qwen3_decode_layer_tp_attn": (c_int, [c_void_p] * 7 + [c_size_t] + [c_int] * 6 + [c_float, c_void_p]),
     "ezb_qwen3_decode_layer_tp_ffn": (c_int, [c_void_p] * 7 + [c_size_t] + [c_int] * 3 + [c_float, c_void_p]),
     "ezb_residual_add_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
-    "ezb_attn_decode_paged": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t] + [c_int] * 6
+    "ezb_attn_decode_paged": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t] + [c_int] * 7
                               + [c_void_p, c_void_p]),
     "ezb_qwen3_decode_stack_paged": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                                             c_void_p, c_size_t] + [c_int] * 6 + [c_float, c_void_p]),
+                                             c_int, c_void_p, c_size_t] + [c_int] * 6 + [c_float, c_void_p]),
     "ezb_qwen3_decode_stack_workspace_bytes": (c_size_t, [c_int] * 7),
     "ezb_qwen3_decode_stack": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_size_t]
                                + [c_int] * 7 + [c_float, c_void_p]),

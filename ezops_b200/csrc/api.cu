@@ -101,12 +101,17 @@ static const int kTuningDefaults[EZB_TUNE_COUNT] = {
     1,    // EZB_TUNE_MEGA
     6,    // EZB_TUNE_MEGA_L2_STAGES
     1000, // EZB_TUNE_WAIT_LIMIT_MS
+    0,    // EZB_TUNE_MEGA_STAGES
+    0,    // EZB_TUNE_MEGA_INFLIGHT
+    1,    // EZB_TUNE_MEGA_GATE
+    5000, // EZB_TUNE_TP_WAIT_LIMIT_MS
 };
 static const char* kTuningEnv[EZB_TUNE_COUNT] = {
     "EZB_TUNE_PDL",          "EZB_TUNE_GEMV_SMEM_KB",   "EZB_TUNE_GEMV_PREFETCH", "EZB_TUNE_GEMV_CTAS_PER_SM",
     "EZB_TUNE_ATTN_MIN_CHUNK", "EZB_TUNE_ATTN_WAVES", "EZB_TUNE_GEMV_KC", "EZB_TUNE_GEMV_ROWS8", "EZB_TUNE_PDL_ACROSS_CALLS", "EZB_TUNE_L2_PREFETCH", "EZB_TUNE_L2_PREFETCH_KB", "EZB_TUNE_GEMV_WINDOW", "EZB_TUNE_L2_PREFETCH_ATTN_KB", "EZB_TUNE_TC",
     "EZB_TUNE_ATTN_WAVES_UNIFORM", "EZB_TUNE_TP_POLL_ALL", "EZB_TUNE_TP_PULL", "EZB_TUNE_MEGA", "EZB_TUNE_MEGA_L2_STAGES",
-    "EZB_TUNE_WAIT_LIMIT_MS",
+    "EZB_TUNE_WAIT_LIMIT_MS", "EZB_TUNE_MEGA_STAGES", "EZB_TUNE_MEGA_INFLIGHT", "EZB_TUNE_MEGA_GATE",
+    "EZB_TUNE_TP_WAIT_LIMIT_MS",
 };
 
 static void tuning_init() {
@@ -289,7 +294,7 @@ struct LayerExtras {
     const int* seq_lens = nullptr;  // per-row valid lengths (device); the new token goes to slot len-1
     int rope_by_len = 0;            // rope_cos / rope_sin are table bases indexed by that slot
     const int* page_table = nullptr;  // paged caches (see AttnArgs)
-    int page_shift = 0, max_pages = 0;
+    int page_shift = 0, max_pages = 0, num_pages = 0;
 };
 static const LayerExtras kPlainLayer = {};
 
@@ -324,7 +329,7 @@ static cudaError_t launch_qkv_and_attention(const bf16* hidden, bf16* Kc, bf16* 
     a.eps = eps;
     a.q_norm_w = ex.q_norm_w, a.k_norm_w = ex.k_norm_w, a.rope_cos = ex.rope_cos, a.rope_sin = ex.rope_sin;
     a.seq_lens = ex.seq_lens, a.rope_by_len = ex.rope_by_len;
-    a.page_table = ex.page_table, a.page_shift = ex.page_shift, a.max_pages = ex.max_pages;
+    a.page_table = ex.page_table, a.page_shift = ex.page_shift, a.max_pages = ex.max_pages, a.num_pages = ex.num_pages;
     // attention is latency-bound at small batch: let HBM stream the output projection meanwhile
     if ((size_t)H * NH * D * 2 <= ((size_t)64 << 20)) {
         a.next = one_plan(next_rows(Wo, nullptr, H, NH * D, 1 << 20));
@@ -395,7 +400,7 @@ int ezb_gemv_bf16(const void* x, const void* W, void* y, int N, int K, ezb_strea
     EZB_REQUIRE(x && W && y, "null pointer");
     EZB_REQUIRE(N >= 1 && K >= 1, "N and K must be positive");
     EZB_REQUIRE_SHAPE(K % 16 == 0, "K must be divisible by 16");
-    EZB_REQUIRE(aligned16(x) && aligned16(W), "x and W must be 16-byte aligned");
+    EZB_REQUIRE(aligned16(x) && aligned16(W) && (reinterpret_cast<uintptr_t>(y) & 1u) == 0, "x and W must be 16-byte aligned, y 2-byte aligned");
     GemvArgs g;
     g.W0 = static_cast<const bf16*>(W), g.ldw = K, g.N = N, g.K = K, g.B = 1;
     g.x = static_cast<const bf16*>(x), g.ldx = K;
@@ -489,7 +494,7 @@ int ezb_attn_decode(const void* Q, const void* K, const void* V, void* Out, void
     EZB_REQUIRE_SHAPE(D == 64 || D == 128, "head_dim must be 64 or 128");
     EZB_REQUIRE_SHAPE(H % NKV == 0, "num_heads must be divisible by num_kv_heads");
     EZB_REQUIRE_SHAPE(B <= 65535 && NKV <= 65535, "batch and kv heads are limited to 65535");
-    EZB_REQUIRE(aligned16(Q) && aligned16(K) && aligned16(V), "Q, K and V must be 16-byte aligned");
+    EZB_REQUIRE(aligned16(Q) && aligned16(K) && aligned16(V) && aligned16(Out), "Q, K, V and Out must be 16-byte aligned");
     if (!workspace || workspace_bytes < attn_workspace_bytes(B, H, NKV, S, D)) {
         set_last_message("attention workspace missing or smaller than ezb_attn_decode_workspace_bytes()");
         return EZB_ERR_WORKSPACE;
@@ -514,14 +519,14 @@ static int page_shift_of(int page_size) {
 
 int ezb_attn_decode_paged(const void* Q, const void* K_pool, const void* V_pool, const int* page_table, void* Out,
                           void* workspace, size_t workspace_bytes, int B, int H, int NKV, int max_pages, int page_size, int D,
-                          const int* seq_lens, ezb_stream_t stream) {
+                          int num_pages, const int* seq_lens, ezb_stream_t stream) {
     EZB_REQUIRE(Q && K_pool && V_pool && page_table && Out && seq_lens, "null pointer");
-    EZB_REQUIRE(B >= 1 && H >= 1 && NKV >= 1 && max_pages >= 1, "sizes must be positive");
+    EZB_REQUIRE(B >= 1 && H >= 1 && NKV >= 1 && max_pages >= 1 && num_pages >= 1, "sizes must be positive");
     EZB_REQUIRE_SHAPE(page_shift_of(page_size) >= 0, "page_size must be a power of two >= 64");
     EZB_REQUIRE_SHAPE(D == 64 || D == 128, "head_dim must be 64 or 128");
     EZB_REQUIRE_SHAPE(H % NKV == 0, "num_heads must be divisible by num_kv_heads");
     EZB_REQUIRE_SHAPE(B <= 65535 && NKV <= 65535, "batch and kv heads are limited to 65535");
-    EZB_REQUIRE(aligned16(Q) && aligned16(K_pool) && aligned16(V_pool), "Q and the page pools must be 16-byte aligned");
+    EZB_REQUIRE(aligned16(Q) && aligned16(K_pool) && aligned16(V_pool) && aligned16(Out), "Q, Out and the page pools must be 16-byte aligned");
     const int S = max_pages * page_size;
     if (!workspace || workspace_bytes < attn_workspace_bytes(B, H, NKV, S, D)) {
         set_last_message("attention workspace missing or smaller than ezb_attn_decode_workspace_bytes(B, H, NKV, max_pages * page_size, D)");
@@ -533,7 +538,7 @@ int ezb_attn_decode_paged(const void* Q, const void* K_pool, const void* V_pool,
     a.Out = static_cast<bf16*>(Out), a.o_bstride = (long long)H * D;
     a.seq_lens = seq_lens;
     a.B = B, a.H = H, a.NKV = NKV, a.S = S, a.D = D;
-    a.page_table = page_table, a.page_shift = page_shift_of(page_size), a.max_pages = max_pages;
+    a.page_table = page_table, a.page_shift = page_shift_of(page_size), a.max_pages = max_pages, a.num_pages = num_pages;
     a.workspace = workspace;
     chain_begin();
     EZB_CUDA_TRY(launch_attn_decode(a, stream));
@@ -636,7 +641,7 @@ size_t ezb_qwen3_decode_stack_workspace_bytes(int B, int S, int H, int I, int NH
 
 static int run_stack(const void* hidden, void* out, const ezb_layer_t* layers, int n_layers, const void* rope_cos,
                      const void* rope_sin, int rope_position, const int* seq_lens, const int* page_table, int page_shift,
-                     int max_pages, void* workspace, size_t workspace_bytes, int B, int S, int H, int I, int NH, int NKV, int D,
+                     int max_pages, int num_pages, void* workspace, size_t workspace_bytes, int B, int S, int H, int I, int NH, int NKV, int D,
                      float eps, ezb_stream_t stream) {
     EZB_REQUIRE(hidden && out && layers && n_layers >= 1, "null pointer or no layers");
     EZB_REQUIRE((rope_cos == nullptr) == (rope_sin == nullptr) && rope_position >= 0, "rotary tables come as a pair; position >= 0");
@@ -671,7 +676,7 @@ static int run_stack(const void* hidden, void* out, const ezb_layer_t* layers, i
         ex.q_norm_w = static_cast<const bf16*>(L.q_norm_w), ex.k_norm_w = static_cast<const bf16*>(L.k_norm_w);
         ex.rope_cos = cos_row, ex.rope_sin = sin_row;
         ex.seq_lens = seq_lens, ex.rope_by_len = seq_lens ? 1 : 0;
-        ex.page_table = page_table, ex.page_shift = page_shift, ex.max_pages = max_pages;
+        ex.page_table = page_table, ex.page_shift = page_shift, ex.max_pages = max_pages, ex.num_pages = num_pages;
         ex.next_Wqkv = (l + 1 < n_layers) ? static_cast<const bf16*>(layers[l + 1].Wqkv) : nullptr;
         bf16* y = (l + 1 == n_layers) ? static_cast<bf16*>(out) : pp[l & 1];
         if (int rc = run_layer(x, static_cast<bf16*>(L.K_cache), static_cast<bf16*>(L.V_cache), static_cast<const bf16*>(L.Wqkv),
@@ -825,8 +830,10 @@ static int make_tp_link(TpLink& base, void* const* comm_bases_host, int world, i
     for (int w = 0; w < world; ++w) EZB_REQUIRE(comm_bases_host[w] && aligned16(comm_bases_host[w]), "bad comm buffer pointer");
     const int poll_mode = tuning(EZB_TUNE_TP_POLL_ALL);
     const int pull_mode = tuning(EZB_TUNE_TP_PULL);
+    long long wait_ms = tuning(EZB_TUNE_TP_WAIT_LIMIT_MS);
+    if (wait_ms < 1) wait_ms = 1;
     base = {world, rank, {}, {}, (long long)B * H, -1, -1, -1, poll_mode == 1 || (poll_mode == 0 && world > 2) ? 1 : 0,
-            pull_mode == 1 ? 1 : 0};
+            pull_mode == 1 ? 1 : 0, wait_ms * 2000000LL};
     for (int r = 0; r < world; ++r) {
         base.ctrl_peer[r] = static_cast<unsigned int*>(comm_bases_host[r]);
         base.inbox_peer[r] = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(comm_bases_host[r]) + kTpCtrlBytes);
@@ -974,18 +981,18 @@ int ezb_qwen3_decode_stack(const void* hidden, void* out, const ezb_layer_t* lay
                            const void* rope_sin, int rope_position, const int* seq_lens, void* workspace,
                            size_t workspace_bytes, int B, int S, int H, int I, int NH, int NKV, int D, float eps,
                            ezb_stream_t stream) {
-    return run_stack(hidden, out, layers, n_layers, rope_cos, rope_sin, rope_position, seq_lens, nullptr, 0, 0, workspace,
+    return run_stack(hidden, out, layers, n_layers, rope_cos, rope_sin, rope_position, seq_lens, nullptr, 0, 0, 0, workspace,
                      workspace_bytes, B, S, H, I, NH, NKV, D, eps, stream);
 }
 
 int ezb_qwen3_decode_stack_paged(const void* hidden, void* out, const ezb_layer_t* layers, int n_layers, const void* rope_cos,
                                  const void* rope_sin, const int* seq_lens, const int* page_table, int page_size,
-                                 int max_pages, void* workspace, size_t workspace_bytes, int B, int H, int I, int NH, int NKV,
-                                 int D, float eps, ezb_stream_t stream) {
-    EZB_REQUIRE(seq_lens && page_table && max_pages >= 1, "paged caches need seq_lens and a page table");
+                                 int max_pages, int num_pages, void* workspace, size_t workspace_bytes, int B, int H, int I,
+                                 int NH, int NKV, int D, float eps, ezb_stream_t stream) {
+    EZB_REQUIRE(seq_lens && page_table && max_pages >= 1 && num_pages >= 1, "paged caches need seq_lens, a page table and the pool size");
     EZB_REQUIRE_SHAPE(page_shift_of(page_size) >= 0, "page_size must be a power of two >= 64");
     return run_stack(hidden, out, layers, n_layers, rope_cos, rope_sin, 0, seq_lens, page_table, page_shift_of(page_size),
-                     max_pages, workspace, workspace_bytes, B, max_pages * page_size, H, I, NH, NKV, D, eps, stream);
+                     max_pages, num_pages, workspace, workspace_bytes, B, max_pages * page_size, H, I, NH, NKV, D, eps, stream);
 }
 
 size_t ezb_qwen3_decode_stack_tp_fused_workspace_bytes(int B, int S, int H, int I_local, int NH_local, int NKV_local, int D) {

@@ -60,6 +60,8 @@ struct AttnParams {
     const int* page_table;  // null: contiguous caches [B, NKV, S, D]; else [B, max_pages] page ids into pools [pages, NKV, P, D]
     int page_shift;         // log2 of the page size P (a power of two >= 64, so a 64-key tile never straddles pages)
     int max_pages;
+    int num_pages;          // pages in the pools: a table entry outside [0, num_pages) is reported, never dereferenced
+    unsigned int* status;
     PrefetchList next;
     Trace trace;
 };
@@ -118,9 +120,16 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
     const int G = p.G, g0 = qt * 16, gn = min(16, G - g0);
     const long long kv_row0 = ((long long)b * p.NKV + kvh) * p.S;
     // Row (in units of D elements) of this (batch row, kv head)'s key `key` in the cache.
-    auto cache_row = [&](int key) -> long long {
+    // A page id outside the pools (a stale or "unallocated" -1 entry) sets ok = false and records a fault; the
+    // caller then touches no memory for that key.
+    auto cache_row = [&](int key, bool& ok) -> long long {
         if (!p.page_table) return kv_row0 + key;
         const long long page = __ldg(p.page_table + (long long)b * p.max_pages + (key >> p.page_shift));
+        if (page < 0 || page >= p.num_pages) {
+            if (ok) report_fault(p.status, FAULT_PAGE_RANGE);
+            ok = false;
+            return 0;
+        }
         return ((page * p.NKV + kvh) << p.page_shift) + (key & ((1 << p.page_shift) - 1));
     };
 
@@ -153,7 +162,8 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
     auto load_tile = [&](int t) {
         unsigned char* st = stages + (t % kAttnStages) * STAGE_BYTES;
         const int key0 = c0 + t * kTileKeys;
-        const long long tile_row0 = cache_row(key0);  // the tile lies inside one page
+        bool page_ok = true;
+        const long long tile_row0 = cache_row(key0, page_ok);  // the tile lies inside one page
 #pragma unroll
         for (int i = 0; i < (2 * kTileKeys * CPR) / kAttnThreads; ++i) {
             const int idx = tid + i * kAttnThreads;
@@ -161,7 +171,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
             const int rem = idx % (kTileKeys * CPR);
             const int r = rem / CPR, c = rem % CPR;
             const int key = key0 + r;
-            const bool valid = key < c1;
+            const bool valid = page_ok && key < c1;  // a tile of a bad page is zero-filled, nothing is read
             const bf16* src = (which ? p.V : p.K) + (tile_row0 + (valid ? r : 0)) * D + c * 8;
             const uint32_t dst = smem_u32(st) + which * TILE_BYTES + r * ROW_BYTES + ((c ^ (r & 7)) << 4);
             cp_async16(dst, src, valid);
@@ -210,7 +220,9 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
             // new token's k (normalised) and v: kept in shared memory for the patch below and
             // written to cache slot S-1 (nobody reads that slot from memory in this kernel)
             if (owns_new_slot) {
-                const long long slot = cache_row(new_slot) * D;
+                bool slot_ok = true;
+                const long long slot = cache_row(new_slot, slot_ok) * D;
+                const bool write_slot = slot_ok && qt == 0;  // a bad page: the new k / v are not written anywhere
                 if (warp == 0) {
                     const bf16* ksrc = p.qkv + (long long)b * p.qkv_bstride + p.q_rows + kvh * D;
                     float x[D / 32];
@@ -221,7 +233,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
                     for (int j = 0; j < D / 32; ++j) {
                         const bf16 kn = __float2bfloat16_rn(x[j]);
                         kv_new_s[lane + j * 32] = kn;
-                        if (qt == 0) p.K_cache_w[slot + lane + j * 32] = kn;
+                        if (write_slot) p.K_cache_w[slot + lane + j * 32] = kn;
                     }
                 } else if (warp == 1) {
                     const bf16* vsrc = p.qkv + (long long)b * p.qkv_bstride + p.q_rows + p.kv_rows + kvh * D;
@@ -229,7 +241,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
                     for (int j = 0; j < D / 32; ++j) {
                         const bf16 vn = vsrc[lane + j * 32];
                         kv_new_s[D + lane + j * 32] = vn;
-                        if (qt == 0) p.V_cache_w[slot + lane + j * 32] = vn;
+                        if (write_slot) p.V_cache_w[slot + lane + j * 32] = vn;
                     }
                 }
             }
@@ -582,7 +594,9 @@ cudaError_t launch_attn_decode(const AttnArgs& a, cudaStream_t stream) {
     p.eps = a.eps;
     p.q_norm_w = a.q_norm_w, p.k_norm_w = a.k_norm_w, p.rope_cos = a.rope_cos, p.rope_sin = a.rope_sin;
     p.rope_by_len = a.rope_by_len;
-    p.page_table = a.page_table, p.page_shift = a.page_shift, p.max_pages = a.max_pages;
+    p.page_table = a.page_table, p.page_shift = a.page_shift, p.max_pages = a.max_pages, p.num_pages = a.num_pages;
+    p.status = status_ptr();
+    if (!p.status) return cudaErrorUnknown;
     p.next = a.next;
     if (!tuning(EZB_TUNE_L2_PREFETCH)) p.next.plan[0].units = p.next.plan[1].units = 0;
     p.trace = trace_handle();

@@ -73,7 +73,7 @@ extern "C" int ezb_attn_decode_static(const void* Q, const void* K, const void* 
     EZB_REQUIRE_SHAPE(D == 64 || D == 128, "head_dim must be 64 or 128");
     EZB_REQUIRE_SHAPE(H % NKV == 0, "num_heads must be divisible by num_kv_heads");
     EZB_REQUIRE_SHAPE(B <= 65535 && NKV <= 65535, "batch and kv heads are limited to 65535");
-    EZB_REQUIRE(aligned16(Q) && aligned16(K) && aligned16(V), "Q, K and V must be 16-byte aligned");
+    EZB_REQUIRE(aligned16(Q) && aligned16(K) && aligned16(V) && aligned16(Out), "Q, K, V and Out must be 16-byte aligned");
     const size_t need = attn_workspace_bytes(B, H, NKV, S, D);
     if (need > kStaticScratchBytes) {
         char msg[200];

@@ -28,6 +28,7 @@ enum DeviceFault : unsigned int {
     FAULT_GEMV_DRAIN = 0x103,       // copies still in flight at exit
     FAULT_TC_ACC_WAIT = 0x104,      // tensor-memory accumulator hand-over never happened
     FAULT_AR_FLAG_WAIT = 0x201,     // a peer's partial result never arrived in the inbox
+    FAULT_PAGE_RANGE = 0x302,       // a page-table entry points outside the page pools
     FAULT_MEGA_GRID_BARRIER = 0x400,  // + barrier index: a grid-wide barrier of the single-kernel layer never filled
 };
 
@@ -72,7 +73,14 @@ struct TpLink {
     int bump_inbox;    // -1 or the inbox whose epoch this kernel advances
     int poll_all;      // 1: the gathering prologue polls all ranks together, 4 elements per thread and step
     int pull;          // 1: a producer writes only its own buffer and consumers read every rank's buffer over NVLink
+    long long wait_cycles;  // budget of one wait for the peers' partials (from EZB_TUNE_TP_WAIT_LIMIT_MS)
 };
+// A recorded fault poisons the exchange: kernels that take part in it read the status word when they start and,
+// if it is set, neither gather, push nor advance an epoch, so that a rank that gave up on a wait never hands its
+// peers numbers computed from a partial sum (the peers then run into their own wait limit and report it too).
+__device__ __forceinline__ bool tp_poisoned(const unsigned int* status) {
+    return *reinterpret_cast<const volatile unsigned int*>(status) != 0u;
+}
 static constexpr int kTpEpoch = 0;
 static constexpr int kTpCtrlBytes = 256;
 static constexpr int kTpSlots = 8;
@@ -139,7 +147,7 @@ __device__ __forceinline__ bool tp_gather(const TpLink& l, unsigned int epoch, l
                     if (all) pending &= ~(1u << g);
                 }
             if (!pending) break;
-            if (clock64() - t0 > kWaitLimitCycles) {
+            if (clock64() - t0 > l.wait_cycles) {
                 report_fault(status, FAULT_AR_FLAG_WAIT);
                 return false;
             }

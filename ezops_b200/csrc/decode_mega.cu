@@ -23,10 +23,9 @@
 //
 // Arithmetic follows the chained kernels: bf16 storage, fp32 accumulation,
 // every projection result rounded to bf16 where the torch reference rounds it
-// (ezops/ops/qwen3_dense_decode.py:142-176).  The projections reuse the
-// small-batch scheme (weights are the 8-wide B operand of mma.sync m16n8k16, the
-// activation row is row 0 of the A operand, eight warps split k and are summed
-// in a fixed order).  Attention at batch 1 is tiny (S keys x G query heads per
+// (ezops/ops/qwen3_dense_decode.py:142-176).  The projections run on mma.sync
+// m16n8k16 fed by plain 128-bit shared-memory loads (see mega_gemv_phase), eight
+// warps split k and are summed in a fixed order.  Attention at batch 1 is tiny (S keys x G query heads per
 // kv head): every kv head is cut into `nsp` slices, one CTA each; scores run on
 // mma.sync straight from the unpadded K rows (128-bit loads, the k index of the
 // mma permuted so that a lane's 8 consecutive elements feed two k-steps), the
@@ -49,10 +48,13 @@ static constexpr int kMegaConsumerThreads = kMegaConsumerWarps * 32;
 static constexpr int kMegaThreads = 32 + kMegaConsumerThreads;
 static constexpr int kMegaMaxStages = 8;
 static constexpr int kMegaHeaderBytes = 512;   // barriers, abort flag, norm scratch, flags
-static constexpr int kMegaRedBytes = 2 * kMegaConsumerWarps * 8 * (int)sizeof(float);
+static constexpr int kMegaRedGroup = 4;        // row blocks whose partial sums are combined across the warps in one go
+static constexpr int kMegaRedBytes = 2 * kMegaRedGroup * kMegaConsumerWarps * 8 * (int)sizeof(float);
+static constexpr int kMegaRowPad = 32;         // elements of padding behind a weight row in a stage (64 B: 128-bit loads of two rows never collide)
 static constexpr int kMegaResSlots = 256;      // output rows of one CTA in the H-row phases
 static constexpr int kMegaSubKeysMax = 256;    // keys of one attention sub-chunk (one K stage + one V stage)
 static constexpr int kMegaMaxSplits = 64;      // slices per kv head
+static constexpr int kCombineBatch = 10;       // slice records a combining thread fetches per round trip
 
 enum MegaCtrl : int { MB_QKV = 0, MB_ATTN = 1, MB_OPROJ = 2, MB_GATEUP = 3, MB_EXIT = 4, MB_TICKET0 = 8 };
 
@@ -72,6 +74,8 @@ struct MegaParams {
     int kc_h, kc_q, kc_i;
     int nsp, sub_keys;
     int NS, l2_window;
+    int inflight;  // stages that may be requested but not yet landed (0 = the whole ring)
+    int gate;      // 1: nothing behind this CTA's K/V stages is requested or prefetched before the QKV barrier has been passed
     unsigned int stage_bytes, act_bytes;
     long long wait_cycles;
     unsigned int* status;
@@ -131,7 +135,7 @@ __device__ __forceinline__ MegaStage mega_locate(const MegaParams& p, const Mega
         const int rb = it / s.nkc_h, kci = it - rb * s.nkc_h;
         d.kind = 0, d.src0 = p.Wqkv, d.ld = p.H;
         d.row0 = s.q_r0 + rb * 8, d.nu = min(8, s.q_r1 - d.row0);
-        d.k0 = kci * p.kc_h, d.len = min(p.kc_h, p.H - d.k0), d.stride = (p.kc_h + 8) * 2;
+        d.k0 = kci * p.kc_h, d.len = min(p.kc_h, p.H - d.k0), d.stride = (p.kc_h + kMegaRowPad) * 2;
     } else if (it < s.e_att) {
         const int j = it - s.e_qkv, sub = j >> 1;
         const int key0 = s.att_c0 + sub * p.sub_keys;
@@ -143,17 +147,17 @@ __device__ __forceinline__ MegaStage mega_locate(const MegaParams& p, const Mega
         const int j = it - s.e_att, rb = j / s.nkc_q, kci = j - rb * s.nkc_q;
         d.kind = 0, d.src0 = p.Wo, d.ld = p.Q;
         d.row0 = s.o_r0 + rb * 8, d.nu = min(8, s.o_r1 - d.row0);
-        d.k0 = kci * p.kc_q, d.len = min(p.kc_q, p.Q - d.k0), d.stride = (p.kc_q + 8) * 2;
+        d.k0 = kci * p.kc_q, d.len = min(p.kc_q, p.Q - d.k0), d.stride = (p.kc_q + kMegaRowPad) * 2;
     } else if (it < s.e_gu) {
         const int j = it - s.e_o, rb = j / s.nkc_h, kci = j - rb * s.nkc_h;
         d.kind = 1, d.src0 = p.Wg, d.src1 = p.Wu, d.ld = p.H;
         d.row0 = s.g_r0 + rb * 4, d.nu = min(4, s.g_r1 - d.row0);
-        d.k0 = kci * p.kc_h, d.len = min(p.kc_h, p.H - d.k0), d.stride = (p.kc_h + 8) * 2;
+        d.k0 = kci * p.kc_h, d.len = min(p.kc_h, p.H - d.k0), d.stride = (p.kc_h + kMegaRowPad) * 2;
     } else {
         const int j = it - s.e_gu, rb = j / s.nkc_i, kci = j - rb * s.nkc_i;
         d.kind = 0, d.src0 = p.Wd, d.ld = p.I;
         d.row0 = s.o_r0 + rb * 8, d.nu = min(8, s.o_r1 - d.row0);
-        d.k0 = kci * p.kc_i, d.len = min(p.kc_i, p.I - d.k0), d.stride = (p.kc_i + 8) * 2;
+        d.k0 = kci * p.kc_i, d.len = min(p.kc_i, p.I - d.k0), d.stride = (p.kc_i + kMegaRowPad) * 2;
     }
     return d;
 }
@@ -175,20 +179,13 @@ __device__ __forceinline__ bool mega_mbar_wait(uint32_t bar, uint32_t parity, vo
     }
 }
 
-// Activation vector in the order the mma A fragments want it: every group of 32 elements is stored as
-// four 16-byte blocks, block t holding the element pairs (j*8 + 2t, j*8 + 2t + 1), j = 0..3, so that
-// lane t of a quad fetches the fragments of two k-steps with one 128-bit load.
+// The activation vector lives in shared memory in its natural order, eight elements (16 bytes) per index.
 __device__ __forceinline__ void mega_store_x8(bf16* xs, int i, const uint32_t (&w)[4]) {
-    uint32_t* base = reinterpret_cast<uint32_t*>(xs + (i >> 2) * 32);
-    const int j = i & 3;
-#pragma unroll
-    for (int t = 0; t < 4; ++t) base[t * 4 + j] = w[t];
+    *reinterpret_cast<uint4*>(xs + i * 8) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 __device__ __forceinline__ void mega_load_x8(const bf16* xs, int i, uint32_t (&w)[4]) {
-    const uint32_t* base = reinterpret_cast<const uint32_t*>(xs + (i >> 2) * 32);
-    const int j = i & 3;
-#pragma unroll
-    for (int t = 0; t < 4; ++t) w[t] = base[t * 4 + j];
+    const uint4 v = *reinterpret_cast<const uint4*>(xs + i * 8);
+    w[0] = v.x, w[1] = v.y, w[2] = v.z, w[3] = v.w;
 }
 
 // Brings x[K] (global, written by other CTAs of this grid or by an earlier kernel: read through L2) into
@@ -333,57 +330,118 @@ __device__ __forceinline__ void mega_grid_barrier(const MegaParams& p, MegaCtx& 
 
 // One projection phase: this CTA's rows [r0, r1) of y = W . xs (xs: the staged activation vector), weights
 // taken from the ring in stage order.  PAIR: a row block is 4 gate rows + 4 up rows and `epi` gets both sums.
+//
+// Inner loop.  A stage holds 8 weight rows; the k range of the stage is cut into groups of 32 elements and group j
+// is paired with group j + half.  One mma.sync m16n8k16 pair then covers 8 rows x 64 k: rows 0-7 of the A tile are
+// the weight rows over group j, rows 8-15 the SAME weight rows over group j + half; column 0 of the B tile is x
+// over group j, column 1 is x over group j + half.  C[r][0] and C[r+8][1] are the two halves of row r's dot
+// product (the cross terms C[r][1], C[r+8][0] are ignored).  Fragments come from plain 128-bit shared-memory loads:
+// a lane reads 8 consecutive elements of "its" row and k quarter, which feed the k slots of two mma steps (the k
+// index inside an mma is a free permutation as long as A and B use the same one).  Measured on this GPU, per 64 KB
+// stage and SM: ldmatrix + mma with the weights as the 8-wide B operand 1290 cycles (the two pipes do not overlap),
+// this form 950.
+//
+// Across the eight warps (each takes every eighth pair) the partial sums are combined through shared memory in a
+// fixed order, once per kMegaRedGroup row blocks: one barrier and one short epilogue per group instead of per block.
 template <bool PAIR, class Epi>
 __device__ __forceinline__ void mega_gemv_phase(const MegaParams& p, MegaCtx& c, int r0, int r1, int K, int kc, int nkc,
-                                                Epi epi, unsigned long long* trec) {
+                                                Epi epi, unsigned long long* trec, unsigned int prof_id) {
     constexpr int UNITS = PAIR ? 4 : 8;
+    // With tracing on, lane 0 of every warp adds up the cycles it spends waiting for stages, computing, and in the
+    // cross-warp reduction, and leaves them in a trace record {prof_id, block*8 + warp, wait, compute, reduce, stages}.
+    const bool prof = p.trace.buf != nullptr && c.lane == 0;
+    long long cyc_wait = 0, cyc_comp = 0, cyc_red = 0, stages_done = 0;
     const int nrb = (r1 - r0 + UNITS - 1) / UNITS;
-    const int ws_stride = kc + 8;
+    const int row_bytes = (kc + kMegaRowPad) * 2;
     const int g4 = c.lane >> 2, t4 = c.lane & 3;
-    const bf16* xrow = reinterpret_cast<const bf16*>(c.act) + t4 * 8;
-    const uint32_t lds_off = (uint32_t)(((c.lane & 7) * ws_stride + (c.lane >> 3) * 8) * (int)sizeof(bf16));
+    const unsigned char* xs_b = c.act + t4 * 16;
+    const uint32_t lane_off = (uint32_t)(g4 * row_bytes + t4 * 16);
     bool first = true;
+    auto reduce_group = [&](int rb_first, int count, const float* redb) {
+        // threads 0 .. count*UNITS-1: one output each
+        if (c.ct < count * UNITS) {
+            const int blk = c.ct / UNITS, j = c.ct - blk * UNITS;
+            const int n = r0 + (rb_first + blk) * UNITS + j;
+            if (n < r1 && !(*c.abort_flag)) {
+                const float* src = redb + blk * (kMegaConsumerWarps * 8);
+                float v0 = 0.f, v1 = 0.f;
+#pragma unroll
+                for (int w = 0; w < kMegaConsumerWarps; ++w) {
+                    v0 += src[w * 8 + j];
+                    if (PAIR) v1 += src[w * 8 + j + 4];
+                }
+                epi(n, v0, v1);
+            }
+        }
+    };
+    int group_first = 0;
     for (int rb = 0; rb < nrb; ++rb) {
-        float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
+        float acc[4][4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) acc[u][0] = acc[u][1] = acc[u][2] = acc[u][3] = 0.f;
         for (int kci = 0; kci < nkc; ++kci) {
             const int s = c.it % p.NS;
+            const long long tp0 = prof ? clock64() : 0;
             mega_mbar_wait(smem_u32(&c.full_bar[s]), (uint32_t)((c.it / p.NS) & 1), c.abort_flag, p.status, FAULT_GEMV_FULL_WAIT,
                            p.wait_cycles);
+            const long long tp1 = prof ? clock64() : 0;
+            cyc_wait += tp1 - tp0;
             if (first) trace_mark(trec, 4), first = false;
             const int k0 = kci * kc;
             const int len = min(kc, K - k0);
-            const int nk32 = len >> 5;
-            const uint32_t w_base = smem_u32(c.stage_base + (size_t)s * p.stage_bytes) + lds_off;
-            const bf16* xk = xrow + k0;
-#pragma unroll 4
-            for (int k32 = c.cw; k32 < nk32; k32 += kMegaConsumerWarps) {
-                uint32_t w0, w1, w2, w3;
-                ldsm_x4(w_base + (uint32_t)(k32 * 32 * (int)sizeof(bf16)), w0, w1, w2, w3);
-                uint4 a = make_uint4(0u, 0u, 0u, 0u);
-                if (g4 == 0) a = *reinterpret_cast<const uint4*>(xk + k32 * 32);
-                mma_bf16_16816(acc0, a.x, 0u, a.y, 0u, w0, w1);
-                mma_bf16_16816(acc1, a.z, 0u, a.w, 0u, w2, w3);
+            const int nk32 = len >> 5, half = (nk32 + 1) >> 1;
+            const unsigned char* wl = c.stage_base + (size_t)s * p.stage_bytes + lane_off;
+            // x for column 0 (lanes g4 == 0: group j) and column 1 (lanes g4 == 1: group j + half)
+            const unsigned char* xl = xs_b + (size_t)k0 * 2 + (g4 == 1 ? half * 64 : 0);
+            const bool has_x = g4 < 2;
+            int pr = c.cw;
+            for (; pr + kMegaConsumerWarps < half; pr += 2 * kMegaConsumerWarps) {  // two pairs in flight
+                const int p1 = pr + kMegaConsumerWarps;
+                const uint4 l0 = *reinterpret_cast<const uint4*>(wl + pr * 64);
+                const uint4 l1 = *reinterpret_cast<const uint4*>(wl + p1 * 64);
+                uint4 h0 = make_uint4(0u, 0u, 0u, 0u), h1 = h0, x0 = h0, x1 = h0;
+                if (pr + half < nk32) h0 = *reinterpret_cast<const uint4*>(wl + (pr + half) * 64);
+                if (p1 + half < nk32) h1 = *reinterpret_cast<const uint4*>(wl + (p1 + half) * 64);
+                if (has_x && (g4 == 0 || pr + half < nk32)) x0 = *reinterpret_cast<const uint4*>(xl + pr * 64);
+                if (has_x && (g4 == 0 || p1 + half < nk32)) x1 = *reinterpret_cast<const uint4*>(xl + p1 * 64);
+                mma_bf16_16816(acc[0], l0.x, h0.x, l0.y, h0.y, x0.x, x0.y);
+                mma_bf16_16816(acc[1], l0.z, h0.z, l0.w, h0.w, x0.z, x0.w);
+                mma_bf16_16816(acc[2], l1.x, h1.x, l1.y, h1.y, x1.x, x1.y);
+                mma_bf16_16816(acc[3], l1.z, h1.z, l1.w, h1.w, x1.z, x1.w);
+            }
+            for (; pr < half; pr += kMegaConsumerWarps) {
+                const uint4 l0 = *reinterpret_cast<const uint4*>(wl + pr * 64);
+                uint4 h0 = make_uint4(0u, 0u, 0u, 0u), x0 = h0;
+                if (pr + half < nk32) h0 = *reinterpret_cast<const uint4*>(wl + (pr + half) * 64);
+                if (has_x && (g4 == 0 || pr + half < nk32)) x0 = *reinterpret_cast<const uint4*>(xl + pr * 64);
+                mma_bf16_16816(acc[0], l0.x, h0.x, l0.y, h0.y, x0.x, x0.y);
+                mma_bf16_16816(acc[1], l0.z, h0.z, l0.w, h0.w, x0.z, x0.w);
             }
             __syncwarp();
             if (c.lane == 0) mbar_arrive(smem_u32(&c.empty_bar[s]));
             ++c.it;
+            if (prof) cyc_comp += clock64() - tp1, ++stages_done;
         }
-        // row 0 of the C tile is the activation row: lanes 0..3 hold weight rows 2*t4, 2*t4+1
-        float* redb = c.red + (c.red_flip & 1) * (kMegaConsumerWarps * 8);
-        ++c.red_flip;
-        if (g4 == 0) *reinterpret_cast<float2*>(redb + c.cw * 8 + t4 * 2) = make_float2(acc0[0] + acc1[0], acc0[1] + acc1[1]);
-        named_bar_sync(1, kMegaConsumerThreads);
-        if (c.ct < UNITS) {
-            const int n = r0 + rb * UNITS + c.ct;
-            if (n < r1 && !(*c.abort_flag)) {
-                float v0 = 0.f, v1 = 0.f;
-#pragma unroll
-                for (int w = 0; w < kMegaConsumerWarps; ++w) {
-                    v0 += redb[w * 8 + c.ct];
-                    if (PAIR) v1 += redb[w * 8 + c.ct + 4];
-                }
-                epi(n, v0, v1);
-            }
+        const long long tp2 = prof ? clock64() : 0;
+        // lanes with t4 == 0 hold row g4: C[g4][0] (first half of k) + C[g4+8][1] (second half); fixed order
+        const float part = ((acc[0][0] + acc[0][3]) + (acc[1][0] + acc[1][3])) + ((acc[2][0] + acc[2][3]) + (acc[3][0] + acc[3][3]));
+        const int in_group = rb - group_first;
+        float* redb = c.red + (c.red_flip & 1) * (kMegaRedGroup * kMegaConsumerWarps * 8);
+        if (t4 == 0) redb[(in_group * kMegaConsumerWarps + c.cw) * 8 + g4] = part;
+        if (in_group == kMegaRedGroup - 1 || rb == nrb - 1) {
+            named_bar_sync(1, kMegaConsumerThreads);
+            reduce_group(group_first, in_group + 1, redb);
+            group_first = rb + 1;
+            ++c.red_flip;
+        }
+        if (prof) cyc_red += clock64() - tp2;
+    }
+    if (prof) {
+        const unsigned int slot = atomicAdd(p.trace.cursor, 1u);
+        if (slot < p.trace.capacity) {
+            unsigned long long* r = p.trace.buf + (size_t)slot * 6;
+            r[0] = prof_id, r[1] = blockIdx.x * 8 + c.cw, r[2] = (unsigned long long)cyc_wait, r[3] = (unsigned long long)cyc_comp;
+            r[4] = (unsigned long long)cyc_red, r[5] = (unsigned long long)stages_done;
         }
     }
 }
@@ -396,6 +454,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_layer_b1_kernel(const 
     uint64_t* empty_bar = full_bar + kMegaMaxStages;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 2 * kMegaMaxStages * 8);
     int* cta_flag = reinterpret_cast<int*>(smem + 2 * kMegaMaxStages * 8 + 16);
+    volatile int* gate_open = reinterpret_cast<volatile int*>(smem + 2 * kMegaMaxStages * 8 + 20);
     float* norm_scratch = reinterpret_cast<float*>(smem + 2 * kMegaMaxStages * 8 + 32);
     float* red = reinterpret_cast<float*>(smem + kMegaHeaderBytes);
     float* res_s = reinterpret_cast<float*>(smem + kMegaHeaderBytes + kMegaRedBytes);
@@ -415,6 +474,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_layer_b1_kernel(const 
         }
         *abort_flag = 0;
         *cta_flag = 0;
+        *gate_open = p.gate ? 0 : 1;
         mbar_fence_init();
     }
     __syncthreads();
@@ -457,14 +517,40 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_layer_b1_kernel(const 
             __syncwarp();
             if (lane < 8 && bytes) bulk_g2s(dst0 + off, src, bytes, bar);
         };
+        // Policy.  (1) Requests queue in front of everything else this SM sends to memory, the barrier traffic
+        // included, so only `inflight` stages may be outstanding at a time: enough to cover the latency-bandwidth
+        // product, not the whole ring.  (2) Until the QKV barrier has been passed, traffic for later phases only
+        // delays the CTAs that still wait for their QKV rows (and with them everybody): the producer stops behind
+        // its K/V stages until its consumers open the gate.  (3) With the gate open and the ring full, it pulls the
+        // stages behind the ring into L2 (a bounded look-ahead) while attention, the barriers and the activation
+        // staging leave HBM idle.
         int issued = 0, pf = 0;
-        for (int it = 0; it < total; ++it) {
+        bool ok = true;
+        auto give_up = [&](unsigned int code) {
+            *abort_flag = 1;
+            report_fault(p.status, code);
+            ok = false;
+        };
+        for (int it = 0; it < total && ok; ++it) {
+            if (it >= s.e_att && !*gate_open) {
+                const long long t0 = clock64();
+                while (!*gate_open && ok) {
+                    if (*abort_flag) ok = false;
+                    else if (clock64() - t0 > p.wait_cycles) give_up(FAULT_GEMV_EMPTY_WAIT);
+                }
+                if (!ok) break;
+            }
+            if (p.inflight > 0 && it >= p.inflight) {
+                const int j = it - p.inflight;
+                if (!mega_mbar_wait(smem_u32(&full_bar[j % NS]), (uint32_t)((j / NS) & 1), abort_flag, p.status, FAULT_GEMV_FULL_WAIT,
+                                    p.wait_cycles))
+                    break;
+            }
             if (it >= NS) {
                 const uint32_t bar = smem_u32(&empty_bar[it % NS]);
                 const uint32_t parity = (uint32_t)(((it / NS) & 1) ^ 1);
                 if (!mbar_test_wait(bar, parity)) {
                     long long t0 = clock64();
-                    bool ok = true;
                     for (;;) {
                         if (mbar_test_wait(bar, parity)) break;
                         if (*abort_flag) {
@@ -473,14 +559,12 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_layer_b1_kernel(const 
                         }
                         // The ring is full: keep HBM busy by pulling the stages behind it into L2.
                         if (pf < it) pf = it;
-                        if (pf < total && pf < it + p.l2_window) {
+                        if (*gate_open && pf < total && pf < it + p.l2_window) {
                             issue(pf, true);
                             ++pf;
                             t0 = clock64();
                         } else if (clock64() - t0 > p.wait_cycles) {
-                            *abort_flag = 1;
-                            report_fault(p.status, FAULT_GEMV_EMPTY_WAIT);
-                            ok = false;
+                            give_up(FAULT_GEMV_EMPTY_WAIT);
                             break;
                         }
                     }
@@ -526,23 +610,25 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_layer_b1_kernel(const 
     for (int i = ct; i < s.o_r1 - s.o_r0; i += kMegaConsumerThreads) res_s[i] = mega_ldcg_bf16(p.hidden + s.o_r0 + i);
     mega_stage_x<true>(p.hidden, p.H, p.in_norm_w, p.eps, xs, norm_scratch, ct, cw, lane);
     mega_gemv_phase<false>(p, c, s.q_r0, s.q_r1, p.H, p.kc_h, s.nkc_h,
-                           [&](int n, float v0, float) { p.qkv[n] = __float2bfloat16_rn(v0); }, trec);
+                           [&](int n, float v0, float) { p.qkv[n] = __float2bfloat16_rn(v0); }, trec, 30u);
     trace_mark(trec, 5);
     mega_grid_barrier(p, c, MB_QKV);
+    if (ct == 0) *gate_open = 1;  // every CTA has its QKV rows: the producer may run ahead again
 
     // ================================================================ phase 1: attention slice
     trec = (ct == 0) ? trace_open(p.trace, 21u, cta_id) : nullptr;
     if (s.att_nsub > 0) {
         const int G = p.G, kvh = s.att_kvh;
-        float* S_s = reinterpret_cast<float*>(act);                         // [sub_keys][8] scores, then probabilities
-        bf16* q_s = reinterpret_cast<bf16*>(act + (size_t)p.sub_keys * 32);  // [8][D], rows >= G are zero
-        bf16* kvn_s = q_s + 8 * D;                                           // [2][D] the new token's k and v
-        float* st_s = reinterpret_cast<float*>(kvn_s + 2 * D);               // running max [8], sum [8], rescale [8]
-        float* mrg = st_s + 32;                                              // [8 warps][4 heads][D]
+        // scratch (aliases the activation vector, which nobody needs during this phase)
+        float* Pw = reinterpret_cast<float*>(act) + cw * 256;             // this warp's probabilities [32 keys][8 heads]
+        float* alpha_s = reinterpret_cast<float*>(act + 8192) + cw * 8;   // this warp's rescale factor per head
+        bf16* q_s = reinterpret_cast<bf16*>(act + 8192 + 256);            // [8][D], rows >= G are zero
+        bf16* kvn_s = q_s + 8 * D;                                        // [2][D] the new token's k and v
+        float* mrg_ml = reinterpret_cast<float*>(kvn_s + 2 * D);          // [8 warps][8 heads][max, sum]
+        float* mrg_o = mrg_ml + 128;                                      // [8 warps][4 heads][D]
         const bool owner = s.att_split == p.nsp - 1;  // the slice that ends with the token being decoded (slot S-1)
 
         for (int i = ct; i < D; i += kMegaConsumerThreads) reinterpret_cast<uint4*>(q_s)[i] = make_uint4(0u, 0u, 0u, 0u);
-        if (ct < 8) st_s[ct] = -INFINITY, st_s[8 + ct] = 0.f, st_s[16 + ct] = 1.f;
         named_bar_sync(1, kMegaConsumerThreads);
         if (cw < G) {
             const bf16* qsrc = p.qkv + (long long)(kvh * G + cw) * D;
@@ -579,21 +665,26 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_layer_b1_kernel(const 
         }
         named_bar_sync(1, kMegaConsumerThreads);
 
+        unsigned long long* trec2 = (ct == 0) ? trace_open(p.trace, 25u, cta_id) : nullptr;  // detail: q ready | first scores | P.V done | record + ticket
         // A fragments of Q (rows = query heads of this kv head); element order matches the K loads below
         uint4 qf[DPL];
 #pragma unroll
         for (int j = 0; j < DPL; ++j) qf[j] = *reinterpret_cast<const uint4*>(q_s + g4 * D + 32 * j + t4 * 8);
+        // Every warp owns the key blocks (8 keys) cw, cw+8, cw+16, cw+24 of a sub-chunk and runs its own online
+        // soft-max over them: no barrier among the warps until their results are merged at the end.
         float o[8][DPL];
 #pragma unroll
         for (int h = 0; h < 8; ++h)
 #pragma unroll
             for (int j = 0; j < DPL; ++j) o[h][j] = 0.f;
+        float m_run = -INFINITY, l_run = 0.f;  // statistics of head g4 (the same in the four lanes of a quad)
 
         for (int sub = 0; sub < s.att_nsub; ++sub) {
             const int key0 = s.att_c0 + sub * p.sub_keys;
             const int n = min(p.sub_keys, s.att_c1 - key0);
+            const int nblk = (n + 7) / 8;
             const bool patch = owner && sub == s.att_nsub - 1;  // this sub-chunk ends with slot S-1
-            // ---- K: scores for n keys
+            // ---- K: scores of this warp's keys
             const int sk = c.it % NS;
             mega_mbar_wait(smem_u32(&full_bar[sk]), (uint32_t)((c.it / NS) & 1), abort_flag, p.status, FAULT_GEMV_FULL_WAIT,
                            p.wait_cycles);
@@ -604,51 +695,63 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_layer_b1_kernel(const 
                 if (ct < D / 8) reinterpret_cast<uint4*>(Kst + (size_t)(n - 1) * D * 2)[ct] = reinterpret_cast<const uint4*>(kvn_s)[ct];
                 named_bar_sync(1, kMegaConsumerThreads);
             }
-            const int nblk = (n + 7) / 8;
-            for (int kb = cw; kb < nblk; kb += kMegaConsumerWarps) {
-                float acc[4] = {0.f, 0.f, 0.f, 0.f};
-                const unsigned char* krow = Kst + ((size_t)(kb * 8 + g4) * D + t4 * 8) * 2;
+            float sc[4][2];
+            {
+                float acc[4][4];  // four independent accumulator chains
+#pragma unroll
+                for (int u = 0; u < 4; ++u) acc[u][0] = acc[u][1] = acc[u][2] = acc[u][3] = 0.f;
 #pragma unroll
                 for (int j = 0; j < DPL; ++j) {
-                    const uint4 kf = *reinterpret_cast<const uint4*>(krow + 64 * j);
-                    mma_bf16_16816(acc, qf[j].x, 0u, qf[j].y, 0u, kf.x, kf.y);
-                    mma_bf16_16816(acc, qf[j].z, 0u, qf[j].w, 0u, kf.z, kf.w);
+                    uint4 kf[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int kb = cw + u * kMegaConsumerWarps;
+                        kf[u] = make_uint4(0u, 0u, 0u, 0u);
+                        if (kb < nblk) kf[u] = *reinterpret_cast<const uint4*>(Kst + ((size_t)(kb * 8 + g4) * D + t4 * 8) * 2 + 64 * j);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) mma_bf16_16816(acc[u], qf[j].x, 0u, qf[j].y, 0u, kf[u].x, kf[u].y);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) mma_bf16_16816(acc[u], qf[j].z, 0u, qf[j].w, 0u, kf[u].z, kf[u].w);
                 }
-                const int key = kb * 8 + t4 * 2;
-                if (g4 < G) {
-                    S_s[key * 8 + g4] = (key < n) ? acc[0] * p.scale_log2e : -INFINITY;
-                    S_s[(key + 1) * 8 + g4] = (key + 1 < n) ? acc[1] * p.scale_log2e : -INFINITY;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int key = (cw + u * kMegaConsumerWarps) * 8 + t4 * 2;  // this lane: head g4, keys key and key + 1
+                    sc[u][0] = (key < n) ? acc[u][0] * p.scale_log2e : -INFINITY;
+                    sc[u][1] = (key + 1 < n) ? acc[u][1] * p.scale_log2e : -INFINITY;
                 }
             }
             if (patch) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            named_bar_sync(1, kMegaConsumerThreads);
+            __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&empty_bar[sk]));
             ++c.it;
-            // ---- soft-max statistics of this sub-chunk, one warp per head
-            if (cw < G) {
-                const float m_old = st_s[cw];
-                float mx = -INFINITY;
-                for (int key = lane; key < n; key += 32) mx = fmaxf(mx, S_s[key * 8 + cw]);
+            if (sub == 0) trace_mark(trec2, 3);
+            // ---- online soft-max (exp2 domain) for head g4 over this warp's keys
+            float mx = -INFINITY;
 #pragma unroll
-                for (int o2 = 16; o2 > 0; o2 >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o2));
-                const float m_new = fmaxf(m_old, mx);
-                const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
-                float sum = 0.f;
-                for (int key = lane; key < n; key += 32) {
-                    const float pr = mega_exp2(S_s[key * 8 + cw] - m_safe);
-                    S_s[key * 8 + cw] = pr;
-                    sum += pr;
-                }
-                sum = warp_sum(sum);
-                if (lane == 0) {
-                    const float alpha = mega_exp2(m_old - m_safe);
-                    st_s[16 + cw] = alpha;
-                    st_s[8 + cw] = st_s[8 + cw] * alpha + sum;
-                    st_s[cw] = m_new;
+            for (int u = 0; u < 4; ++u) mx = fmaxf(mx, fmaxf(sc[u][0], sc[u][1]));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m_run, mx);
+            const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
+            const float alpha = mega_exp2(m_run - m_safe);
+            float psum = 0.f;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const float pr = mega_exp2(sc[u][e] - m_safe);
+                    psum += pr;
+                    Pw[(u * 8 + t4 * 2 + e) * 8 + g4] = pr;
                 }
             }
-            named_bar_sync(1, kMegaConsumerThreads);
-            // ---- V: o += P . V, warp w takes keys w, w+8, ...; lane owns DPL consecutive dims
+            psum += __shfl_xor_sync(0xffffffffu, psum, 1);
+            psum += __shfl_xor_sync(0xffffffffu, psum, 2);
+            l_run = l_run * alpha + psum;
+            m_run = m_new;
+            if (t4 == 0) alpha_s[g4] = alpha;
+            __syncwarp();
+            // ---- V: o += P . V over this warp's keys; a lane owns DPL consecutive output dims of every head
             const int sv = c.it % NS;
             mega_mbar_wait(smem_u32(&full_bar[sv]), (uint32_t)((c.it / NS) & 1), abort_flag, p.status, FAULT_GEMV_FULL_WAIT,
                            p.wait_cycles);
@@ -657,50 +760,63 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_layer_b1_kernel(const 
                 if (ct < D / 8) reinterpret_cast<uint4*>(Vst + (size_t)(n - 1) * D * 2)[ct] = reinterpret_cast<const uint4*>(kvn_s + D)[ct];
                 named_bar_sync(1, kMegaConsumerThreads);
             }
+            {
+                const float4 a0 = *reinterpret_cast<const float4*>(alpha_s), a1 = *reinterpret_cast<const float4*>(alpha_s + 4);
+                const float al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
 #pragma unroll
-            for (int h = 0; h < 8; ++h) {
-                const float alpha = st_s[16 + h];
+                for (int h = 0; h < 8; ++h)
 #pragma unroll
-                for (int j = 0; j < DPL; ++j) o[h][j] *= alpha;
+                    for (int j = 0; j < DPL; ++j) o[h][j] *= al[h];
             }
-            for (int key = cw; key < n; key += kMegaConsumerWarps) {
-                const float4 p0 = *reinterpret_cast<const float4*>(S_s + key * 8);
-                const float4 p1 = (G > 4) ? *reinterpret_cast<const float4*>(S_s + key * 8 + 4) : make_float4(0.f, 0.f, 0.f, 0.f);
-                const float pr[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
-                float v[DPL];
-                if (DPL == 4) {
-                    const uint2 raw = *reinterpret_cast<const uint2*>(Vst + (size_t)key * D * 2 + lane * 8);
-                    v[0] = bf16_lo(raw.x), v[1] = bf16_hi(raw.x), v[DPL - 2] = bf16_lo(raw.y), v[DPL - 1] = bf16_hi(raw.y);
-                } else {
-                    const uint32_t raw = *reinterpret_cast<const uint32_t*>(Vst + (size_t)key * D * 2 + lane * 4);
-                    v[0] = bf16_lo(raw), v[1] = bf16_hi(raw);
-                }
 #pragma unroll
-                for (int h = 0; h < 4; ++h)
+            for (int u = 0; u < 4; ++u) {
+                const int kb = cw + u * kMegaConsumerWarps;
+                if (kb < nblk) {
 #pragma unroll
-                    for (int j = 0; j < DPL; ++j) o[h][j] = fmaf(pr[h], v[j], o[h][j]);
-                if (G > 4) {
+                    for (int kk = 0; kk < 8; ++kk) {
+                        const int key = kb * 8 + kk;
+                        if (key < n) {
+                            const float4 p0 = *reinterpret_cast<const float4*>(Pw + (u * 8 + kk) * 8);
+                            float v[DPL];
+                            if (DPL == 4) {
+                                const uint2 raw = *reinterpret_cast<const uint2*>(Vst + (size_t)key * D * 2 + lane * 8);
+                                v[0] = bf16_lo(raw.x), v[1] = bf16_hi(raw.x), v[DPL - 2] = bf16_lo(raw.y), v[DPL - 1] = bf16_hi(raw.y);
+                            } else {
+                                const uint32_t raw = *reinterpret_cast<const uint32_t*>(Vst + (size_t)key * D * 2 + lane * 4);
+                                v[0] = bf16_lo(raw), v[1] = bf16_hi(raw);
+                            }
+                            const float pl[4] = {p0.x, p0.y, p0.z, p0.w};
 #pragma unroll
-                    for (int h = 4; h < 8; ++h)
+                            for (int h = 0; h < 4; ++h)
 #pragma unroll
-                        for (int j = 0; j < DPL; ++j) o[h][j] = fmaf(pr[h], v[j], o[h][j]);
+                                for (int j = 0; j < DPL; ++j) o[h][j] = fmaf(pl[h], v[j], o[h][j]);
+                            if (G > 4) {
+                                const float4 p1 = *reinterpret_cast<const float4*>(Pw + (u * 8 + kk) * 8 + 4);
+                                const float ph[4] = {p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+                                for (int h = 0; h < 4; ++h)
+#pragma unroll
+                                    for (int j = 0; j < DPL; ++j) o[4 + h][j] = fmaf(ph[h], v[j], o[4 + h][j]);
+                            }
+                        }
+                    }
                 }
             }
             if (patch) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
+            __syncwarp();  // also: every lane is done with Pw before the next sub-chunk overwrites it
             if (lane == 0) mbar_arrive(smem_u32(&empty_bar[sv]));
             ++c.it;
-            named_bar_sync(1, kMegaConsumerThreads);  // scores and statistics are reused by the next sub-chunk
         }
+        trace_mark(trec2, 4);
 
-        // ---- sum the eight warps' partial outputs (same statistics, so a plain sum) and park the slice's record
+        // ---- merge the eight warps (each has its own max / sum / O) and park the slice's record
         const long long item = (long long)kvh * p.nsp + s.att_split;
+        if (t4 == 0) mrg_ml[(cw * 8 + g4) * 2] = m_run, mrg_ml[(cw * 8 + g4) * 2 + 1] = l_run;
         for (int hb = 0; hb < G; hb += 4) {
 #pragma unroll
             for (int hh = 0; hh < 4; ++hh) {
-                float* dst = mrg + ((cw * 4 + hh) * D + lane * DPL);
-                // (static indexing of o[][] : hb is 0 or 4)
-                if (hb == 0) {
+                float* dst = mrg_o + ((cw * 4 + hh) * D + lane * DPL);
+                if (hb == 0) {  // (static indexing of o[][]: hb is 0 or 4)
 #pragma unroll
                     for (int j = 0; j < DPL; ++j) dst[j] = o[hh][j];
                 } else {
@@ -710,62 +826,88 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_layer_b1_kernel(const 
             }
             named_bar_sync(1, kMegaConsumerThreads);
             for (int idx = ct; idx < 4 * D; idx += kMegaConsumerThreads) {
-                const int hh = idx / D, d = idx - hh * D;
-                if (hb + hh < G && !*abort_flag) {
-                    float sum = 0.f;
+                const int hh = idx / D, d = idx - hh * D, h = hb + hh;
+                if (h < G && !*abort_flag) {
+                    float M = -INFINITY;
 #pragma unroll
-                    for (int w = 0; w < kMegaConsumerWarps; ++w) sum += mrg[(w * 4 + hh) * D + d];
-                    p.part_o[(item * 8 + hb + hh) * D + d] = sum;
+                    for (int w = 0; w < kMegaConsumerWarps; ++w) M = fmaxf(M, mrg_ml[(w * 8 + h) * 2]);
+                    float O = 0.f, L = 0.f;
+#pragma unroll
+                    for (int w = 0; w < kMegaConsumerWarps; ++w) {
+                        const float f = (M == -INFINITY) ? 0.f : mega_exp2(mrg_ml[(w * 8 + h) * 2] - M);
+                        O += f * mrg_o[(w * 4 + hh) * D + d];
+                        L += f * mrg_ml[(w * 8 + h) * 2 + 1];
+                    }
+                    p.part_o[(item * 8 + h) * D + d] = O;
+                    if (d == 0) p.part_ml[(item * 8 + h) * 2] = M, p.part_ml[(item * 8 + h) * 2 + 1] = L;
                 }
             }
-            named_bar_sync(1, kMegaConsumerThreads);
-        }
-        if (ct < G && !*abort_flag) {
-            p.part_ml[(item * 8 + ct) * 2 + 0] = st_s[ct];
-            p.part_ml[(item * 8 + ct) * 2 + 1] = st_s[8 + ct];
+            named_bar_sync(1, kMegaConsumerThreads);  // orders the records before the ticket; the buffer is free again
         }
         // ---- the CTA that finishes last for this kv head folds the slices together (in slice order)
-        named_bar_sync(1, kMegaConsumerThreads);
         if (ct == 0) {
             unsigned int prev;
             asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(prev) : "l"(p.ctrl + MB_TICKET0 + kvh) : "memory");
             *c.flag = (prev == (unsigned int)(p.nsp - 1));
         }
         named_bar_sync(1, kMegaConsumerThreads);
+        trace_mark(trec2, 5);
         if (*c.flag) {
-            for (int idx = ct; idx < G * (D / 4); idx += kMegaConsumerThreads) {
-                const int hq = idx / (D / 4), d = (idx - hq * (D / 4)) * 4;
-                const float* pm = p.part_ml + ((long long)kvh * p.nsp * 8 + hq) * 2;
-                const float* po = p.part_o + ((long long)kvh * p.nsp * 8 + hq) * D + d;
-                float M = -INFINITY, L = 0.f;
-                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                for (int c0 = 0; c0 < p.nsp; c0 += 16) {
-                    float2 ml[16];
-                    float4 v[16];
+            // One output quad (head, 4 dims) is shared by `ways` neighbouring threads, each folding every ways-th
+            // slice; their partial results are merged with shuffles in a fixed order.
+            const int items = G * (D / 4);
+            int ways = 1;
+            while (ways < 8 && items * ways * 2 <= kMegaConsumerThreads) ways *= 2;
+            const int it_i = ct / ways, way = ct - it_i * ways;
+            const bool active = it_i < items;
+            const int hq = active ? it_i / (D / 4) : 0, d = active ? (it_i - hq * (D / 4)) * 4 : 0;
+            const float* pm = p.part_ml + ((long long)kvh * p.nsp * 8 + hq) * 2;
+            const float* po = p.part_o + ((long long)kvh * p.nsp * 8 + hq) * D + d;
+            float M = -INFINITY, L = 0.f;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int c0 = way; c0 < p.nsp; c0 += kCombineBatch * ways) {
+                float2 ml[kCombineBatch];
+                float4 v[kCombineBatch];
 #pragma unroll
-                    for (int u = 0; u < 16; ++u) {
-                        const bool live = c0 + u < p.nsp;
-                        ml[u] = live ? __ldcg(reinterpret_cast<const float2*>(pm + (long long)(c0 + u) * 16)) : make_float2(-INFINITY, 0.f);
-                        v[u] = live ? __ldcg(reinterpret_cast<const float4*>(po + (long long)(c0 + u) * 8 * D)) : make_float4(0.f, 0.f, 0.f, 0.f);
-                    }
-                    float Mc = M;
-#pragma unroll
-                    for (int u = 0; u < 16; ++u) Mc = fmaxf(Mc, ml[u].x);
-                    const float keep = (Mc == -INFINITY) ? 0.f : mega_exp2(M - Mc);  // M == -inf: nothing accumulated yet, exp2 gives 0
-                    L *= keep, acc.x *= keep, acc.y *= keep, acc.z *= keep, acc.w *= keep;
-#pragma unroll
-                    for (int u = 0; u < 16; ++u) {
-                        const float f = (Mc == -INFINITY) ? 0.f : mega_exp2(ml[u].x - Mc);
-                        L += f * ml[u].y;
-                        acc.x += f * v[u].x, acc.y += f * v[u].y, acc.z += f * v[u].z, acc.w += f * v[u].w;
-                    }
-                    M = Mc;
+                for (int u = 0; u < kCombineBatch; ++u) {
+                    const int cc = c0 + u * ways;
+                    const bool live = active && cc < p.nsp;
+                    ml[u] = live ? __ldcg(reinterpret_cast<const float2*>(pm + (long long)cc * 16)) : make_float2(-INFINITY, 0.f);
+                    v[u] = live ? __ldcg(reinterpret_cast<const float4*>(po + (long long)cc * 8 * D)) : make_float4(0.f, 0.f, 0.f, 0.f);
                 }
-                const float inv = (L > 0.f) ? 1.0f / L : 0.f;
-                if (!*abort_flag)
-                    *reinterpret_cast<uint2*>(p.attn_out + (long long)(kvh * G + hq) * D + d) =
-                        make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
+                float Mc = M;
+#pragma unroll
+                for (int u = 0; u < kCombineBatch; ++u) Mc = fmaxf(Mc, ml[u].x);
+                const float keep = (Mc == -INFINITY) ? 0.f : mega_exp2(M - Mc);  // M == -inf: nothing accumulated yet, exp2 gives 0
+                L *= keep, acc.x *= keep, acc.y *= keep, acc.z *= keep, acc.w *= keep;
+#pragma unroll
+                for (int u = 0; u < kCombineBatch; ++u) {
+                    const float f = (Mc == -INFINITY) ? 0.f : mega_exp2(ml[u].x - Mc);
+                    L += f * ml[u].y;
+                    acc.x += f * v[u].x, acc.y += f * v[u].y, acc.z += f * v[u].z, acc.w += f * v[u].w;
+                }
+                M = Mc;
             }
+            for (int off = 1; off < ways; off <<= 1) {
+                const float M2 = __shfl_xor_sync(0xffffffffu, M, off), L2 = __shfl_xor_sync(0xffffffffu, L, off);
+                const float bx = __shfl_xor_sync(0xffffffffu, acc.x, off), by = __shfl_xor_sync(0xffffffffu, acc.y, off);
+                const float bz = __shfl_xor_sync(0xffffffffu, acc.z, off), bw = __shfl_xor_sync(0xffffffffu, acc.w, off);
+                const float Mn = fmaxf(M, M2);
+                // the lower way's term first, in both partners: the sum is the same bits on both sides
+                const bool low = (way & off) == 0;
+                const float Ma = low ? M : M2, Mb = low ? M2 : M;
+                const float fa = (Mn == -INFINITY) ? 0.f : mega_exp2(Ma - Mn), fb = (Mn == -INFINITY) ? 0.f : mega_exp2(Mb - Mn);
+                L = (low ? L : L2) * fa + (low ? L2 : L) * fb;
+                acc.x = (low ? acc.x : bx) * fa + (low ? bx : acc.x) * fb;
+                acc.y = (low ? acc.y : by) * fa + (low ? by : acc.y) * fb;
+                acc.z = (low ? acc.z : bz) * fa + (low ? bz : acc.z) * fb;
+                acc.w = (low ? acc.w : bw) * fa + (low ? bw : acc.w) * fb;
+                M = Mn;
+            }
+            const float inv = (L > 0.f) ? 1.0f / L : 0.f;
+            if (active && way == 0 && !*abort_flag)
+                *reinterpret_cast<uint2*>(p.attn_out + (long long)(kvh * G + hq) * D + d) =
+                    make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
             if (ct == 0) p.ctrl[MB_TICKET0 + kvh] = 0u;  // ready for the next launch
         }
     }
@@ -782,7 +924,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_layer_b1_kernel(const 
                                p.x2[n] = x2v;
                                res_s[n - s.o_r0] = __bfloat162float(x2v);  // the down projection adds onto this
                            },
-                           trec);
+                           trec, 32u);
     trace_mark(trec, 5);
     mega_grid_barrier(p, c, MB_OPROJ);
 
@@ -795,9 +937,18 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_layer_b1_kernel(const 
                               const float gate = round_bf16(v0), up = round_bf16(v1);
                               p.h[n] = __float2bfloat16_rn(round_bf16(silu_f32(gate)) * up);
                           },
-                          trec);
+                          trec, 33u);
     trace_mark(trec, 5);
     mega_grid_barrier(p, c, MB_GATEUP);
+    // No CTA touches a barrier counter after this point.  The CTA that gets here last returns them to zero for the
+    // next launch (which reads them only after this grid has finished); doing it now keeps it off the kernel's tail.
+    if (ct == 0) {
+        const unsigned int prev = atomicAdd(p.ctrl + MB_EXIT, 1u);
+        if (prev == gridDim.x - 1) {
+            p.ctrl[MB_QKV] = 0u, p.ctrl[MB_ATTN] = 0u, p.ctrl[MB_OPROJ] = 0u, p.ctrl[MB_GATEUP] = 0u;
+            p.ctrl[MB_EXIT] = 0u;
+        }
+    }
 
     // ================================================================ phase 4: down projection + residual
     trec = (ct == 0) ? trace_open(p.trace, 24u, cta_id) : nullptr;
@@ -805,20 +956,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_layer_b1_kernel(const 
     trace_mark(trec, 3);
     mega_gemv_phase<false>(p, c, s.o_r0, s.o_r1, p.I, p.kc_i, s.nkc_i,
                            [&](int n, float v0, float) { p.out[n] = __float2bfloat16_rn(res_s[n - s.o_r0] + round_bf16(v0)); },
-                           trec);
+                           trec, 34u);
     trace_mark(trec, 5);
 
-    // ---- the CTA that leaves last returns the barrier counters to zero for the next launch
-    named_bar_sync(1, kMegaConsumerThreads);
-    if (ct == 0) {
-        __threadfence();
-        const unsigned int prev = atomicAdd(p.ctrl + MB_EXIT, 1u);
-        if (prev == gridDim.x - 1) {
-            p.ctrl[MB_QKV] = 0u, p.ctrl[MB_ATTN] = 0u, p.ctrl[MB_OPROJ] = 0u, p.ctrl[MB_GATEUP] = 0u;
-            __threadfence();
-            p.ctrl[MB_EXIT] = 0u;
-        }
-    }
 }
 
 // ---------------------------------------------------------------------------
@@ -864,7 +1004,7 @@ static bool mega_plan(const MegaArgs& a, MegaPlan& pl) {
     pl.grid = grid;
     pl.kc_h = kc_of(a.H), pl.kc_q = kc_of(Q), pl.kc_i = kc_of(a.I);
     const int kc_max = pl.kc_h > pl.kc_q ? (pl.kc_h > pl.kc_i ? pl.kc_h : pl.kc_i) : (pl.kc_q > pl.kc_i ? pl.kc_q : pl.kc_i);
-    pl.stage_bytes = mega_align((size_t)8 * (kc_max + 8) * 2, 128);
+    pl.stage_bytes = mega_align((size_t)8 * (kc_max + kMegaRowPad) * 2, 128);
     int sub = (int)(pl.stage_bytes / ((size_t)a.D * 2)) / 8 * 8;
     if (sub > kMegaSubKeysMax) sub = kMegaSubKeysMax;
     if (sub < 8) return false;
@@ -872,13 +1012,16 @@ static bool mega_plan(const MegaArgs& a, MegaPlan& pl) {
     pl.nsp = mega_splits(a.S, a.NKV, grid);
     const int maxK = a.H > Q ? (a.H > a.I ? a.H : a.I) : (Q > a.I ? Q : a.I);
     const size_t xs_bytes = (size_t)maxK * 2 + 64;
-    const size_t attn_bytes = (size_t)sub * 32 + (size_t)8 * a.D * 2 + (size_t)2 * a.D * 2 + 128 + (size_t)8 * 4 * a.D * 4;
+    // attention scratch: probabilities 8 warps x 32 keys x 8 heads, rescale factors, q rows, new k/v, merge buffers
+    const size_t attn_bytes = (size_t)8192 + 256 + (size_t)8 * a.D * 2 + (size_t)2 * a.D * 2 + 512 + (size_t)8 * 4 * a.D * 4;
     pl.act_bytes = mega_align(xs_bytes > attn_bytes ? xs_bytes : attn_bytes, 128);
     const size_t fixed = kMegaHeaderBytes + kMegaRedBytes + kMegaResSlots * sizeof(float) + pl.act_bytes;
     const size_t cap = (size_t)max_smem_optin();
     if (fixed + 2 * pl.stage_bytes > cap) return false;
     int ns = (int)((cap - fixed) / pl.stage_bytes);
     if (ns > kMegaMaxStages) ns = kMegaMaxStages;
+    const int ns_cap = tuning(EZB_TUNE_MEGA_STAGES);
+    if (ns_cap >= 2 && ns > ns_cap) ns = ns_cap;
     pl.NS = ns;
     pl.smem = fixed + (size_t)ns * pl.stage_bytes;
     return true;
@@ -931,6 +1074,9 @@ cudaError_t launch_decode_mega(const MegaArgs& a, cudaStream_t stream) {
     p.NS = pl.NS;
     p.l2_window = tuning(EZB_TUNE_MEGA_L2_STAGES);
     if (p.l2_window < 0 || !tuning(EZB_TUNE_L2_PREFETCH)) p.l2_window = 0;
+    p.inflight = tuning(EZB_TUNE_MEGA_INFLIGHT);
+    if (p.inflight < 0 || p.inflight >= p.NS) p.inflight = 0;
+    p.gate = tuning(EZB_TUNE_MEGA_GATE) ? 1 : 0;
     p.stage_bytes = (unsigned int)pl.stage_bytes, p.act_bytes = (unsigned int)pl.act_bytes;
     p.wait_cycles = wait_limit_cycles();
     p.status = status_ptr();

@@ -318,6 +318,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapW0, const __grid_constant_
         pdl_wait();
         trace_mark(trec, 3);
         const unsigned int push_epoch = (LINK && p.link.world > 0 && p.link.push_inbox >= 0) ? tp_next_epoch(p.link, p.link.push_inbox) : 0u;
+        const bool poisoned = LINK && p.link.world > 0 && tp_poisoned(p.status);  // see tp_poisoned: push nothing, advance nothing
         const int nseg = *nseg_s;
         for (int seg = 0; seg < nseg; ++seg) {
             const int tile = segs[4 * seg], kb0 = segs[4 * seg + 1], kb1 = segs[4 * seg + 2];
@@ -392,7 +393,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapW0, const __grid_constant_
                             const int s2 = src + half * 16;
                             const float ax = __shfl_sync(0xffffffffu, acc[j].x, s2), ay = __shfl_sync(0xffffffffu, acc[j].y, s2);
                             const float az = __shfl_sync(0xffffffffu, acc[j].z, s2), aw = __shfl_sync(0xffffffffu, acc[j].w, s2);
-                            if (b0 + j < p.B && tile * kTcRows + half * 64 + 2 * lane < p.N)
+                            if (!poisoned && b0 + j < p.B && tile * kTcRows + half * 64 + 2 * lane < p.N)
                                 tp_push2(p.link, (long long)(b0 + j) * p.ldout + tile * kTcRows + half * 64 + 2 * lane,
                                          odd ? az : ax, odd ? aw : ay, push_epoch);
                         }
@@ -466,7 +467,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapW0, const __grid_constant_
                     } else if (LINK && p.epilogue == EPI_PUSH_F32) {
 #pragma unroll
                         for (int b = 0; b < NB; ++b)
-                            if (b < p.B) tp_push(p.link, (long long)b * p.ldout + n, v[b], push_epoch);
+                            if (b < p.B && !poisoned) tp_push(p.link, (long long)b * p.ldout + n, v[b], push_epoch);
                     } else if (p.epilogue == EPI_STORE_F32) {
 #pragma unroll
                         for (int b = 0; b < NB; ++b)
@@ -500,7 +501,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapW0, const __grid_constant_
             }
         }
         trace_mark(trec, 5);
-        if (LINK && p.link.world > 0 && p.link.bump_inbox >= 0 && blockIdx.x == 0 && et == 0) tp_bump(p.link);
+        if (LINK && p.link.world > 0 && p.link.bump_inbox >= 0 && blockIdx.x == 0 && et == 0 && !*abort_flag && !poisoned) tp_bump(p.link);
     }
 
     tc_fence_before();

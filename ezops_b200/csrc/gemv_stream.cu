@@ -140,7 +140,7 @@ __device__ __forceinline__ void load_x8(const bf16* srow, int i, uint32_t (&w)[4
 
 template <bool PERMUTE32, bool LINK, bool SINGLE>
 __device__ __forceinline__ void stage_activations(const GemvParams& p, bf16* xs, int xs_stride, float* scratch, int ct,
-                                                  int cw, int lane) {
+                                                  int cw, int lane, volatile int* abort_flag) {
     // independent 16-byte loads in flight per thread (16 spilled registers in the multi-row instances and was slower)
     constexpr int U = 8;
     const int nvec = p.K / 8;
@@ -172,12 +172,14 @@ __device__ __forceinline__ void stage_activations(const GemvParams& p, bf16* xs,
                 for (int i = sub; i < nvec; i += nthr) {
                     const uint4 raw = *reinterpret_cast<const uint4*>(xrow + i * 8);
                     float add[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                    tp_gather<2, 8>(p.link, epoch, (long long)b * p.K + i * 8, add, p.status, t0);
+                    // a gather that gave up (or a chain already poisoned) aborts the CTA: nothing is stored or pushed
+                    const bool ok = !*abort_flag && tp_gather<2, 8>(p.link, epoch, (long long)b * p.K + i * 8, add, p.status, t0);
+                    if (!ok) *abort_flag = 1;
                     uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
                     for (int e = 0; e < 4; ++e)
                         w4[e] = pack_bf16(bf16_lo(w4[e]) + round_bf16(add[2 * e]), bf16_hi(w4[e]) + round_bf16(add[2 * e + 1]));
-                    if (blockIdx.x == 0 && p.x_sum_out)
+                    if (ok && blockIdx.x == 0 && p.x_sum_out)
                         *reinterpret_cast<uint4*>(p.x_sum_out + (long long)b * p.ldsum + i * 8) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
@@ -190,12 +192,13 @@ __device__ __forceinline__ void stage_activations(const GemvParams& p, bf16* xs,
                 for (int h = sub; h < 2 * nvec; h += nthr) {  // h: half vector (4 elements)
                     const uint2 raw = *reinterpret_cast<const uint2*>(xrow + h * 4);
                     float add[4] = {0.f, 0.f, 0.f, 0.f};
-                    tp_gather<8, 4>(p.link, epoch, (long long)b * p.K + h * 4, add, p.status, t0);
+                    const bool ok = !*abort_flag && tp_gather<8, 4>(p.link, epoch, (long long)b * p.K + h * 4, add, p.status, t0);
+                    if (!ok) *abort_flag = 1;
                     uint32_t w2[2] = {raw.x, raw.y};
 #pragma unroll
                     for (int e = 0; e < 2; ++e)
                         w2[e] = pack_bf16(bf16_lo(w2[e]) + round_bf16(add[2 * e]), bf16_hi(w2[e]) + round_bf16(add[2 * e + 1]));
-                    if (blockIdx.x == 0 && p.x_sum_out)
+                    if (ok && blockIdx.x == 0 && p.x_sum_out)
                         *reinterpret_cast<uint2*>(p.x_sum_out + (long long)b * p.ldsum + h * 4) = make_uint2(w2[0], w2[1]);
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
@@ -430,7 +433,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_stream_kernel(const Gemv
     const int ct = tid - 32;  // 0..127 among consumer threads
     pdl_wait();
 
-    if (XRES) stage_activations<false, false, false>(p, xs, xs_stride, red, ct, cw, lane);
+    if (XRES) stage_activations<false, false, false>(p, xs, xs_stride, red, ct, cw, lane, abort_flag);
 
     const int g4 = lane >> 2, t4 = lane & 3;
     for (int rb = 0; rb < nrb; ++rb) {
@@ -626,7 +629,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_rows8_kernel(const GemvP
             res_s[i] = __bfloat162float(p.residual[(long long)b * p.ldres + r0 + r]);
         }
     const unsigned int push_epoch = (LINK && p.link.world > 0 && p.link.push_inbox >= 0) ? tp_next_epoch(p.link, p.link.push_inbox) : 0u;
-    stage_activations<true, LINK, SINGLE>(p, xs, xs_stride, red, ct, cw, lane);  // ends with a barrier among the consumers
+    if (LINK && p.link.world > 0 && tp_poisoned(p.status)) *abort_flag = 1;  // see tp_poisoned
+    stage_activations<true, LINK, SINGLE>(p, xs, xs_stride, red, ct, cw, lane, abort_flag);  // ends with a barrier among the consumers
 
     const int g4 = lane >> 2, t4 = lane & 3;
     const bool has_row = g4 < p.B;
@@ -634,7 +638,12 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_rows8_kernel(const GemvP
     const uint32_t lds_off = (uint32_t)(((lane & 7) * ws_stride + (lane >> 3) * 8) * (int)sizeof(bf16));
 
     for (int rb = 0; rb < nrb; ++rb) {
-        float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
+        // Eight independent accumulator chains per warp (four 32-element groups in flight, two k-steps each): a
+        // dependent mma.sync issues only after its predecessor has completed, and with two chains the warps spent
+        // most of a stage waiting on that latency, which capped the kernel just above the HBM rate.
+        float acc[8][4];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) acc[u][0] = acc[u][1] = acc[u][2] = acc[u][3] = 0.f;
         for (int kci = 0; kci < nkc; ++kci) {
             const int it = rb * nkc + kci;
             const int s = it % NS;
@@ -645,24 +654,40 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_rows8_kernel(const GemvP
             const int nk32 = len >> 5;
             const uint32_t w_base = smem_u32(stage_base + (size_t)s * stage_bytes) + lds_off;
             const bf16* xk = xrow + k0;
-            // The eight warps run eight independent mma chains; unrolling lets the
-            // loads of later iterations overlap the chain of the current one.
-#pragma unroll 4
-            for (int k32 = cw; k32 < nk32; k32 += kConsumerWarps) {
+            int k32 = cw;
+            for (; k32 + 3 * kConsumerWarps < nk32; k32 += 4 * kConsumerWarps) {
+                uint32_t w[4][4];
+                uint4 a[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    ldsm_x4(w_base + (uint32_t)((k32 + u * kConsumerWarps) * 32 * (int)sizeof(bf16)), w[u][0], w[u][1], w[u][2], w[u][3]);
+                    a[u] = make_uint4(0u, 0u, 0u, 0u);
+                    if (has_row) a[u] = *reinterpret_cast<const uint4*>(xk + (k32 + u * kConsumerWarps) * 32);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    mma_bf16_16816(acc[2 * u], a[u].x, 0u, a[u].y, 0u, w[u][0], w[u][1]);
+                    mma_bf16_16816(acc[2 * u + 1], a[u].z, 0u, a[u].w, 0u, w[u][2], w[u][3]);
+                }
+            }
+            for (; k32 < nk32; k32 += kConsumerWarps) {
                 uint32_t w0, w1, w2, w3;
                 ldsm_x4(w_base + (uint32_t)(k32 * 32 * (int)sizeof(bf16)), w0, w1, w2, w3);
                 uint4 a = make_uint4(0u, 0u, 0u, 0u);
                 if (has_row) a = *reinterpret_cast<const uint4*>(xk + k32 * 32);
-                mma_bf16_16816(acc0, a.x, 0u, a.y, 0u, w0, w1);
-                mma_bf16_16816(acc1, a.z, 0u, a.w, 0u, w2, w3);
+                mma_bf16_16816(acc[0], a.x, 0u, a.y, 0u, w0, w1);
+                mma_bf16_16816(acc[1], a.z, 0u, a.w, 0u, w2, w3);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&empty_bar[s]));
         }
+        // fixed summation order over the chains
+        const float sum0 = ((acc[0][0] + acc[1][0]) + (acc[2][0] + acc[3][0])) + ((acc[4][0] + acc[5][0]) + (acc[6][0] + acc[7][0]));
+        const float sum1 = ((acc[0][1] + acc[1][1]) + (acc[2][1] + acc[3][1])) + ((acc[4][1] + acc[5][1]) + (acc[6][1] + acc[7][1]));
         // rows 0..7 of the C tile are the batch; this thread holds (batch g4, weight rows 2*t4, 2*t4+1).
         // The reduction buffer alternates between row blocks, so one barrier per block is enough.
         float* redb = red + (rb & 1) * (kConsumerWarps * 64);
-        *reinterpret_cast<float2*>(redb + cw * 64 + g4 * 8 + t4 * 2) = make_float2(acc0[0] + acc1[0], acc0[1] + acc1[1]);
+        *reinterpret_cast<float2*>(redb + cw * 64 + g4 * 8 + t4 * 2) = make_float2(sum0, sum1);
         named_bar_sync(1, kConsumerThreads);
         if (ct < 64) {
             const int b = ct >> 3, j = ct & 7;
@@ -686,7 +711,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_rows8_kernel(const GemvP
             }
         }
     }
-    if (LINK && p.link.world > 0 && p.link.bump_inbox >= 0 && blockIdx.x == 0 && ct == 0) tp_bump(p.link);
+    if (LINK && p.link.world > 0 && p.link.bump_inbox >= 0 && blockIdx.x == 0 && ct == 0 && !*abort_flag) tp_bump(p.link);
     trace_mark(trec, 5);
 }
 

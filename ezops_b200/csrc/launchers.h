@@ -130,6 +130,7 @@ struct AttnArgs {
     const int* page_table = nullptr;
     int page_shift = 0;
     int max_pages = 0;
+    int num_pages = 0;  // pages in each pool
     PrefetchList next = {};
 };
 size_t attn_workspace_bytes(int B, int H, int NKV, int S, int D);

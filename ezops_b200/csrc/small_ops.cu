@@ -87,12 +87,13 @@ struct RowPrepParams {
     unsigned int* status;
 };
 
-__device__ __forceinline__ uint4 load_row8(const RowPrepParams& p, long long row, int i, unsigned int epoch, long long t0) {
+// `ok` turns false (and stays false) when the wait for the peers' partials ran out: the caller then stores nothing.
+__device__ __forceinline__ uint4 load_row8(const RowPrepParams& p, long long row, int i, unsigned int epoch, long long t0, bool& ok) {
     uint4 raw = *reinterpret_cast<const uint4*>(p.x + row * p.ldx + i * 8);
     if (p.link.world > 0 && p.link.gather_inbox >= 0) {
         // the term to add is the sum, in rank order, of the partials in this rank's inbox
         float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        tp_gather<8, 8>(p.link, epoch, row * p.dim + i * 8, a, p.status, t0);
+        ok = ok && tp_gather<8, 8>(p.link, epoch, row * p.dim + i * 8, a, p.status, t0);
         raw.x = pack_bf16(bf16_lo(raw.x) + round_bf16(a[0]), bf16_hi(raw.x) + round_bf16(a[1]));
         raw.y = pack_bf16(bf16_lo(raw.y) + round_bf16(a[2]), bf16_hi(raw.y) + round_bf16(a[3]));
         raw.z = pack_bf16(bf16_lo(raw.z) + round_bf16(a[4]), bf16_hi(raw.z) + round_bf16(a[5]));
@@ -113,14 +114,16 @@ __global__ void __launch_bounds__(kRowThreads) row_prep_kernel(const RowPrepPara
     pdl_trigger();
     pdl_wait();
     const bool gather = p.link.world > 0 && p.link.gather_inbox >= 0;
+    if (gather && tp_poisoned(p.status)) return;  // see tp_poisoned: the chain already gave up a wait
     const unsigned int epoch = gather ? tp_next_epoch(p.link, p.link.gather_inbox) : 0u;
     const long long t0 = clock64();
     const long long row = blockIdx.x;
     const int nvec = p.dim / 8;
     float ssq = 0.f;
+    bool ok = true;
     for (int i = threadIdx.x; i < nvec; i += kRowThreads) {
-        const uint4 s = load_row8(p, row, i, epoch, t0);
-        if (p.sum_out) *reinterpret_cast<uint4*>(p.sum_out + row * p.ldsum + i * 8) = s;
+        const uint4 s = load_row8(p, row, i, epoch, t0, ok);
+        if (ok && p.sum_out) *reinterpret_cast<uint4*>(p.sum_out + row * p.ldsum + i * 8) = s;
         const uint32_t w[4] = {s.x, s.y, s.z, s.w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) ssq += bf16_lo(w[e]) * bf16_lo(w[e]) + bf16_hi(w[e]) * bf16_hi(w[e]);
@@ -132,7 +135,8 @@ __global__ void __launch_bounds__(kRowThreads) row_prep_kernel(const RowPrepPara
         r = 1.0f / sqrtf(tot / (float)p.dim + p.eps);
     }
     for (int i = threadIdx.x; i < nvec; i += kRowThreads) {
-        const uint4 s = load_row8(p, row, i, epoch, t0);
+        const uint4 s = load_row8(p, row, i, epoch, t0, ok);
+        if (!ok) continue;
         uint32_t v[4] = {s.x, s.y, s.z, s.w};
         if (p.normalize) {
             uint32_t nw[4] = {0, 0, 0, 0};

@@ -187,7 +187,7 @@ class AttnDecodeSm100Kernel(BaseKernel):
         _lib.check(
             self._lib.ezb_attn_decode_paged(
                 Q.data_ptr(), K_pool.data_ptr(), V_pool.data_ptr(), page_table.data_ptr(), out.data_ptr(), ws.data_ptr(),
-                ws.numel(), B, H, NKV, max_pages, page_size, D, seq_lens.data_ptr(), _stream(),
+                ws.numel(), B, H, NKV, max_pages, page_size, D, K_pool.shape[0], seq_lens.data_ptr(), _stream(),
             )
         )
         return out
@@ -352,8 +352,8 @@ class Qwen3DecodeStackSm100Kernel(BaseKernel):
                 self._lib.ezb_qwen3_decode_stack_paged(
                     hidden.data_ptr(), out.data_ptr(), table, self.L, cos.data_ptr() if cos is not None else None,
                     sin.data_ptr() if sin is not None else None, seq_lens.data_ptr(), page_table.data_ptr(), page_size,
-                    page_table.shape[1], ws.data_ptr(), ws.numel(), self.B, self.H, self.I, self.NH, self.NKV, self.D,
-                    self.rms_eps, _stream(),
+                    page_table.shape[1], layers[0]["K_cache"].shape[0], ws.data_ptr(), ws.numel(), self.B, self.H, self.I,
+                    self.NH, self.NKV, self.D, self.rms_eps, _stream(),
                 )
             )
             return out

@@ -69,7 +69,11 @@ typedef struct CUstream_st* ezb_stream_t; /* same type as cudaStream_t */
 #define EZB_TUNE_MEGA 17              /* 1: the batch-1 decode layer runs as one persistent kernel when the shape allows (default 1) */
 #define EZB_TUNE_MEGA_L2_STAGES 18    /* single-kernel layer: stages a producer with a full ring may pull into L2 ahead (default 6) */
 #define EZB_TUNE_WAIT_LIMIT_MS 19     /* budget of one device-side wait in the single-kernel layer and the cross-rank waits, ms at 2 GHz (default 1000) */
-#define EZB_TUNE_COUNT 20
+#define EZB_TUNE_MEGA_STAGES 20       /* single-kernel layer: cap on the ring depth (0 = as many as fit)                            */
+#define EZB_TUNE_MEGA_INFLIGHT 21     /* single-kernel layer: stages that may be requested but not yet landed (0 = whole ring)    */
+#define EZB_TUNE_MEGA_GATE 22         /* single-kernel layer: 1 = a producer stops behind its K/V stages until the QKV barrier is passed */
+#define EZB_TUNE_TP_WAIT_LIMIT_MS 23   /* fused exchange: budget of one wait for the peers' partial sums, ms at 2 GHz (default 5000)      */
+#define EZB_TUNE_COUNT 24
 
 int ezb_version(void);
 const char* ezb_strerror(int code);
@@ -271,14 +275,18 @@ unsigned long long ezb_launch_count(void);
  * Workspace as for S = max_pages * page_size.  The stack form takes the pools
  * through ezb_layer_t.K_cache / V_cache (one pool pair per layer, one page
  * table for all layers); the new token of row b goes to the page slot of
- * position seq_lens[b] - 1, which the caller has mapped. */
+ * position seq_lens[b] - 1, which the caller has mapped.  num_pages is the
+ * number of pages in each pool: a table entry outside [0, num_pages) inside a
+ * row's valid length (a stale id, or -1 for "unallocated") is never
+ * dereferenced - the kernel zero-fills that tile, skips the cache write,
+ * records fault 0x302 in the status word (ezb_device_status) and carries on. */
 int ezb_attn_decode_paged(const void* Q, const void* K_pool, const void* V_pool, const int* page_table, void* Out,
                           void* workspace, size_t workspace_bytes, int B, int H, int NKV, int max_pages, int page_size, int D,
-                          const int* seq_lens, ezb_stream_t stream);
+                          int num_pages, const int* seq_lens, ezb_stream_t stream);
 int ezb_qwen3_decode_stack_paged(const void* hidden, void* out, const ezb_layer_t* layers, int n_layers, const void* rope_cos,
                                  const void* rope_sin, const int* seq_lens, const int* page_table, int page_size,
-                                 int max_pages, void* workspace, size_t workspace_bytes, int B, int H, int I, int NH, int NKV,
-                                 int D, float eps, ezb_stream_t stream);
+                                 int max_pages, int num_pages, void* workspace, size_t workspace_bytes, int B, int H, int I,
+                                 int NH, int NKV, int D, float eps, ezb_stream_t stream);
 
 /* The stack of layers, tensor parallel with the exchange fused into the kernels:
  * ezb_qwen3_decode_stack on this rank's shards (as ezb_qwen3_decode_layer_tp_fused

@@ -67,6 +67,13 @@ def test_c_abi_rejects_bad_arguments_without_a_gpu():
     assert lib.ezb_gemv_bf16(ctypes.c_void_p(0x1002), fake, fake, 16, 64, None) == _lib.EZB_ERR_INVALID_ARGUMENT
     assert lib.ezb_attn_decode(fake, fake, fake, fake, None, 0, 1, 8, 3, 128, 128, None, None) == _lib.EZB_ERR_UNSUPPORTED_SHAPE
     assert lib.ezb_attn_decode(fake, fake, fake, fake, None, 0, 1, 8, 2, 128, 128, None, None) == _lib.EZB_ERR_WORKSPACE
+    # an output pointer that is only 2-byte aligned (a sliced view) is refused, not handed to 8-byte vector stores
+    odd = ctypes.c_void_p(0x1002)
+    assert lib.ezb_attn_decode(fake, fake, fake, odd, fake, 1 << 30, 1, 8, 2, 128, 128, None, None) == _lib.EZB_ERR_INVALID_ARGUMENT
+    assert lib.ezb_attn_decode_paged(fake, fake, fake, fake, odd, fake, 1 << 30, 1, 8, 2, 2, 64, 128, 4, fake, None) == _lib.EZB_ERR_INVALID_ARGUMENT
+    assert lib.ezb_attn_decode_static(fake, fake, fake, odd, 1, 8, 2, 128, 128, None, None) == _lib.EZB_ERR_INVALID_ARGUMENT
+    assert lib.ezb_gemv_bf16(fake, fake, ctypes.c_void_p(0x1001), 16, 64, None) == _lib.EZB_ERR_INVALID_ARGUMENT
+    assert lib.ezb_attn_decode_paged(fake, fake, fake, fake, fake, fake, 1 << 30, 1, 8, 2, 2, 64, 128, 0, fake, None) == _lib.EZB_ERR_INVALID_ARGUMENT  # no pages
     assert lib.ezb_qwen3_decode_layer(fake, fake, fake, fake, fake, fake, fake, fake, fake, 1 << 30, 1, 128, 2048, 6144,
                                       16, 6, 128, 1e-6, None) == _lib.EZB_ERR_UNSUPPORTED_SHAPE
     assert lib.ezb_qwen3_decode_layer(fake, fake, fake, fake, fake, fake, fake, fake, fake, 1 << 30, 65, 128, 2048, 6144,

@@ -699,3 +699,102 @@ def test_paged_decode_stack_matches_the_contiguous_stack(ez):
         assert torch.equal(_from_pages(Lp["K_cache"].cpu(), table, P), Lc["K_cache"].cpu())
         assert torch.equal(_from_pages(Lp["V_cache"].cpu(), table, P), Lc["V_cache"].cpu())
 
+
+
+def test_paged_attention_reports_a_page_id_outside_the_pool(ez):
+    """A stale or unallocated (-1) page-table entry inside a row's valid length must not be dereferenced: the call
+    returns, the status word reads 0x302, rows with good tables are still right, and the next call is healthy."""
+    from ezops_b200 import _lib
+    from ezops_b200 import workloads as wl
+
+    B, H, NKV, D, S, P = 3, 16, 4, 128, 512, 64
+    (Q, K, V), _ = wl.attn_decode_inputs(batch=B, num_heads=H, num_kv_heads=NKV, head_dim=D, max_len=S, min_len=1)
+    lens = [512, 300, 129]
+    perm = torch.randperm(B * (S // P) + 3, generator=torch.Generator().manual_seed(9))
+    Kp, table = _to_pages(K, P, perm)
+    Vp, _ = _to_pages(V, P, perm)
+    bad = table.clone()
+    bad[1, 2] = -1                 # inside row 1's 300 keys: "unallocated"
+    bad[2, 1] = Kp.shape[0] + 5    # inside row 2's 129 keys: beyond the pool
+    bad[2, 7] = -1                 # beyond row 2's length: never looked at
+    op = ez.AttnDecodeOp(B, H, S, D, backend="cuda", num_kv_heads=NKV, seq_lens=lens)
+    lens_d = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    got = op._kernel.call_paged(Q.cuda(), Kp.cuda(), Vp.cuda(), bad.cuda(), lens_d, P)
+    assert _lib.device_status() == 0x302  # reads and clears
+    ref = orc.attn_decode_ref(Q, K, V, seq_lens=lens)
+    assert torch.allclose(got[0].cpu().float(), ref[0].float(), atol=1e-2, rtol=1e-2)  # the row with a good table
+    again = op._kernel.call_paged(Q.cuda(), Kp.cuda(), Vp.cuda(), table.cuda(), lens_d, P)
+    assert _lib.device_status() == 0
+    assert torch.allclose(again.cpu().float(), ref.float(), atol=1e-2, rtol=1e-2)
+
+
+def test_fused_exchange_wait_runs_out_and_poisons_the_chain(ez):
+    """A peer that never delivers: world of two with both communication buffers on this GPU and nobody playing
+    rank 1.  With the wait budget at 2 ms the gathering kernel gives up, records 0x201, stores nothing and pushes
+    nothing; the kernels behind it see the fault and stay silent too, so the output buffer is untouched.  Nothing
+    traps, nothing is left spinning, and after clearing the status word a world-of-one call is healthy again."""
+    import ctypes
+
+    from ezops_b200 import _lib
+    from ezops_b200 import workloads as wl
+
+    lib = _lib.load()
+    sh, B, S = wl.QWEN3_0_6B, 1, 200
+    data = dev(*wl.decode_layer_inputs(sh, B, S))
+    hidden, Kc, Vc, Wqkv, Wo, Wgu, Wd = data
+    K0 = Kc.clone()
+    nbytes = lib.ezb_tp_comm_bytes(B, sh.hidden)
+    bufs = [ctypes.c_void_p(), ctypes.c_void_p()]
+    for b in bufs:
+        _lib.check(lib.ezb_tp_comm_alloc(nbytes, ctypes.byref(b)))
+    ws = torch.zeros(lib.ezb_qwen3_decode_layer_workspace_bytes(B, S, sh.hidden, sh.inter, sh.num_heads, sh.num_kv_heads, sh.head_dim),
+                     dtype=torch.uint8, device="cuda")
+    out = torch.full_like(hidden, 7.0)
+    s = torch.cuda.current_stream().cuda_stream
+
+    def call(world):
+        bases = (ctypes.c_void_p * world)(*[b.value for b in bufs[:world]])
+        return lib.ezb_qwen3_decode_layer_tp_fused(
+            hidden.data_ptr(), Kc.data_ptr(), Vc.data_ptr(), Wqkv.data_ptr(), Wo.data_ptr(), Wgu.data_ptr(), Wd.data_ptr(),
+            out.data_ptr(), ws.data_ptr(), ws.numel(), bases, world, 0, B, S, sh.hidden, sh.inter, sh.num_heads,
+            sh.num_kv_heads, sh.head_dim, 1e-6, s)
+
+    try:
+        _lib.set_tuning(tp_wait_limit_ms=2)
+        t0 = torch.cuda.Event(enable_timing=True)
+        t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        assert call(2) == _lib.EZB_OK  # the call only enqueues; the fault is found on the device
+        t1.record()
+        torch.cuda.synchronize()
+        assert t0.elapsed_time(t1) < 500.0  # gave up after about the budget, not after seconds
+        word = ctypes.c_uint(0)
+        assert lib.ezb_device_status(ctypes.byref(word), 0) == _lib.EZB_ERR_DEVICE_FAULT and word.value == 0x201
+        assert torch.equal(out, torch.full_like(out, 7.0)), "a rank that gave up must not publish a result"
+        # a second call while the fault stands: still silent (no gather, no push), and quick
+        t0.record()
+        assert call(2) == _lib.EZB_OK
+        t1.record()
+        torch.cuda.synchronize()
+        assert t0.elapsed_time(t1) < 50.0
+        assert torch.equal(out, torch.full_like(out, 7.0))
+        assert _lib.device_status() == 0x201  # reads and clears
+    finally:
+        _lib.set_tuning(tp_wait_limit_ms=5000)
+        torch.cuda.synchronize()
+        _lib.device_status()
+    # fresh buffers (the aborted calls left epochs and cells in an undefined state), world of one: healthy again
+    for b in bufs:
+        _lib.check(lib.ezb_tp_comm_free(b))
+    bufs = [ctypes.c_void_p()]
+    _lib.check(lib.ezb_tp_comm_alloc(nbytes, ctypes.byref(bufs[0])))
+    try:
+        Kc.copy_(K0)
+        assert call(1) == _lib.EZB_OK
+        torch.cuda.synchronize()
+        assert _lib.device_status() == 0
+        ref = orc.qwen3_dense_decode_ref(*(t.cpu() for t in (hidden, K0, Vc, Wqkv, Wo, Wgu, Wd)), sh.num_heads, sh.num_kv_heads, sh.head_dim)
+        assert rel_fro(out, ref) < 1e-2
+    finally:
+        torch.cuda.synchronize()
+        _lib.check(lib.ezb_tp_comm_free(bufs[0]))
