@@ -285,6 +285,29 @@ __device__ __forceinline__ float mega_ldcg_bf16(const bf16* ptr) {
     return bf16_bits_to_float((uint32_t)__ldcg(reinterpret_cast<const unsigned short*>(ptr)));
 }
 
+// ---- explicit shared-memory loads (a pointer that went through a struct loses its address space, and generic loads
+// are what the compiler then emits)
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float4 lds128f(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
+}
+
 // Everything a consumer thread carries through the phases.
 struct MegaCtx {
     uint64_t* full_bar;
@@ -349,12 +372,12 @@ __device__ __forceinline__ void mega_gemv_phase(const MegaParams& p, MegaCtx& c,
     constexpr int UNITS = PAIR ? 4 : 8;
     // With tracing on, lane 0 of every warp adds up the cycles it spends waiting for stages, computing, and in the
     // cross-warp reduction, and leaves them in a trace record {prof_id, block*8 + warp, wait, compute, reduce, stages}.
-    const bool prof = p.trace.buf != nullptr && c.lane == 0;
+    const bool prof = p.trace.buf != nullptr && (p.trace.capacity & 1u) && c.lane == 0;  // per-warp cycle accounting: odd capacities only
     long long cyc_wait = 0, cyc_comp = 0, cyc_red = 0, stages_done = 0;
     const int nrb = (r1 - r0 + UNITS - 1) / UNITS;
     const int row_bytes = (kc + kMegaRowPad) * 2;
     const int g4 = c.lane >> 2, t4 = c.lane & 3;
-    const unsigned char* xs_b = c.act + t4 * 16;
+    const uint32_t xs_b = smem_u32(c.act) + t4 * 16;
     const uint32_t lane_off = (uint32_t)(g4 * row_bytes + t4 * 16);
     bool first = true;
     auto reduce_group = [&](int rb_first, int count, const float* redb) {
@@ -390,30 +413,30 @@ __device__ __forceinline__ void mega_gemv_phase(const MegaParams& p, MegaCtx& c,
             const int k0 = kci * kc;
             const int len = min(kc, K - k0);
             const int nk32 = len >> 5, half = (nk32 + 1) >> 1;
-            const unsigned char* wl = c.stage_base + (size_t)s * p.stage_bytes + lane_off;
+            const uint32_t wl = smem_u32(c.stage_base) + (uint32_t)s * p.stage_bytes + lane_off;
             // x for column 0 (lanes g4 == 0: group j) and column 1 (lanes g4 == 1: group j + half)
-            const unsigned char* xl = xs_b + (size_t)k0 * 2 + (g4 == 1 ? half * 64 : 0);
+            const uint32_t xl = xs_b + (uint32_t)k0 * 2 + (g4 == 1 ? half * 64 : 0);
             const bool has_x = g4 < 2;
             int pr = c.cw;
             for (; pr + kMegaConsumerWarps < half; pr += 2 * kMegaConsumerWarps) {  // two pairs in flight
                 const int p1 = pr + kMegaConsumerWarps;
-                const uint4 l0 = *reinterpret_cast<const uint4*>(wl + pr * 64);
-                const uint4 l1 = *reinterpret_cast<const uint4*>(wl + p1 * 64);
+                const uint4 l0 = lds128(wl + pr * 64);
+                const uint4 l1 = lds128(wl + p1 * 64);
                 uint4 h0 = make_uint4(0u, 0u, 0u, 0u), h1 = h0, x0 = h0, x1 = h0;
-                if (pr + half < nk32) h0 = *reinterpret_cast<const uint4*>(wl + (pr + half) * 64);
-                if (p1 + half < nk32) h1 = *reinterpret_cast<const uint4*>(wl + (p1 + half) * 64);
-                if (has_x && (g4 == 0 || pr + half < nk32)) x0 = *reinterpret_cast<const uint4*>(xl + pr * 64);
-                if (has_x && (g4 == 0 || p1 + half < nk32)) x1 = *reinterpret_cast<const uint4*>(xl + p1 * 64);
+                if (pr + half < nk32) h0 = lds128(wl + (pr + half) * 64);
+                if (p1 + half < nk32) h1 = lds128(wl + (p1 + half) * 64);
+                if (has_x && (g4 == 0 || pr + half < nk32)) x0 = lds128(xl + pr * 64);
+                if (has_x && (g4 == 0 || p1 + half < nk32)) x1 = lds128(xl + p1 * 64);
                 mma_bf16_16816(acc[0], l0.x, h0.x, l0.y, h0.y, x0.x, x0.y);
                 mma_bf16_16816(acc[1], l0.z, h0.z, l0.w, h0.w, x0.z, x0.w);
                 mma_bf16_16816(acc[2], l1.x, h1.x, l1.y, h1.y, x1.x, x1.y);
                 mma_bf16_16816(acc[3], l1.z, h1.z, l1.w, h1.w, x1.z, x1.w);
             }
             for (; pr < half; pr += kMegaConsumerWarps) {
-                const uint4 l0 = *reinterpret_cast<const uint4*>(wl + pr * 64);
+                const uint4 l0 = lds128(wl + pr * 64);
                 uint4 h0 = make_uint4(0u, 0u, 0u, 0u), x0 = h0;
-                if (pr + half < nk32) h0 = *reinterpret_cast<const uint4*>(wl + (pr + half) * 64);
-                if (has_x && (g4 == 0 || pr + half < nk32)) x0 = *reinterpret_cast<const uint4*>(xl + pr * 64);
+                if (pr + half < nk32) h0 = lds128(wl + (pr + half) * 64);
+                if (has_x && (g4 == 0 || pr + half < nk32)) x0 = lds128(xl + pr * 64);
                 mma_bf16_16816(acc[0], l0.x, h0.x, l0.y, h0.y, x0.x, x0.y);
                 mma_bf16_16816(acc[1], l0.z, h0.z, l0.w, h0.w, x0.z, x0.w);
             }
@@ -665,7 +688,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_layer_b1_kernel(const 
         }
         named_bar_sync(1, kMegaConsumerThreads);
 
-        unsigned long long* trec2 = (ct == 0) ? trace_open(p.trace, 25u, cta_id) : nullptr;  // detail: q ready | first scores | P.V done | record + ticket
+        unsigned long long* trec2 = (ct == 0) ? trace_open(p.trace, 25u, cta_id) : nullptr;  // detail: q ready | V stage landed | P.V done | record + ticket
         // A fragments of Q (rows = query heads of this kv head); element order matches the K loads below
         uint4 qf[DPL];
 #pragma unroll
@@ -707,7 +730,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_layer_b1_kernel(const 
                     for (int u = 0; u < 4; ++u) {
                         const int kb = cw + u * kMegaConsumerWarps;
                         kf[u] = make_uint4(0u, 0u, 0u, 0u);
-                        if (kb < nblk) kf[u] = *reinterpret_cast<const uint4*>(Kst + ((size_t)(kb * 8 + g4) * D + t4 * 8) * 2 + 64 * j);
+                        if (kb < nblk) kf[u] = lds128(smem_u32(Kst) + (uint32_t)(((kb * 8 + g4) * D + t4 * 8) * 2 + 64 * j));
                     }
 #pragma unroll
                     for (int u = 0; u < 4; ++u) mma_bf16_16816(acc[u], qf[j].x, 0u, qf[j].y, 0u, kf[u].x, kf[u].y);
@@ -725,7 +748,6 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_layer_b1_kernel(const 
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&empty_bar[sk]));
             ++c.it;
-            if (sub == 0) trace_mark(trec2, 3);
             // ---- online soft-max (exp2 domain) for head g4 over this warp's keys
             float mx = -INFINITY;
 #pragma unroll
@@ -768,35 +790,46 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_layer_b1_kernel(const 
 #pragma unroll
                     for (int j = 0; j < DPL; ++j) o[h][j] *= al[h];
             }
+            if (sub == 0) trace_mark(trec2, 3);
+            {
+                const uint32_t pw_a = smem_u32(Pw), v_a = smem_u32(Vst) + lane * (DPL * 2);
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int kb = cw + u * kMegaConsumerWarps;
-                if (kb < nblk) {
+                for (int u = 0; u < 4; ++u) {
+                    const int kb = cw + u * kMegaConsumerWarps;
+                    if (kb < nblk) {
+                        // the eight keys of a block: all loads first.  Keys beyond n have probability 0 and read the
+                        // row of key n-1 instead (finite values), so no branch per key is needed.
+                        float4 pl[8], ph[8];
+                        float v[8][DPL];
 #pragma unroll
-                    for (int kk = 0; kk < 8; ++kk) {
-                        const int key = kb * 8 + kk;
-                        if (key < n) {
-                            const float4 p0 = *reinterpret_cast<const float4*>(Pw + (u * 8 + kk) * 8);
-                            float v[DPL];
+                        for (int kk = 0; kk < 8; ++kk) {
+                            const int key = min(kb * 8 + kk, n - 1);
+                            pl[kk] = lds128f(pw_a + (uint32_t)((u * 8 + kk) * 32));
+                            ph[kk] = (G > 4) ? lds128f(pw_a + (uint32_t)((u * 8 + kk) * 32 + 16)) : make_float4(0.f, 0.f, 0.f, 0.f);
                             if (DPL == 4) {
-                                const uint2 raw = *reinterpret_cast<const uint2*>(Vst + (size_t)key * D * 2 + lane * 8);
-                                v[0] = bf16_lo(raw.x), v[1] = bf16_hi(raw.x), v[DPL - 2] = bf16_lo(raw.y), v[DPL - 1] = bf16_hi(raw.y);
+                                const uint2 raw = lds64(v_a + (uint32_t)(key * D * 2));
+                                v[kk][0] = bf16_lo(raw.x), v[kk][1] = bf16_hi(raw.x), v[kk][DPL - 2] = bf16_lo(raw.y), v[kk][DPL - 1] = bf16_hi(raw.y);
                             } else {
-                                const uint32_t raw = *reinterpret_cast<const uint32_t*>(Vst + (size_t)key * D * 2 + lane * 4);
-                                v[0] = bf16_lo(raw), v[1] = bf16_hi(raw);
+                                const uint32_t raw = lds32(v_a + (uint32_t)(key * D * 2));
+                                v[kk][0] = bf16_lo(raw), v[kk][1] = bf16_hi(raw);
                             }
-                            const float pl[4] = {p0.x, p0.y, p0.z, p0.w};
+                        }
+#pragma unroll
+                        for (int kk = 0; kk < 8; ++kk) {
+                            const float p4[4] = {pl[kk].x, pl[kk].y, pl[kk].z, pl[kk].w};
 #pragma unroll
                             for (int h = 0; h < 4; ++h)
 #pragma unroll
-                                for (int j = 0; j < DPL; ++j) o[h][j] = fmaf(pl[h], v[j], o[h][j]);
-                            if (G > 4) {
-                                const float4 p1 = *reinterpret_cast<const float4*>(Pw + (u * 8 + kk) * 8 + 4);
-                                const float ph[4] = {p1.x, p1.y, p1.z, p1.w};
+                                for (int j = 0; j < DPL; ++j) o[h][j] = fmaf(p4[h], v[kk][j], o[h][j]);
+                        }
+                        if (G > 4) {
+#pragma unroll
+                            for (int kk = 0; kk < 8; ++kk) {
+                                const float p4[4] = {ph[kk].x, ph[kk].y, ph[kk].z, ph[kk].w};
 #pragma unroll
                                 for (int h = 0; h < 4; ++h)
 #pragma unroll
-                                    for (int j = 0; j < DPL; ++j) o[4 + h][j] = fmaf(ph[h], v[j], o[4 + h][j]);
+                                    for (int j = 0; j < DPL; ++j) o[4 + h][j] = fmaf(p4[h], v[kk][j], o[4 + h][j]);
                             }
                         }
                     }

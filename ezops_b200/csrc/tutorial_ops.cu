@@ -127,7 +127,9 @@ cudaError_t launch_vector_add_f32(const float* A, const float* B, float* C, long
 
 cudaError_t launch_softmax_f32(const float* X, float* Out, int rows, int dim, cudaStream_t stream) {
     const size_t bytes = (size_t)dim * sizeof(float);
-    const int staged = bytes <= 48 * 1024;  // the default dynamic shared-memory limit: no attribute to set
+    // The 48 KB a launch may use without an opt-in attribute cover static + dynamic shared memory, and the kernel
+    // holds a few static words (the reduction scratch): leave 1 KB for them.
+    const int staged = bytes <= 47 * 1024;
     count_launch();
     softmax_f32_kernel<<<rows, kThreads, staged ? bytes : 0, stream>>>(X, Out, dim, staged);
     return cudaGetLastError();

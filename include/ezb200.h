@@ -67,10 +67,10 @@ typedef struct CUstream_st* ezb_stream_t; /* same type as cudaStream_t */
 #define EZB_TUNE_TP_POLL_ALL 15       /* fused exchange prologue: 0 = by world size (all ranks at once when > 2), 1 = always, 2 = never */
 #define EZB_TUNE_TP_PULL 16           /* fused exchange direction: 0 = push (default), 1 = pull (consumers read the peers' buffers) */
 #define EZB_TUNE_MEGA 17              /* 1: the batch-1 decode layer runs as one persistent kernel when the shape allows (default 1) */
-#define EZB_TUNE_MEGA_L2_STAGES 18    /* single-kernel layer: stages a producer with a full ring may pull into L2 ahead (default 6) */
+#define EZB_TUNE_MEGA_L2_STAGES 18    /* single-kernel layer: stages a producer with a full ring may pull into L2 ahead (default 0) */
 #define EZB_TUNE_WAIT_LIMIT_MS 19     /* budget of one device-side wait in the single-kernel layer and the cross-rank waits, ms at 2 GHz (default 1000) */
 #define EZB_TUNE_MEGA_STAGES 20       /* single-kernel layer: cap on the ring depth (0 = as many as fit)                            */
-#define EZB_TUNE_MEGA_INFLIGHT 21     /* single-kernel layer: stages that may be requested but not yet landed (0 = whole ring)    */
+#define EZB_TUNE_MEGA_INFLIGHT 21     /* single-kernel layer: stages that may be requested but not yet landed (0 = whole ring; default 2) */
 #define EZB_TUNE_MEGA_GATE 22         /* single-kernel layer: 1 = a producer stops behind its K/V stages until the QKV barrier is passed */
 #define EZB_TUNE_TP_WAIT_LIMIT_MS 23   /* fused exchange: budget of one wait for the peers' partial sums, ms at 2 GHz (default 5000)      */
 #define EZB_TUNE_COUNT 24

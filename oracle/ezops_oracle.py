@@ -294,3 +294,19 @@ def shard_layer_weights(Wqkv, Wo, Wgu, Wd, num_heads, num_kv_heads, head_dim, tp
 def shard_kv_cache(cache, tp: int, rank: int):
     nkv = cache.shape[1] // tp
     return cache[:, rank * nkv : (rank + 1) * nkv].contiguous()
+
+
+# ---- the reference's teaching operators (CPU, float64 accumulation: an oracle independent of any GPU result) ----
+def vector_add_ref(A: torch.Tensor, B: torch.Tensor) -> torch.Tensor:
+    """C = A + B in fp32 (ezops/ops/vector_add.py:29-30)."""
+    return A.cpu() + B.cpu()
+
+
+def softmax_ref(X: torch.Tensor) -> torch.Tensor:
+    """Row soft-max (ezops/ops/softmax.py:35-36), computed in float64 and rounded to fp32 once."""
+    return torch.softmax(X.cpu().double(), dim=-1).float()
+
+
+def reduce_sum_ref(A: torch.Tensor) -> torch.Tensor:
+    """Sum of all elements (ezops/ops/reduce.py:32-33), accumulated in float64."""
+    return A.cpu().double().sum().float().reshape(1)

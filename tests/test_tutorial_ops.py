@@ -7,6 +7,7 @@ import torch
 
 import ezops_b200 as ez
 from ezops_b200.ops.utils import check_determinism, check_input_readonly
+from oracle import ezops_oracle as orc
 
 
 def test_reference_forwards_on_cpu():
@@ -25,13 +26,27 @@ def test_reference_forwards_on_cpu():
         assert "cuda" in ez.list_backends(name)
 
 
+def test_cpu_oracle_of_the_teaching_ops_agrees_with_the_op_references():
+    """The float64 CPU oracle the GPU tests compare against, tied to the operators' own fp32 references."""
+    torch.manual_seed(3)
+    X = torch.randn(5, 777)
+    want = torch.empty_like(X)
+    ez.SoftmaxOp(5, 777)(X, want)
+    assert torch.allclose(orc.softmax_ref(X), want, atol=1e-6, rtol=1e-5)
+    assert torch.allclose(orc.softmax_ref(X).sum(-1), torch.ones(5), atol=1e-6)
+    A = torch.randn(10000)
+    assert torch.allclose(orc.reduce_sum_ref(A), A.sum().reshape(1), atol=1e-3)
+    assert torch.equal(orc.vector_add_ref(A, A), A + A)
+
+
 @pytest.mark.gpu
-@pytest.mark.parametrize("batch,dim", [(1, 64), (128, 1024), (3, 100), (7, 4097), (4096, 4096), (2, 20000)])
+@pytest.mark.parametrize("batch,dim", [(1, 64), (128, 1024), (3, 100), (7, 4097), (4096, 4096), (2, 20000),
+                                       (3, 12032), (3, 12033), (3, 12288), (3, 12289)])  # around the shared-memory staging limit
 def test_softmax_cuda(batch, dim):
     torch.manual_seed(42)
     ref = ez.SoftmaxOp(batch, dim, backend="ref")
-    X, want = ref.gen_data()
-    ref._ref_forward(X, want)
+    X, _ = ref.gen_data()
+    want = orc.softmax_ref(X).cuda()  # CPU oracle, float64 accumulation: independent of this GPU's torch kernels
     op = ez.SoftmaxOp(batch, dim, backend="cuda")
     got = torch.empty_like(want)
     op(X, got)
@@ -47,21 +62,21 @@ def test_vector_add_and_reduce_cuda(n):
     A, B, C = ez.VectorAddOp(n).gen_data()
     op = ez.VectorAddOp(n, backend="cuda")
     op(A, B, C)
-    assert torch.equal(C, A + B)
+    assert torch.equal(C.cpu(), orc.vector_add_ref(A, B))  # CPU oracle
     assert check_input_readonly(op, inputs=(A, B), outputs=C)
     # unaligned views take the scalar path
     if n > 8:
         op1 = ez.VectorAddOp(n - 1, backend="cuda")
         C1 = torch.empty(n, device="cuda")[1:]  # 1-D slices are contiguous but start 4 bytes off the 16-byte grid
         op1(A[1:], B[1:], C1)
-        assert torch.equal(C1, A[1:] + B[1:])
+        assert torch.equal(C1.cpu(), orc.vector_add_ref(A[1:], B[1:]))
         red1 = ez.ReduceOp(n - 1, backend="cuda")
         out1 = torch.empty(1, device="cuda")
         red1(A[1:], out1)
-        assert red1.check(out1, A[1:].double().sum().float().reshape(1))
+        assert red1.check(out1.cpu(), orc.reduce_sum_ref(A[1:]))
     red = ez.ReduceOp(n, backend="cuda")
     out = torch.empty(1, device="cuda")
     red(A, out)
-    assert red.check(out, A.double().sum().float().reshape(1)), (out.item(), A.double().sum().item())
+    assert red.check(out.cpu(), orc.reduce_sum_ref(A)), (out.item(), A.double().sum().item())
     assert check_determinism(red, inputs=(A,), outputs=out)
     assert check_input_readonly(red, inputs=(A,), outputs=out)
