@@ -150,8 +150,26 @@ def o_proj_ffn_fp64(attn, residual, Wo, post_norm_w, Wg, Wu, Wd, eps: float = RM
 
 
 # ------------------------------------------------------ the decode layer ----
+def gqa_decode_attention_by_kv_head(q: torch.Tensor, K_cache: torch.Tensor, V_cache: torch.Tensor) -> torch.Tensor:
+    """softmax(q K^T / sqrt(D)) V for one query token with grouped queries, one kv head at a time in fp32 and
+    rounded to bf16 once: the same function as ``F.scaled_dot_product_attention(q[:, :, None], K, V,
+    enable_gqa=True)`` (ezops/ops/qwen3_dense_decode.py:166-170) without materialising K and V once per query head,
+    which at Qwen3-32B, batch 64, 8192 keys would be 2 x 17 GB.  q [B, NH, D], caches [B, NKV, S, D] -> [B, NH, D]."""
+    B, NH, D = q.shape
+    NKV = K_cache.shape[1]
+    G = NH // NKV
+    out = torch.empty(B, NH, D, dtype=q.dtype)
+    scale = 1.0 / (D**0.5)
+    for h in range(NKV):
+        qg = q[:, h * G : (h + 1) * G].float()                      # [B, G, D]
+        scores = torch.einsum("bgd,bsd->bgs", qg, K_cache[:, h].float()) * scale
+        probs = torch.softmax(scores, dim=-1)
+        out[:, h * G : (h + 1) * G] = torch.einsum("bgs,bsd->bgd", probs, V_cache[:, h].float()).to(q.dtype)
+    return out
+
+
 def qwen3_dense_decode_ref(hidden, K_cache, V_cache, Wqkv, Wo, Wgu, Wd, num_heads, num_kv_heads, head_dim,
-                           eps: float = RMS_EPS, sdpa_math: bool = False) -> torch.Tensor:
+                           eps: float = RMS_EPS, sdpa_math: bool = False, lean_attention: bool = False) -> torch.Tensor:
     """ezops/ops/qwen3_dense_decode.py:142-176.  Mutates slot S-1 of the caches.
 
     The reference restricts SDPA to [cuDNN, MATH] (qwen3_dense_decode.py:167).
@@ -160,7 +178,9 @@ def qwen3_dense_decode_ref(hidden, K_cache, V_cache, Wqkv, Wo, Wgu, Wd, num_head
     ``sdpa_math=True`` reproduces the CPU selection literally (this is what the
     golden fixtures were generated through); the default leaves the backend
     free, which on CPU picks the fused kernel with fp32 softmax -- the staging
-    the reference has on a GPU and the one GPU kernels are compared with."""
+    the reference has on a GPU and the one GPU kernels are compared with.
+    ``lean_attention=True`` computes that attention one kv head at a time (see
+    gqa_decode_attention_by_kv_head), for shapes whose expanded K/V would not fit."""
     B = hidden.shape[0]
     q_rows, kv_rows = num_heads * head_dim, num_kv_heads * head_dim
     inter = Wgu.shape[0] // 2
@@ -173,7 +193,9 @@ def qwen3_dense_decode_ref(hidden, K_cache, V_cache, Wqkv, Wo, Wgu, Wd, num_head
     K_cache[:, :, -1, :] = k
     V_cache[:, :, -1, :] = v
 
-    if sdpa_math:
+    if lean_attention:  # large shapes: the same attention without a copy of K and V per query head
+        attn = gqa_decode_attention_by_kv_head(q, K_cache, V_cache)
+    elif sdpa_math:
         from torch.nn.attention import SDPBackend, sdpa_kernel
 
         with sdpa_kernel([SDPBackend.MATH]):

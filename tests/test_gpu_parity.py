@@ -380,6 +380,33 @@ def test_decode_layer_qwen3_32b_small_batch(ez):
     _layer_case(ez, 2, 512, wl.QWEN3_32B, std=0.02)
 
 
+def test_decode_layer_qwen3_32b_batch_64_kv_8192(ez):
+    """The tensor-parallel configuration of the benchmark on one GPU, unsharded: Qwen3-32B (hidden 5120, 64 q / 8 kv
+    heads, intermediate 25600), batch 64, 8192 cached tokens, N(0, 0.02) weights: 0.98 GB of weights and 2.1 GB of KV
+    cache.  The oracle computes the attention one kv head at a time (same function as the reference's SDPA call,
+    tied to it on a small case in tests/test_oracle_golden.py); acceptance is the reference's relative Frobenius
+    bound of 1e-2 (ezops/ops/qwen3_dense_decode.py:64-69)."""
+    from ezops_b200 import workloads as wl
+
+    sh, B, S = wl.QWEN3_32B, 64, 8192
+    hidden, K0, V0, Wqkv, Wo, Wgu, Wd = wl.decode_layer_inputs(sh, B, S)
+    op = ez.Qwen3DenseDecodeOp(B, S, sh.hidden, sh.inter, sh.num_heads, sh.head_dim, backend="cuda", num_kv_heads=sh.num_kv_heads)
+    dargs = dev(hidden, K0, V0, Wqkv, Wo, Wgu, Wd)
+    out = op(*dargs)
+    again = op(*dargs)
+    torch.cuda.synchronize()
+    assert torch.equal(out, again)  # deterministic, idempotent on the updated cache
+    # three untouched slots of the caches and the written one, before the oracle overwrites the CPU copies' last slot
+    for slot in (0, 4095, S - 2):
+        assert torch.equal(dargs[1][:, :, slot].cpu(), K0[:, :, slot]) and torch.equal(dargs[2][:, :, slot].cpu(), V0[:, :, slot])
+    ref = orc.qwen3_dense_decode_ref(hidden, K0, V0, Wqkv, Wo, Wgu, Wd, sh.num_heads, sh.num_kv_heads, sh.head_dim, lean_attention=True)
+    assert op.check(out.cpu(), ref), rel_fro(out, ref)
+    assert rel_fro(out, ref) < 1e-2
+    assert max_abs(out, ref) <= 2e-2 * ref.float().abs().max().item() + 0.0626, max_abs(out, ref)  # one bf16 step at |x| ~ 8..16
+    assert torch.allclose(dargs[1][:, :, -1].cpu().float(), K0[:, :, -1].float(), atol=1e-2, rtol=1e-2)  # K0 now holds the oracle's new k
+    assert torch.allclose(dargs[2][:, :, -1].cpu().float(), V0[:, :, -1].float(), atol=1e-2, rtol=1e-2)
+
+
 def test_decode_layer_constructor_checks(ez):
     with pytest.raises(ValueError, match="divisible"):
         ez.Qwen3DenseDecodeOp(1, 128, num_heads=16, head_dim=128, hidden_size=2048, intermediate_size=6144,

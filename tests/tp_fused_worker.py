@@ -26,10 +26,12 @@ def main() -> int:
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     ok = True
     # batch 1 and 3: gather and push inside the small-batch kernel; batch 16: row kernel + tensor-core kernel
-    for sh, B, S in [(wl.QWEN3_VL_2B, 1, 700), (wl.QWEN3_8B, 3, 1025), (wl.QWEN3_VL_2B, 16, 400)]:
+    # the last case is the benchmark's tensor-parallel configuration (Qwen3-32B shapes, batch 64) at a shorter cache
+    for sh, B, S in [(wl.QWEN3_VL_2B, 1, 700), (wl.QWEN3_8B, 3, 1025), (wl.QWEN3_VL_2B, 16, 400), (wl.QWEN3_32B, 64, 1536)]:
         hidden, K0, V0, Wqkv, Wo, Wgu, Wd = wl.decode_layer_inputs(sh, B, S)
         heads = (sh.num_heads, sh.num_kv_heads, sh.head_dim)
-        ref = orc.qwen3_dense_decode_ref(hidden, K0.clone(), V0.clone(), Wqkv, Wo, Wgu, Wd, *heads) if rank == 0 else None
+        ref = (orc.qwen3_dense_decode_ref(hidden, K0.clone(), V0.clone(), Wqkv, Wo, Wgu, Wd, *heads, lean_attention=B >= 32)
+               if rank == 0 else None)
         args = (B, S, sh.hidden, sh.inter, sh.num_heads, sh.head_dim, sh.num_kv_heads)
         nccl = tpm.TensorParallelDecodeLayer(*args)
         fused = tpm.TensorParallelDecodeLayer(*args, exchange="fused")
