@@ -8,6 +8,7 @@ from .ops import (
     FusedQkNormRopeOp,
     GemvOp,
     Op,
+    PdlGemmOp,
     Qwen3DecodeStackOp,
     Qwen3DenseDecodeOp,
     ReduceOp,
@@ -24,6 +25,7 @@ __all__ = [
     "FusedQkNormRopeOp",
     "GemvOp",
     "Op",
+    "PdlGemmOp",
     "Qwen3DecodeStackOp",
     "Qwen3DenseDecodeOp",
     "ReduceOp",

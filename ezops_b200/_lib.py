@@ -80,6 +80,7 @@ SIGNATURES = {
     "ezb_softmax_f32": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "ezb_reduce_workspace_bytes": (c_size_t, []),
     "ezb_reduce_sum_f32": (c_int, [c_void_p, c_void_p, c_longlong, c_void_p, c_size_t, c_void_p]),
+    "ezb_pdl_gemm_f32": (c_int, [c_void_p] * 5 + [c_int] * 5 + [c_void_p]),
     "ezb_launch_count": (ctypes.c_ulonglong, []),
     "ezb_hbm_stream": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_float, c_int, c_int, c_void_p]),
     "ezb_tp_comm_bytes": (c_size_t, [c_int, c_int]),

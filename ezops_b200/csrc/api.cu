@@ -759,6 +759,16 @@ int ezb_reduce_sum_f32(const float* A, float* Out, long long n, void* workspace,
     return EZB_OK;
 }
 
+int ezb_pdl_gemm_f32(const float* x, const float* W1, const float* W2, float* y, float* z, int M, int K, int N, int P, int use_pdl,
+                     ezb_stream_t stream) {
+    EZB_REQUIRE(x && W1 && W2 && y && z, "null pointer");
+    EZB_REQUIRE(M >= 1 && K >= 1 && N >= 1 && P >= 1, "sizes must be positive");
+    EZB_REQUIRE_SHAPE(K % 4 == 0 && N % 4 == 0 && P % 4 == 0, "K, N and P must be divisible by 4 (16-byte row segments)");
+    EZB_REQUIRE(aligned16(x) && aligned16(W1) && aligned16(W2) && aligned16(y) && aligned16(z), "pointers must be 16-byte aligned");
+    EZB_CUDA_TRY(launch_pdl_gemm_f32(x, W1, W2, y, z, M, K, N, P, use_pdl != 0, static_cast<cudaStream_t>(stream)));
+    return EZB_OK;
+}
+
 unsigned long long ezb_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int ezb_hbm_stream(int op, const void* b, const void* c, void* a, long long n_vec4, float scalar, int block_size,

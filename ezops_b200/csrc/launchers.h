@@ -166,6 +166,9 @@ cudaError_t launch_hbm_stream(int op, const void* b, const void* c, void* a, lon
 // The reference's teaching operators (tutorial_ops.cu).
 cudaError_t launch_vector_add_f32(const float* A, const float* B, float* C, long long n, cudaStream_t stream);
 cudaError_t launch_softmax_f32(const float* X, float* Out, int rows, int dim, cudaStream_t stream);
+// Two chained fp32 GEMMs y = x . W1, z = y . W2 (pdl_gemm.cu); use_pdl: the second may start while the first drains.
+cudaError_t launch_pdl_gemm_f32(const float* x, const float* W1, const float* W2, float* y, float* z, int M, int K, int N, int P,
+                                bool use_pdl, cudaStream_t stream);
 size_t reduce_workspace_bytes();  // zero-filled once by the caller
 cudaError_t launch_reduce_sum_f32(const float* A, float* Out, long long n, void* workspace, cudaStream_t stream);
 

@@ -420,3 +420,39 @@ class ReduceSm100Kernel(BaseKernel):
             self._ws = _zeros_bytes(self._lib.ezb_reduce_workspace_bytes(), A.device)
         _lib.check(self._lib.ezb_reduce_sum_f32(A.data_ptr(), Out.data_ptr(), self.n, self._ws.data_ptr(), self._ws.numel(), _stream()))
 
+
+
+class _PdlGemmSm100Base(BaseKernel):
+    """y = x @ W1, z = y @ W2 on fp32 tensors (constructor contract: ezops/ops/pdl_gemm.py:39-47; call contract
+    ``(x, W1, W2, y, z) -> None`` as ezops/kernels/pdl_gemm/pdl_gemm_cu.py:34-42)."""
+
+    use_pdl = 0
+
+    def __init__(self, M: int, K: int, N: int, P: int):
+        if min(M, K, N, P) < 1:
+            raise ValueError("M, K, N and P must be positive")
+        if K % 4 or N % 4 or P % 4:
+            raise ValueError(f"K ({K}), N ({N}) and P ({P}) must be divisible by 4")
+        self.M, self.K, self.N, self.P, self._lib = M, K, N, P, _lib.load()
+
+    def __call__(self, x, W1, W2, y, z) -> None:
+        M, K, N, P = self.M, self.K, self.N, self.P
+        for name, t, shape in (("x", x, (M, K)), ("W1", W1, (K, N)), ("W2", W2, (N, P)), ("y", y, (M, N)), ("z", z, (M, P))):
+            _require_f32(t, name, shape)
+        _lib.check(self._lib.ezb_pdl_gemm_f32(x.data_ptr(), W1.data_ptr(), W2.data_ptr(), y.data_ptr(), z.data_ptr(),
+                                              M, K, N, P, self.use_pdl, _stream()))
+
+
+@register_kernel("pdl_gemm", "cuda")
+class PdlGemmSm100Kernel(_PdlGemmSm100Base):
+    """Two ordinary launches: the second GEMM starts when the first has finished."""
+
+    use_pdl = 0
+
+
+@register_kernel("pdl_gemm", "cuda_pdl")
+class PdlGemmPdlSm100Kernel(_PdlGemmSm100Base):
+    """The second GEMM is launched with programmatic stream serialization: its CTAs fetch their W2 tiles while the
+    first GEMM drains and read y only after ``griddepcontrol.wait``."""
+
+    use_pdl = 1

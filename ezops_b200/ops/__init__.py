@@ -6,7 +6,7 @@ from .gemv import GemvOp
 from .qwen3_decode_stack import Qwen3DecodeStackOp
 from .qwen3_dense_decode import Qwen3DenseDecodeOp
 from .rmsnorm import RmsNormOp
-from .tutorial import ReduceOp, SoftmaxOp, VectorAddOp
+from .tutorial import PdlGemmOp, ReduceOp, SoftmaxOp, VectorAddOp
 from .utils.roofline import RooflineResult
 
 __all__ = [
@@ -15,6 +15,7 @@ __all__ = [
     "FusedQkNormRopeOp",
     "GemvOp",
     "Op",
+    "PdlGemmOp",
     "Qwen3DecodeStackOp",
     "Qwen3DenseDecodeOp",
     "ReduceOp",

@@ -260,6 +260,15 @@ int ezb_softmax_f32(const float* X, float* Out, int rows, int dim, ezb_stream_t 
 size_t ezb_reduce_workspace_bytes(void);
 int ezb_reduce_sum_f32(const float* A, float* Out, long long n, void* workspace, size_t workspace_bytes, ezb_stream_t stream);
 
+/* Two chained fp32 GEMMs, y[M,N] = x[M,K] . W1[K,N] and z[M,P] = y . W2[N,P] (row-major, TF32 tensor-core
+ * arithmetic with fp32 accumulation), the reference's demonstration of programmatic dependent launch.  Replaces
+ * pdl_gemm_baseline_cu (use_pdl = 0; ezops/kernels/pdl_gemm/pdl_gemm_cu.cu:163-196) and pdl_gemm_pdl_cu (use_pdl = 1;
+ * :202-248) behind PdlGemmOp.forward (ezops/ops/pdl_gemm.py:49-57).  With use_pdl the second GEMM is launched with
+ * the programmatic-serialization attribute: its CTAs request their W2 tiles while the first GEMM drains and read y
+ * only after it has finished.  Both settings give the same bits.  K, N, P divisible by 4. */
+int ezb_pdl_gemm_f32(const float* x, const float* W1, const float* W2, float* y, float* z, int M, int K, int N, int P, int use_pdl,
+                     ezb_stream_t stream);
+
 /* Kernel launches issued by the library in this process so far (every kernel of
  * the library goes through one launch helper).  A diagnostic with no
  * counterpart in the reference: benchmarks report launches per step from it

@@ -332,3 +332,11 @@ def softmax_ref(X: torch.Tensor) -> torch.Tensor:
 def reduce_sum_ref(A: torch.Tensor) -> torch.Tensor:
     """Sum of all elements (ezops/ops/reduce.py:32-33), accumulated in float64."""
     return A.cpu().double().sum().float().reshape(1)
+
+
+def pdl_gemm_ref(x: torch.Tensor, W1: torch.Tensor, W2: torch.Tensor):
+    """y = x @ W1, z = y @ W2 (ezops/ops/pdl_gemm.py:69-76), accumulated in float64 and rounded to fp32 once per
+    GEMM: (y, z)."""
+    y = (x.cpu().double() @ W1.cpu().double()).float()
+    z = (y.double() @ W2.cpu().double()).float()
+    return y, z

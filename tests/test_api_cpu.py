@@ -22,7 +22,7 @@ ROOT = Path(__file__).resolve().parent.parent
 def test_registry_lists_the_six_ops_with_a_cuda_backend():
     # the reference's six operators of the decode path, plus the multi-layer stack built on top of them
     assert list_ops() == sorted(["attn_decode", "fused_o_proj_ffn", "fused_qk_norm_rope", "gemv", "qwen3_decode_stack",
-                                 "qwen3_dense_decode", "rmsnorm", "reduce", "softmax", "vector_add"])
+                                 "qwen3_dense_decode", "rmsnorm", "reduce", "softmax", "vector_add", "pdl_gemm"])
     for op in list_ops():
         assert "cuda" in list_backends(op)
         cls = get_kernel(op, "cuda")

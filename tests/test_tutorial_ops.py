@@ -22,8 +22,16 @@ def test_reference_forwards_on_cpu():
     op = ez.ReduceOp(5000)
     op(V, S)
     assert op.check(S, V.double().sum().float().reshape(1)) and op._atol == pytest.approx(5e-4)
-    for name in ("vector_add", "softmax", "reduce"):
+    for name in ("vector_add", "softmax", "reduce", "pdl_gemm"):
         assert "cuda" in ez.list_backends(name)
+    assert "cuda_pdl" in ez.list_backends("pdl_gemm")
+    x, W1, W2, y, z = ez.PdlGemmOp(8, 12, 16, 4).gen_data(device="cpu")
+    op = ez.PdlGemmOp(8, 12, 16, 4)
+    op(x, W1, W2, y, z)
+    y64, z64 = orc.pdl_gemm_ref(x, W1, W2)
+    assert op.check(y, y64) and op.check(z, z64)
+    with pytest.raises(ValueError, match="divisible by 4"):
+        ez.PdlGemmOp(8, 12, 18, 4, backend="cuda")
 
 
 def test_cpu_oracle_of_the_teaching_ops_agrees_with_the_op_references():
@@ -80,3 +88,44 @@ def test_vector_add_and_reduce_cuda(n):
     assert red.check(out.cpu(), orc.reduce_sum_ref(A)), (out.item(), A.double().sum().item())
     assert check_determinism(red, inputs=(A,), outputs=out)
     assert check_input_readonly(red, inputs=(A,), outputs=out)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,K,N,P", [(64, 128, 128, 128), (64, 512, 512, 512), (128, 1024, 1024, 1024), (256, 2048, 2048, 2048),
+                                     (1, 4, 4, 4), (70, 100, 36, 52), (129, 2052, 68, 200)])
+def test_pdl_gemm_cuda(M, K, N, P):
+    """The reference's four benchmark workloads (benchmarks/bench_pdl_gemm.py:36-42) and ragged shapes, against the
+    float64 CPU oracle with the operator's own acceptance (relative Frobenius error < 1e-2: TF32 inputs); the
+    launch with and without programmatic dependent launch must give the same bits."""
+    torch.manual_seed(42)
+    x, W1, W2, y, z = ez.PdlGemmOp(M, K, N, P).gen_data()
+    y64, z64 = orc.pdl_gemm_ref(x, W1, W2)
+    plain = ez.PdlGemmOp(M, K, N, P, backend="cuda")
+    plain(x, W1, W2, y, z)
+    assert plain.check(y.cpu(), y64) and plain.check(z.cpu(), z64)
+    rel = ((z.cpu().double() - z64.double()).norm() / z64.double().norm()).item()
+    assert rel < 2e-3, rel  # TF32 rounding of two chained products
+    pdl = ez.PdlGemmOp(M, K, N, P, backend="cuda_pdl")
+    y2, z2 = torch.full_like(y, float("nan")), torch.full_like(z, float("nan"))
+    for _ in range(3):
+        pdl(x, W1, W2, y2, z2)
+    assert torch.equal(y2, y) and torch.equal(z2, z)
+    assert check_determinism(pdl, inputs=(x, W1, W2), outputs=(y2, z2))
+    assert check_input_readonly(pdl, inputs=(x, W1, W2), outputs=(y2, z2))
+
+
+@pytest.mark.gpu
+def test_pdl_gemm_under_a_cuda_graph():
+    torch.manual_seed(1)
+    op = ez.PdlGemmOp(64, 512, 512, 512, backend="cuda_pdl")
+    x, W1, W2, y, z = op.gen_data()
+    op(x, W1, W2, y, z)
+    want = z.clone()
+    g = torch.cuda.CUDAGraph()
+    z.zero_()
+    with torch.cuda.graph(g):
+        op(x, W1, W2, y, z)
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(z, want)
