@@ -10,7 +10,15 @@ job: algorithmic bytes of one layer step (every weight and every valid KV row
 once; the same total at every N, so scaling is "strong") divided by the device
 time of a step, timed with CUDA events over exactly K steps replayed from a CUDA
 graph, max over ranks.  Steps rotate over four independent sets of layer weights
-and KV caches (1.6 GB), so no step finds its inputs in L2.
+and KV caches (1.6 GB), so no step finds its inputs in L2.  The timed steps are
+enqueued directly behind ``--lead-in`` untimed ones (no host synchronisation in
+between), so with several ranks the processes' launch skew is absorbed before the
+first timed step and the clock samples describe the load the steps run under.
+At one GPU and batch 1 a step is ONE kernel launch (the whole layer as a
+persistent kernel); ``roofline`` then describes that kernel and
+``weight_streaming_leg`` the stand-alone GEMV kernel the other paths are built on.
+The process returns normally (exit hooks run); with several ranks the process
+group is destroyed under a guard timer.
 
 Further legs, all outside the timed region of ``value``:
   e2e          the same layer through the operator API with the step's input in
@@ -66,6 +74,8 @@ def parse_args():
     ap.add_argument("--stack", action="store_true", help="same as --calls stack")
     ap.add_argument("--roofline-only", action="store_true",
                     help="run only the roofline leg (a few launches of the dominant kernel): the command an ncu capture wraps")
+    ap.add_argument("--lead-in", type=int, default=200,
+                    help="untimed steps issued directly in front of the timed ones (same stream, no host sync in between)")
     ap.add_argument("--no-cross-call-pdl", action="store_true",
                     help="order the first kernel of every layer call fully after the previous call")
     return ap.parse_args()
@@ -468,7 +478,7 @@ def main():
     # the ranks are then coupled on the device (by the exchange inside the steps) before t0, so host launch skew
     # between the processes is not charged to the first timed step; the clock sampler sees the same load before
     # and during the timed region (a 20-step region alone is shorter than one NVML query).
-    lead_in = max(unroll, (max(200, warmup) + unroll - 1) // unroll * unroll)
+    lead_in = max(unroll, (max(args.lead_in, 1) + unroll - 1) // unroll * unroll)
     sync_all()
     with ClockSampler(local_rank) as clocks:
         issue_steps(lead_in)

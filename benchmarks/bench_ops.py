@@ -9,7 +9,10 @@ achieved GB/s on the algorithmic bytes, the fraction of 8 TB/s and of the
 measured copy peak, and the SOL score.  ``--cpu`` adds the same torch reference
 timed on the host cores.
 
-    python benchmarks/bench_ops.py [-k gemv,rmsnorm,rope,attn,ffn,layer] [--cpu] [--json out.json]
+    python benchmarks/bench_ops.py [-k gemv,rmsnorm,rope,attn,ffn,layer,stack,pdl_gemm] [--cpu] [--json out.json]
+
+The reference's one-script-per-operator command line (``python benchmarks/bench_gemv.py -h`` / ``-k <backends>``) is
+kept by the small ``benchmarks/bench_<op>.py`` files, which run one workload group of this module.
 """
 
 from __future__ import annotations
@@ -194,12 +197,39 @@ def run_stack(cpu, peak, num_layers=36, batches=(1, 8)):
     return rows
 
 
-RUNNERS = {"stack": run_stack, "gemv": run_gemv, "rmsnorm": run_rmsnorm, "rope": run_rope, "attn": run_attn, "ffn": run_ffn, "layer": run_layer}
+def run_pdl_gemm(cpu, peak):
+    """The reference's four chained-GEMM workloads (benchmarks/bench_pdl_gemm.py:36-42): torch, two ordinary launches,
+    and the second launch overlapped with the first (programmatic dependent launch).  The interesting number is the
+    last column against the one before it."""
+    rows = []
+    for M, K, N, P, label in ((64, 128, 128, 128, "tiny-mlp"), (64, 512, 512, 512, "small-mlp"), (128, 1024, 1024, 1024, "medium-mlp"),
+                              (256, 2048, 2048, 2048, "large-mlp")):
+        torch.manual_seed(42)
+        ref = ez.PdlGemmOp(M, K, N, P, backend="ref")
+        d = ref.gen_data()
+        ref(*d)
+        want = d[4].clone()
+        us = {}
+        ok = True
+        for backend in ("ref", "cuda", "cuda_pdl"):
+            op = ez.PdlGemmOp(M, K, N, P, backend=backend)
+            d[4].zero_()
+            op(*d)
+            ok = ok and op.check(d[4], want)
+            us[backend] = bench_kernel(op, args=d, n_warmup=30, n_repeat=200, n_trials=5) * 1e3
+        nbytes = 4 * (M * K + K * N + N * P + 2 * M * N + M * P)
+        r = row(f"pdl_gemm {label} {M}x{K}x{N}x{P}: no PDL {us['cuda']:.2f} us, PDL", us["cuda_pdl"], us["ref"], nbytes, ok, None, peak)
+        r["no_pdl_us"] = us["cuda"]
+        rows.append(r)
+    return rows
+
+
+RUNNERS = {"pdl_gemm": run_pdl_gemm, "stack": run_stack, "gemv": run_gemv, "rmsnorm": run_rmsnorm, "rope": run_rope, "attn": run_attn, "ffn": run_ffn, "layer": run_layer}
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("-k", "--ops", default=",".join(k for k in RUNNERS if k != "stack"))
+    ap.add_argument("-k", "--ops", default=",".join(k for k in RUNNERS if k not in ("stack", "pdl_gemm")))
     ap.add_argument("--cpu", action="store_true", help="also time the torch reference on the host cores")
     ap.add_argument("--json", default=None)
     ap.add_argument("--profile", default=None, help="GPU profile under assets/ for the SOL score (default: detected)")

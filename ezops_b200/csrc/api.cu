@@ -105,13 +105,14 @@ static const int kTuningDefaults[EZB_TUNE_COUNT] = {
     2,    // EZB_TUNE_MEGA_INFLIGHT (two of the three stages of the ring outstanding: 77.7 us against 78.3 with all three)
     1,    // EZB_TUNE_MEGA_GATE
     5000, // EZB_TUNE_TP_WAIT_LIMIT_MS
+    0,    // EZB_TUNE_TP_STRONG_STORES
 };
 static const char* kTuningEnv[EZB_TUNE_COUNT] = {
     "EZB_TUNE_PDL",          "EZB_TUNE_GEMV_SMEM_KB",   "EZB_TUNE_GEMV_PREFETCH", "EZB_TUNE_GEMV_CTAS_PER_SM",
     "EZB_TUNE_ATTN_MIN_CHUNK", "EZB_TUNE_ATTN_WAVES", "EZB_TUNE_GEMV_KC", "EZB_TUNE_GEMV_ROWS8", "EZB_TUNE_PDL_ACROSS_CALLS", "EZB_TUNE_L2_PREFETCH", "EZB_TUNE_L2_PREFETCH_KB", "EZB_TUNE_GEMV_WINDOW", "EZB_TUNE_L2_PREFETCH_ATTN_KB", "EZB_TUNE_TC",
     "EZB_TUNE_ATTN_WAVES_UNIFORM", "EZB_TUNE_TP_POLL_ALL", "EZB_TUNE_TP_PULL", "EZB_TUNE_MEGA", "EZB_TUNE_MEGA_L2_STAGES",
     "EZB_TUNE_WAIT_LIMIT_MS", "EZB_TUNE_MEGA_STAGES", "EZB_TUNE_MEGA_INFLIGHT", "EZB_TUNE_MEGA_GATE",
-    "EZB_TUNE_TP_WAIT_LIMIT_MS",
+    "EZB_TUNE_TP_WAIT_LIMIT_MS", "EZB_TUNE_TP_STRONG_STORES",
 };
 
 static void tuning_init() {
@@ -843,7 +844,7 @@ static int make_tp_link(TpLink& base, void* const* comm_bases_host, int world, i
     long long wait_ms = tuning(EZB_TUNE_TP_WAIT_LIMIT_MS);
     if (wait_ms < 1) wait_ms = 1;
     base = {world, rank, {}, {}, (long long)B * H, -1, -1, -1, poll_mode == 1 || (poll_mode == 0 && world > 2) ? 1 : 0,
-            pull_mode == 1 ? 1 : 0, wait_ms * 2000000LL};
+            pull_mode == 1 ? 1 : 0, wait_ms * 2000000LL, tuning(EZB_TUNE_TP_STRONG_STORES) ? 1 : 0};
     for (int r = 0; r < world; ++r) {
         base.ctrl_peer[r] = static_cast<unsigned int*>(comm_bases_host[r]);
         base.inbox_peer[r] = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(comm_bases_host[r]) + kTpCtrlBytes);

@@ -58,9 +58,10 @@ static constexpr long long kWaitLimitCycles = 2000000000LL;
 // Two directions.  Push (the default): the producer stores into slot `rank` on every rank and
 // consumers poll their own memory, so a value crosses NVLink once per peer however many CTAs
 // read it.  Pull (EZB_TUNE_TP_PULL): the producer writes slot `rank` of its OWN buffer only and
-// consumers poll slot w of rank w's buffer with peer loads.  Measured on two GPUs at batch 32-64
-// pull was slower than push, and both slower than NCCL there (see the tensor-parallel notes of
-// the design document); at batch <= 8 push is the fast one.
+// consumers poll slot w of rank w's buffer with peer loads.  Measured on two GPUs (us per layer,
+// Qwen3-8B batch 32 KV 4096 | Qwen3-32B batch 64 KV 8192): NCCL all-reduce between the parts 162 | 345,
+// push 168 | 408, pull 200 | 433 - with the stream-K split only the 32-40 CTAs that finish a tile store,
+// 32-64 KB each, which takes them 16-22 us; at batch <= 8 (every CTA stores a few values) push is the fast one.
 // ---------------------------------------------------------------------------
 struct TpLink {
     int world;  // 0: no fused exchange
@@ -74,6 +75,7 @@ struct TpLink {
     int poll_all;      // 1: the gathering prologue polls all ranks together, 4 elements per thread and step
     int pull;          // 1: a producer writes only its own buffer and consumers read every rank's buffer over NVLink
     long long wait_cycles;  // budget of one wait for the peers' partials (from EZB_TUNE_TP_WAIT_LIMIT_MS)
+    int strong_stores;      // 1: cells are published with st.relaxed.sys (see tp_push)
 };
 // A recorded fault poisons the exchange: kernels that take part in it read the status word when they start and,
 // if it is set, neither gather, push nor advance an epoch, so that a rank that gave up on a wait never hands its
@@ -92,23 +94,39 @@ __device__ __forceinline__ unsigned long long* tp_slot(const TpLink& l, int on_r
 __device__ __forceinline__ unsigned int tp_next_epoch(const TpLink& l, int inbox) {
     return l.ctrl_peer[l.rank][kTpEpoch + inbox] + 1u;
 }
-// The store is a plain (weak) 64-bit store: value and tag travel in one naturally aligned word, so
-// nothing has to be ordered around it, and a weak store is posted - a thread can have many in flight.
-// (Measured: with st.relaxed.sys a thread's stores to a peer went out one NVLink round trip at a time,
-// 64 of them cost the tensor-core epilogue 30 us.)  The consumer polls with strong system-scope loads.
+// Publishing a cell.  Default: a plain (weak) 64-bit store.  Value and tag travel in one naturally aligned word and the
+// consumer polls with strong system-scope loads.  This is a HARDWARE ASSUMPTION, not a guarantee of the PTX memory
+// model: a weak store racing with a strong load is formally a data race, and the model promises neither that the 8
+// bytes land together nor when they become visible.  On the GPUs this library targets an aligned 8-byte store is
+// performed as one transaction (what the tests on 2, 4 and 8 GPUs exercise), and a weak store is posted - a thread can
+// have many in flight - whereas with st.relaxed.sys a thread's stores to a peer went out one NVLink round trip at a
+// time (64 of them cost the tensor-core epilogue 30 us).  `strong_stores` (EZB_TUNE_TP_STRONG_STORES) selects the
+// conforming form, st.relaxed.sys.u64 per cell, for platforms where the assumption is in doubt; both forms are tested.
+// The 16-byte form below is two independent cells whose halves may land separately; the per-cell tag check of the
+// consumer tolerates that by construction.
+__device__ __forceinline__ void tp_store_cell(unsigned long long* dst, unsigned long long cell, int strong) {
+    if (strong) asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst), "l"(cell) : "memory");
+    else asm volatile("st.weak.global.u64 [%0], %1;" ::"l"(dst), "l"(cell) : "memory");
+}
 __device__ __forceinline__ void tp_push(const TpLink& l, long long elem, float v, unsigned int epoch) {
     const unsigned long long cell = ((unsigned long long)epoch << 32) | (unsigned long long)__float_as_uint(v);
     for (int w = 0; w < l.world; ++w)
-        if (!l.pull || w == l.rank)
-            asm volatile("st.weak.global.u64 [%0], %1;" ::"l"(tp_slot(l, w, l.push_inbox, l.rank) + elem), "l"(cell) : "memory");
+        if (!l.pull || w == l.rank) tp_store_cell(tp_slot(l, w, l.push_inbox, l.rank) + elem, cell, l.strong_stores);
 }
 // Two neighbouring cells (elem even) in one 16-byte store; each 64-bit half is a cell of its own.
 __device__ __forceinline__ void tp_push2(const TpLink& l, long long elem, float v0, float v1, unsigned int epoch) {
     const unsigned long long c0 = ((unsigned long long)epoch << 32) | (unsigned long long)__float_as_uint(v0);
     const unsigned long long c1 = ((unsigned long long)epoch << 32) | (unsigned long long)__float_as_uint(v1);
     for (int w = 0; w < l.world; ++w)
-        if (!l.pull || w == l.rank)
-            asm volatile("st.weak.global.v2.u64 [%0], {%1, %2};" ::"l"(tp_slot(l, w, l.push_inbox, l.rank) + elem), "l"(c0), "l"(c1) : "memory");
+        if (!l.pull || w == l.rank) {
+            unsigned long long* dst = tp_slot(l, w, l.push_inbox, l.rank) + elem;
+            if (l.strong_stores) {
+                tp_store_cell(dst, c0, 1);
+                tp_store_cell(dst + 1, c1, 1);
+            } else {
+                asm volatile("st.weak.global.v2.u64 [%0], {%1, %2};" ::"l"(dst), "l"(c0), "l"(c1) : "memory");
+            }
+        }
 }
 // Called by exactly one thread of the grid, anywhere in the kernel.
 __device__ __forceinline__ void tp_bump(const TpLink& l) { l.ctrl_peer[l.rank][kTpEpoch + l.bump_inbox] += 1u; }

@@ -498,9 +498,9 @@ def test_tp_parts_sum_to_the_layer(ez, tp, batch):
         assert torch.equal(caches[r][0][:, :, :-1].cpu(), K0[:, r * n:(r + 1) * n, :-1])
 
 
-@pytest.mark.parametrize("poll_all,pull", [(0, 0), (1, 0), (0, 1)])
+@pytest.mark.parametrize("poll_all,pull,strong", [(0, 0, 0), (1, 0, 0), (0, 1, 0), (0, 0, 1)])
 @pytest.mark.parametrize("batch", [1, 4, 8, 16, 40])
-def test_tp_fused_exchange_world_one_matches_the_layer(ez, batch, poll_all, pull):
+def test_tp_fused_exchange_world_one_matches_the_layer(ez, batch, poll_all, pull, strong):
     """The fused exchange with one rank pushes into its own inbox: same bits as the
     single-GPU layer, on every one of several calls in a row (the epochs advance)."""
     from ezops_b200 import _lib
@@ -517,13 +517,14 @@ def test_tp_fused_exchange_world_one_matches_the_layer(ez, batch, poll_all, pull
         _lib.set_tuning(mega=1)
     lay = tpm.TensorParallelDecodeLayer(batch, S, sh.hidden, sh.inter, sh.num_heads, sh.head_dim, sh.num_kv_heads, exchange="fused")
     try:
-        _lib.set_tuning(tp_poll_all=1 if poll_all else 2, tp_pull=1 if pull else 0)  # every form of the exchange
+        # every form of the exchange, the memory-model-conforming stores (st.relaxed.sys) included
+        _lib.set_tuning(tp_poll_all=1 if poll_all else 2, tp_pull=1 if pull else 0, tp_strong_stores=strong)
         for _ in range(3):
             got = lay(*dev(*data))
             assert torch.equal(got, want)
         assert _lib.device_status() == 0
     finally:
-        _lib.set_tuning(tp_poll_all=0, tp_pull=0)
+        _lib.set_tuning(tp_poll_all=0, tp_pull=0, tp_strong_stores=0)
         torch.cuda.synchronize()
         lay.close()
 

@@ -84,3 +84,22 @@ def test_every_op_class_resolves_from_its_snake_case_name():
     nc = _load("ncu_profile")
     for op in ez.list_ops():
         assert hasattr(ez, nc.op_name_to_class(op)), op
+
+
+def test_per_operator_benchmark_scripts_keep_the_reference_command_line():
+    """``python benchmarks/bench_<op>.py -h`` lists the backends and exits; an unknown backend is refused with the
+    list (ezops benchmarks/bench_gemv.py:177-212).  Neither touches a GPU."""
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    bench_dir = Path(__file__).resolve().parent.parent / "benchmarks"
+    for script, expect in (("bench_gemv.py", "cuda"), ("bench_rmsnorm.py", "cuda"), ("bench_fused_qk_norm_rope.py", "cuda"),
+                           ("bench_attn_decode.py", "cuda"), ("bench_fused_o_proj_ffn.py", "cuda"),
+                           ("bench_qwen3_dense_decode.py", "cuda"), ("bench_pdl_gemm.py", "cuda, cuda_pdl")):
+        res = subprocess.run([sys.executable, str(bench_dir / script), "-h"], capture_output=True, text=True, timeout=120, cwd=str(bench_dir))
+        assert res.returncode == 0, res.stderr[-500:]
+        assert res.stdout.strip() == f"Available backends: {expect}", res.stdout
+    res = subprocess.run([sys.executable, str(bench_dir / "bench_gemv.py"), "-k", "triton"], capture_output=True, text=True, timeout=120,
+                         cwd=str(bench_dir))
+    assert "Unknown backends: triton" in res.stdout and "Available: cuda" in res.stdout
