@@ -251,7 +251,7 @@ def ncu_traffic(kernel: str, rows: int, cols: int, batch: int):
     for e in same:
         if e["rows"] == rows:
             return e["dram_read_bytes"] + e["dram_write_bytes"], f"ncu capture ({e['summary']})"
-    if same:
+    if same and kernel != "decode_layer_b1_kernel":  # the whole-layer kernel's traffic is not proportional to one size
         e = same[0]
         scaled = (e["dram_read_bytes"] + e["dram_write_bytes"]) * rows / e["rows"]
         return int(scaled), f"scaled by rows from the ncu capture at {e['rows']} rows ({e['summary']})"
