@@ -38,7 +38,7 @@ TUNE = {
     "l2_prefetch_attn_kb": 12,
     "tc": 13, "attn_waves_uniform": 14, "tp_poll_all": 15, "tp_pull": 16,
     "mega": 17, "mega_l2_stages": 18, "wait_limit_ms": 19, "mega_stages": 20, "mega_inflight": 21, "mega_gate": 22,
-    "tp_wait_limit_ms": 23, "tp_strong_stores": 24,
+    "tp_wait_limit_ms": 23, "tp_strong_stores": 24, "stream_evict_first": 25,
 }
 
 # name -> (restype, argtypes); every symbol include/ezb200.h declares

@@ -106,13 +106,14 @@ static const int kTuningDefaults[EZB_TUNE_COUNT] = {
     1,    // EZB_TUNE_MEGA_GATE
     5000, // EZB_TUNE_TP_WAIT_LIMIT_MS
     0,    // EZB_TUNE_TP_STRONG_STORES
+    1,    // EZB_TUNE_STREAM_EVICT_FIRST
 };
 static const char* kTuningEnv[EZB_TUNE_COUNT] = {
     "EZB_TUNE_PDL",          "EZB_TUNE_GEMV_SMEM_KB",   "EZB_TUNE_GEMV_PREFETCH", "EZB_TUNE_GEMV_CTAS_PER_SM",
     "EZB_TUNE_ATTN_MIN_CHUNK", "EZB_TUNE_ATTN_WAVES", "EZB_TUNE_GEMV_KC", "EZB_TUNE_GEMV_ROWS8", "EZB_TUNE_PDL_ACROSS_CALLS", "EZB_TUNE_L2_PREFETCH", "EZB_TUNE_L2_PREFETCH_KB", "EZB_TUNE_GEMV_WINDOW", "EZB_TUNE_L2_PREFETCH_ATTN_KB", "EZB_TUNE_TC",
     "EZB_TUNE_ATTN_WAVES_UNIFORM", "EZB_TUNE_TP_POLL_ALL", "EZB_TUNE_TP_PULL", "EZB_TUNE_MEGA", "EZB_TUNE_MEGA_L2_STAGES",
     "EZB_TUNE_WAIT_LIMIT_MS", "EZB_TUNE_MEGA_STAGES", "EZB_TUNE_MEGA_INFLIGHT", "EZB_TUNE_MEGA_GATE",
-    "EZB_TUNE_TP_WAIT_LIMIT_MS", "EZB_TUNE_TP_STRONG_STORES",
+    "EZB_TUNE_TP_WAIT_LIMIT_MS", "EZB_TUNE_TP_STRONG_STORES", "EZB_TUNE_STREAM_EVICT_FIRST",
 };
 
 static void tuning_init() {
@@ -581,20 +582,27 @@ size_t ezb_qwen3_decode_layer_workspace_bytes(int B, int S, int H, int I, int NH
     return carve_layer_ws(nullptr, B, S, H, I, NH, NKV, D).total;
 }
 
+static MegaArgs mega_args(const bf16* hid, bf16* Kc, bf16* Vc, const bf16* Wqkv, const bf16* Wo, const bf16* wgu, const bf16* Wd,
+                          bf16* out, const LayerWorkspace& w, int S, int H, int I, int NH, int NKV, int D, float eps,
+                          const LayerExtras& ex) {
+    MegaArgs m;
+    m.hidden = hid, m.out = out, m.Kc = Kc, m.Vc = Vc;
+    m.Wqkv = Wqkv, m.Wo = Wo, m.Wgu = wgu, m.Wd = Wd;
+    m.input_norm_w = ex.input_norm_w, m.post_norm_w = ex.post_norm_w, m.q_norm_w = ex.q_norm_w, m.k_norm_w = ex.k_norm_w;
+    m.rope_cos = ex.rope_cos, m.rope_sin = ex.rope_sin;
+    m.qkv = w.qkv, m.attn_out = w.attn_out, m.x2 = w.x2, m.h = w.h;
+    m.mega_workspace = w.mega;
+    m.S = S, m.H = H, m.I = I, m.NH = NH, m.NKV = NKV, m.D = D, m.eps = eps;
+    return m;
+}
+
 // One layer's five (seven with the tensor-core path) launches.  The caller has opened the chain.
 static int run_layer(const bf16* hid, bf16* Kc, bf16* Vc, const bf16* Wqkv, const bf16* Wo, const bf16* wgu, const bf16* Wd,
                      bf16* out, const LayerWorkspace& w, int B, int S, int H, int I, int NH, int NKV, int D, float eps,
                      const LayerExtras& ex, cudaStream_t stream) {
     if (B == 1 && !ex.seq_lens && !ex.page_table && w.mega) {
         // batch 1 on contiguous caches: the whole layer as one persistent kernel
-        MegaArgs m;
-        m.hidden = hid, m.out = out, m.Kc = Kc, m.Vc = Vc;
-        m.Wqkv = Wqkv, m.Wo = Wo, m.Wgu = wgu, m.Wd = Wd;
-        m.input_norm_w = ex.input_norm_w, m.post_norm_w = ex.post_norm_w, m.q_norm_w = ex.q_norm_w, m.k_norm_w = ex.k_norm_w;
-        m.rope_cos = ex.rope_cos, m.rope_sin = ex.rope_sin;
-        m.qkv = w.qkv, m.attn_out = w.attn_out, m.x2 = w.x2, m.h = w.h;
-        m.mega_workspace = w.mega;
-        m.S = S, m.H = H, m.I = I, m.NH = NH, m.NKV = NKV, m.D = D, m.eps = eps;
+        const MegaArgs m = mega_args(hid, Kc, Vc, Wqkv, Wo, wgu, Wd, out, w, S, H, I, NH, NKV, D, eps, ex);
         if (decode_mega_supported(m)) {
             EZB_CUDA_TRY(launch_decode_mega(m, stream));
             return EZB_OK;
@@ -979,6 +987,18 @@ int ezb_qwen3_decode_layer_tp_fused(const void* hidden, void* K_cache, void* V_c
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     chain_begin();
+    if (B == 1 && w.mega) {
+        // batch 1: the whole rank-local layer and both exchanges in one persistent kernel
+        MegaArgs m = mega_args(static_cast<const bf16*>(hidden), static_cast<bf16*>(K_cache), static_cast<bf16*>(V_cache),
+                               static_cast<const bf16*>(Wqkv_local), static_cast<const bf16*>(Wo_local),
+                               static_cast<const bf16*>(Wgu_local), static_cast<const bf16*>(Wd_local), static_cast<bf16*>(out), w,
+                               S, H, I_local, NH_local, NKV_local, D, eps, kPlainLayer);
+        m.link = base;
+        if (decode_mega_supported(m)) {
+            EZB_CUDA_TRY(launch_decode_mega(m, st));
+            return EZB_OK;
+        }
+    }
     if (int rc = run_layer_tp_fused(static_cast<const bf16*>(hidden), false, nullptr, w.x2, static_cast<bf16*>(K_cache),
                                     static_cast<bf16*>(V_cache), static_cast<const bf16*>(Wqkv_local),
                                     static_cast<const bf16*>(Wo_local), static_cast<const bf16*>(Wgu_local),
@@ -1046,6 +1066,7 @@ int ezb_qwen3_decode_stack_tp_fused(const void* hidden, void* out, const ezb_lay
     const bf16* sin_row = rope_sin ? static_cast<const bf16*>(rope_sin) + row_off : nullptr;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     chain_begin();
+    bool single_kernel = B == 1 && !seq_lens && w.mega;
     for (int l = 0; l < n_layers; ++l) {
         const ezb_layer_t& L = layers_local[l];
         LayerExtras ex;
@@ -1054,6 +1075,21 @@ int ezb_qwen3_decode_stack_tp_fused(const void* hidden, void* out, const ezb_lay
         ex.rope_cos = cos_row, ex.rope_sin = sin_row;
         ex.seq_lens = seq_lens, ex.rope_by_len = seq_lens ? 1 : 0;
         ex.next_Wqkv = (l + 1 < n_layers) ? static_cast<const bf16*>(layers_local[l + 1].Wqkv) : nullptr;
+        if (single_kernel) {
+            // batch 1: one persistent kernel per layer, complete output of layer l in layer_in[l & 1] (the last in out)
+            const bf16* in = l == 0 ? static_cast<const bf16*>(hidden) : layer_in[(l - 1) & 1];
+            bf16* dst = l + 1 == n_layers ? static_cast<bf16*>(out) : layer_in[l & 1];
+            MegaArgs m = mega_args(in, static_cast<bf16*>(L.K_cache), static_cast<bf16*>(L.V_cache), static_cast<const bf16*>(L.Wqkv),
+                                   static_cast<const bf16*>(L.Wo), static_cast<const bf16*>(L.Wgu), static_cast<const bf16*>(L.Wd), dst,
+                                   w, S, H, I_local, NH_local, NKV_local, D, eps, ex);
+            m.link = base;
+            if (decode_mega_supported(m)) {  // same answer for every layer: the sizes do not change
+                EZB_CUDA_TRY(launch_decode_mega(m, st));
+                if (l + 1 == n_layers) return EZB_OK;
+                continue;
+            }
+            single_kernel = false;
+        }
         // layer l > 0 reads x2 of layer l-1 and folds that layer's second sum into its own QKV prologue
         const bf16* x_prev = l == 0 ? static_cast<const bf16*>(hidden) : x2[(l - 1) & 1];
         if (int rc = run_layer_tp_fused(x_prev, l > 0, layer_in[l & 1], x2[l & 1], static_cast<bf16*>(L.K_cache),

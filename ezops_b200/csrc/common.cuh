@@ -134,9 +134,10 @@ __device__ __forceinline__ void tp_bump(const TpLink& l) { l.ctrl_peer[l.rank][k
 // add[0..E-1] += sum over ranks (in rank order) of the E consecutive cells starting at `elem` of this
 // rank's inbox; polls until every cell carries `epoch`, G ranks at a time (G x E 64-bit registers).
 // Returns false (and records the fault) if the wait limit ran out.
+// tp_gather_from names the inbox and the direction itself (a kernel that gathers from more than one inbox).
 template <int G, int E>
-__device__ __forceinline__ bool tp_gather(const TpLink& l, unsigned int epoch, long long elem, float (&add)[E],
-                                          unsigned int* status, long long t0) {
+__device__ __forceinline__ bool tp_gather_from(const TpLink& l, int inbox, bool pull, unsigned int epoch, long long elem,
+                                               float (&add)[E], unsigned int* status, long long t0) {
     static_assert(E % 2 == 0, "cells are fetched in pairs");
     for (int w0 = 0; w0 < l.world; w0 += G) {
         unsigned long long c[G][E];
@@ -148,7 +149,7 @@ __device__ __forceinline__ bool tp_gather(const TpLink& l, unsigned int epoch, l
 #pragma unroll
             for (int g = 0; g < G; ++g)
                 if (pending & (1u << g)) {
-                    const unsigned long long* src = tp_slot(l, l.pull ? w0 + g : l.rank, l.gather_inbox, w0 + g) + elem;
+                    const unsigned long long* src = tp_slot(l, pull ? w0 + g : l.rank, inbox, w0 + g) + elem;
 #pragma unroll
                     for (int q = 0; q < E / 2; ++q)
                         asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];"
@@ -178,6 +179,11 @@ __device__ __forceinline__ bool tp_gather(const TpLink& l, unsigned int epoch, l
             }
     }
     return true;
+}
+template <int G, int E>
+__device__ __forceinline__ bool tp_gather(const TpLink& l, unsigned int epoch, long long elem, float (&add)[E],
+                                          unsigned int* status, long long t0) {
+    return tp_gather_from<G, E>(l, l.gather_inbox, l.pull != 0, epoch, elem, add, status, t0);
 }
 
 // ---------------------------------------------------------------------------
@@ -281,11 +287,26 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
 // 1-D bulk copy global -> shared through the TMA unit, completion counted in
 // bytes on an mbarrier.  Both addresses 16-byte aligned, size a multiple of 16.
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
-        "l"(src), "r"(bytes), "r"(bar)
-        : "memory");
+// `policy` (0 = none) is an L2 cache policy from l2_evict_first_policy(): lines a kernel reads once are marked as the
+// first to be replaced, so a long stream recycles its own lines instead of pushing everything else - dirty lines
+// that would first have to be written back included - out of L2.
+__device__ __forceinline__ unsigned long long l2_evict_first_policy() {
+    unsigned long long pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar,
+                                         unsigned long long policy = 0ull) {
+    if (policy)
+        asm volatile(
+            "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(dst_smem),
+            "l"(src), "r"(bytes), "r"(bar), "l"(policy)
+            : "memory");
+    else
+        asm volatile(
+            "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
+            "l"(src), "r"(bytes), "r"(bar)
+            : "memory");
 }
 
 // ---------------------------------------------------------------------------

@@ -78,8 +78,10 @@ struct MegaParams {
     int gate;      // 1: nothing behind this CTA's K/V stages is requested or prefetched before the QKV barrier has been passed
     unsigned int stage_bytes, act_bytes;
     long long wait_cycles;
+    int evict_first;  // L2 evict-first policy on the streams: 1 = weights, 2 = weights and K/V
     unsigned int* status;
     Trace trace;
+    TpLink link;  // tensor parallel: world > 0, this rank's shard in every weight and cache pointer above
 };
 
 // What one CTA does in every phase; computed identically by producer and consumers.
@@ -96,7 +98,8 @@ template <int D>
 __device__ __forceinline__ MegaSched mega_sched(const MegaParams& p, int cta, int grid) {
     MegaSched s;
     s.q_r0 = (int)((long long)p.R * cta / grid), s.q_r1 = (int)((long long)p.R * (cta + 1) / grid);
-    s.o_r0 = (int)((long long)p.H * cta / grid), s.o_r1 = (int)((long long)p.H * (cta + 1) / grid);
+    // cut on even rows: the tensor-parallel form fetches two neighbouring rows' cells with one 16-byte load
+    s.o_r0 = 2 * (int)((long long)(p.H / 2) * cta / grid), s.o_r1 = 2 * (int)((long long)(p.H / 2) * (cta + 1) / grid);
     s.g_r0 = (int)((long long)p.I * cta / grid), s.g_r1 = (int)((long long)p.I * (cta + 1) / grid);
     s.nkc_h = (p.H + p.kc_h - 1) / p.kc_h;
     s.nkc_q = (p.Q + p.kc_q - 1) / p.kc_q;
@@ -244,6 +247,76 @@ __device__ __forceinline__ void mega_stage_x(const bf16* x, int K, const bf16* n
             }
             mega_store_x8(xs, i, w);
         }
+    }
+    named_bar_sync(1, kMegaConsumerThreads);
+}
+
+// ---- tensor-parallel exchange inside the kernel (the cells and epochs of TpLink, common.cuh)
+__device__ __forceinline__ void mega_tp_push(const TpLink& l, int inbox, long long elem, float v, unsigned int epoch) {
+    const unsigned long long cell = ((unsigned long long)epoch << 32) | (unsigned long long)__float_as_uint(v);
+    for (int w = 0; w < l.world; ++w)
+        tp_store_cell(l.inbox_peer[w] + ((long long)inbox * kTpSlots + l.rank) * l.slot_elems + elem, cell, l.strong_stores);
+}
+
+// Tensor-parallel form of the gate/up staging: x2 = bf16(hidden + bf16(sum over ranks of the o_proj partials in
+// inbox 0)), RMS-normalised into shared memory.  The poll of the cells (this rank's own included) is what orders this
+// phase behind the output projection of every CTA of every rank: no grid barrier in front of it.  The x2 values of the
+// CTA's own rows [o_r0, o_r1) are kept in res_s for the residual of the down projection.
+__device__ __forceinline__ void mega_stage_gather(const TpLink& lg, unsigned int epoch, const bf16* hidden, int K, const bf16* norm_w,
+                                                  float eps, bf16* xs, float* scratch, float* res_s, int o_r0, int o_r1,
+                                                  volatile int* abort_flag, unsigned int* status, int ct, int cw, int lane) {
+    const int nvec = K / 8;
+    const long long t0 = clock64();
+    float ssq = 0.f;
+    for (int i = ct; i < nvec; i += kMegaConsumerThreads) {
+        const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(hidden) + i);
+        float add[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        bool ok = !*abort_flag;
+        if (ok) {
+            if (lg.world <= 2) {
+                ok = tp_gather_from<2, 8>(lg, 0, false, epoch, (long long)i * 8, add, status, t0);
+            } else {
+                float lo[4] = {0.f, 0.f, 0.f, 0.f}, hi[4] = {0.f, 0.f, 0.f, 0.f};
+                ok = tp_gather_from<4, 4>(lg, 0, false, epoch, (long long)i * 8, lo, status, t0) &&
+                     tp_gather_from<4, 4>(lg, 0, false, epoch, (long long)i * 8 + 4, hi, status, t0);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) add[e] = lo[e], add[4 + e] = hi[e];
+            }
+        }
+        if (!ok) *abort_flag = 1;  // a peer never delivered: nothing of this CTA is stored or pushed from here on
+        uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            w[e] = pack_bf16(bf16_lo(w[e]) + round_bf16(add[2 * e]), bf16_hi(w[e]) + round_bf16(add[2 * e + 1]));
+            const float a = bf16_lo(w[e]), b = bf16_hi(w[e]);
+            ssq += a * a + b * b;
+            const int n = i * 8 + 2 * e;
+            if (n >= o_r0 && n < o_r1) res_s[n - o_r0] = a, res_s[n + 1 - o_r0] = b;  // o_r0, o_r1 are even
+        }
+        mega_store_x8(xs, i, w);
+    }
+    ssq = warp_sum(ssq);
+    if (lane == 0) scratch[cw] = ssq;
+    named_bar_sync(1, kMegaConsumerThreads);
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < kMegaConsumerWarps; ++w) tot += scratch[w];
+    const float r = 1.0f / sqrtf(tot / (float)K + eps);
+    for (int i = ct; i < nvec; i += kMegaConsumerThreads) {
+        uint32_t w[4];
+        mega_load_x8(xs, i, w);
+        uint32_t nw[4] = {0u, 0u, 0u, 0u};
+        if (norm_w) {
+            const uint4 q = __ldg(reinterpret_cast<const uint4*>(norm_w) + i);
+            nw[0] = q.x, nw[1] = q.y, nw[2] = q.z, nw[3] = q.w;
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            float lo = bf16_lo(w[e]) * r, hi = bf16_hi(w[e]) * r;
+            if (norm_w) lo *= bf16_lo(nw[e]), hi *= bf16_hi(nw[e]);
+            w[e] = pack_bf16(lo, hi);
+        }
+        mega_store_x8(xs, i, w);
     }
     named_bar_sync(1, kMegaConsumerThreads);
 }
@@ -469,7 +542,9 @@ __device__ __forceinline__ void mega_gemv_phase(const MegaParams& p, MegaCtx& c,
     }
 }
 
-template <int D>
+// LINK: the tensor-parallel instance (partial sums of the two row-parallel projections exchanged through peer memory
+// inside the kernel); the plain instance contains none of that code.
+template <int D, bool LINK>
 __global__ void __launch_bounds__(kMegaThreads, 1) decode_layer_b1_kernel(const MegaParams p) {
     constexpr int DPL = D / 32;  // output dims per lane in P.V
     extern __shared__ __align__(128) unsigned char smem[];
@@ -506,6 +581,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_layer_b1_kernel(const 
     if (warp == 0) {
         // ------------------------------------------------------------ producer
         bool waited = false;
+        const unsigned long long policy = p.evict_first ? l2_evict_first_policy() : 0ull;
         auto issue = [&](int it, bool l2_only) {
             const MegaStage d = mega_locate<D>(p, s, it);
             // The KV cache is mutable state of earlier kernels in the stream: nothing of it is touched
@@ -538,7 +614,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_layer_b1_kernel(const 
             }
             if (lane == 0) mbar_arrive_expect_tx(bar, expect);
             __syncwarp();
-            if (lane < 8 && bytes) bulk_g2s(dst0 + off, src, bytes, bar);
+            if (lane < 8 && bytes) bulk_g2s(dst0 + off, src, bytes, bar, (d.kind == 2 ? p.evict_first > 1 : p.evict_first > 0) ? policy : 0ull);
         };
         // Policy.  (1) Requests queue in front of everything else this SM sends to memory, the barrier traffic
         // included, so only `inflight` stages may be outstanding at a time: enough to cover the latency-bandwidth
@@ -627,6 +703,15 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_layer_b1_kernel(const 
     unsigned long long* trec = (ct == 0) ? trace_open(p.trace, 20u, cta_id) : nullptr;
     pdl_wait();  // hidden, the caches and the control words belong to earlier kernels of the stream
     trace_mark(trec, 3);
+    // tensor parallel: the tags of this launch's two exchanges (inbox 0 after o_proj, inbox 1 after down); a fault
+    // recorded earlier poisons the exchange (see tp_poisoned)
+    unsigned int tp_e0 = 0u, tp_e1 = 0u;
+    if (LINK) {
+        // (inbox 1 one further: the chained kernels advance its epoch between their two exchanges, and a cell they
+        // left behind must never carry the tag this launch waits for)
+        tp_e0 = tp_next_epoch(p.link, 0), tp_e1 = tp_next_epoch(p.link, 1) + 1u;
+        if (tp_poisoned(p.status)) *abort_flag = 1;
+    }
 
     // ================================================================ phase 0: QKV projection
     // residual values of this CTA's H rows, fetched now so that no epilogue waits on a global load
@@ -953,17 +1038,26 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_layer_b1_kernel(const 
     trace_mark(trec, 3);
     mega_gemv_phase<false>(p, c, s.o_r0, s.o_r1, p.Q, p.kc_q, s.nkc_q,
                            [&](int n, float v0, float) {
+                               if (LINK) {  // this rank's partial goes into its slot of inbox 0 on every rank
+                                   mega_tp_push(p.link, 0, n, v0, tp_e0);
+                                   return;
+                               }
                                const bf16 x2v = __float2bfloat16_rn(res_s[n - s.o_r0] + round_bf16(v0));
                                p.x2[n] = x2v;
                                res_s[n - s.o_r0] = __bfloat162float(x2v);  // the down projection adds onto this
                            },
                            trec, 32u);
     trace_mark(trec, 5);
-    mega_grid_barrier(p, c, MB_OPROJ);
+    if (!LINK) mega_grid_barrier(p, c, MB_OPROJ);
 
     // ================================================================ phase 3: gate/up + SwiGLU
     trec = (ct == 0) ? trace_open(p.trace, 23u, cta_id) : nullptr;
-    mega_stage_x<true>(p.x2, p.H, p.post_norm_w, p.eps, xs, norm_scratch, ct, cw, lane);
+    if (LINK) {
+        mega_stage_gather(p.link, tp_e0, p.hidden, p.H, p.post_norm_w, p.eps, xs, norm_scratch, res_s, s.o_r0, s.o_r1, abort_flag,
+                          p.status, ct, cw, lane);
+    } else {
+        mega_stage_x<true>(p.x2, p.H, p.post_norm_w, p.eps, xs, norm_scratch, ct, cw, lane);
+    }
     trace_mark(trec, 3);
     mega_gemv_phase<true>(p, c, s.g_r0, s.g_r1, p.H, p.kc_h, s.nkc_h,
                           [&](int n, float v0, float v1) {
@@ -980,6 +1074,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_layer_b1_kernel(const 
         if (prev == gridDim.x - 1) {
             p.ctrl[MB_QKV] = 0u, p.ctrl[MB_ATTN] = 0u, p.ctrl[MB_OPROJ] = 0u, p.ctrl[MB_GATEUP] = 0u;
             p.ctrl[MB_EXIT] = 0u;
+            // tensor parallel: every CTA has read both epochs long ago; the next launch tags its cells one higher
+            // (not after a fault: a poisoned chain advances nothing)
+            if (LINK && !*abort_flag) p.link.ctrl_peer[p.link.rank][kTpEpoch + 0] += 1u, p.link.ctrl_peer[p.link.rank][kTpEpoch + 1] += 1u;
         }
     }
 
@@ -988,9 +1085,26 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_layer_b1_kernel(const 
     mega_stage_x<false>(p.h, p.I, nullptr, p.eps, xs, norm_scratch, ct, cw, lane);
     trace_mark(trec, 3);
     mega_gemv_phase<false>(p, c, s.o_r0, s.o_r1, p.I, p.kc_i, s.nkc_i,
-                           [&](int n, float v0, float) { p.out[n] = __float2bfloat16_rn(res_s[n - s.o_r0] + round_bf16(v0)); },
+                           [&](int n, float v0, float) {
+                               if (LINK) mega_tp_push(p.link, 1, n, v0, tp_e1);
+                               else p.out[n] = __float2bfloat16_rn(res_s[n - s.o_r0] + round_bf16(v0));
+                           },
                            trec, 34u);
     trace_mark(trec, 5);
+    if (LINK) {
+        // out = x2 + bf16(sum over ranks of the down partials) for this CTA's rows: one thread per pair of rows polls
+        // the pair's cells of every rank in inbox 1 (same bits on every rank: the sum runs in rank order)
+        const int npair = (s.o_r1 - s.o_r0) / 2;
+        const long long t0 = clock64();
+        for (int pr = ct; pr < npair; pr += kMegaConsumerThreads) {
+            const int n = s.o_r0 + 2 * pr;
+            float add[2] = {0.f, 0.f};
+            const bool ok = !*abort_flag && tp_gather_from<8, 2>(p.link, 1, false, tp_e1, n, add, p.status, t0);
+            if (ok)
+                *reinterpret_cast<uint32_t*>(p.out + n) =
+                    pack_bf16(res_s[n - s.o_r0] + round_bf16(add[0]), res_s[n + 1 - s.o_r0] + round_bf16(add[1]));
+        }
+    }
 
 }
 
@@ -1065,9 +1179,9 @@ bool decode_mega_supported(const MegaArgs& a) {
     return mega_plan(a, pl);
 }
 
-template <int D>
+template <int D, bool LINK>
 static cudaError_t launch_mega_instance(const MegaParams& p, const MegaPlan& pl, cudaStream_t stream) {
-    auto kernel = decode_layer_b1_kernel<D>;
+    auto kernel = decode_layer_b1_kernel<D, LINK>;
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1107,6 +1221,7 @@ cudaError_t launch_decode_mega(const MegaArgs& a, cudaStream_t stream) {
     p.NS = pl.NS;
     p.l2_window = tuning(EZB_TUNE_MEGA_L2_STAGES);
     if (p.l2_window < 0 || !tuning(EZB_TUNE_L2_PREFETCH)) p.l2_window = 0;
+    p.evict_first = tuning(EZB_TUNE_STREAM_EVICT_FIRST);
     p.inflight = tuning(EZB_TUNE_MEGA_INFLIGHT);
     if (p.inflight < 0 || p.inflight >= p.NS) p.inflight = 0;
     p.gate = tuning(EZB_TUNE_MEGA_GATE) ? 1 : 0;
@@ -1115,8 +1230,13 @@ cudaError_t launch_decode_mega(const MegaArgs& a, cudaStream_t stream) {
     p.status = status_ptr();
     if (!p.status) return cudaErrorUnknown;
     p.trace = trace_handle();
-    if (a.D == 128) return launch_mega_instance<128>(p, pl, stream);
-    return launch_mega_instance<64>(p, pl, stream);
+    p.link = a.link;
+    if (a.link.world > 0) {
+        if (a.D == 128) return launch_mega_instance<128, true>(p, pl, stream);
+        return launch_mega_instance<64, true>(p, pl, stream);
+    }
+    if (a.D == 128) return launch_mega_instance<128, false>(p, pl, stream);
+    return launch_mega_instance<64, false>(p, pl, stream);
 }
 
 }  // namespace ezb

@@ -71,6 +71,7 @@ struct GemvParams {
     int nstages;   // ring depth
     int prefetch;  // stages requested before the dependency wait
     int window;    // at most this many stages requested but not yet landed (0 = no limit)
+    int evict_first;  // 1: weight rows are read with the L2 evict-first policy
     unsigned int* status;
     PrefetchList next;
     Trace trace;
@@ -373,6 +374,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_stream_kernel(const Gemv
         // Arms the stage's barrier with the byte count of everything that will
         // land in it, then requests the weight rows (lanes 0..WROWS-1, one row
         // segment each).
+        const unsigned long long w_policy = p.evict_first ? l2_evict_first_policy() : 0ull;
         auto request_weights = [&](int it) {
             const int rb = it / nkc, kci = it - rb * nkc, s = it % NS;
             const int k0 = kci * p.kc;
@@ -389,7 +391,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_stream_kernel(const Gemv
                     const bf16* src = (m ? p.W1 : p.W0) + (long long)(row0 + r) * p.ldw + k0;
                     const uint32_t dst = smem_u32(stage_base + (size_t)s * stage_bytes) +
                                          (uint32_t)((m * kRowBlock + r) * ws_stride * (int)sizeof(bf16));
-                    bulk_g2s(dst, src, (uint32_t)(len * (int)sizeof(bf16)), bar);
+                    bulk_g2s(dst, src, (uint32_t)(len * (int)sizeof(bf16)), bar, w_policy);
                 }
             }
         };
@@ -566,6 +568,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_rows8_kernel(const GemvP
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer
+        const unsigned long long w_policy = p.evict_first ? l2_evict_first_policy() : 0ull;
         auto request = [&](int it) {
             const int rb = it / nkc, kci = it - rb * nkc, s = it % NS;
             const int k0 = kci * p.kc;
@@ -581,7 +584,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_rows8_kernel(const GemvP
                 if (u < nu) {
                     const bf16* src = (m ? p.W1 : p.W0) + (long long)(unit0 + u) * p.ldw + k0;
                     const uint32_t dst = smem_u32(stage_base + (size_t)s * stage_bytes) + (uint32_t)(lane * ws_stride * (int)sizeof(bf16));
-                    bulk_g2s(dst, src, (uint32_t)(len * (int)sizeof(bf16)), bar);
+                    bulk_g2s(dst, src, (uint32_t)(len * (int)sizeof(bf16)), bar, w_policy);
                 }
             }
         };
@@ -897,6 +900,7 @@ cudaError_t launch_gemv(const GemvArgs& a, cudaStream_t stream) {
     p.out = a.out, p.ldout = a.ldout;
     p.kc = pl.kc, p.nstages = pl.nstages, p.prefetch = pl.prefetch;
     p.window = tuning(EZB_TUNE_GEMV_WINDOW);
+    p.evict_first = tuning(EZB_TUNE_STREAM_EVICT_FIRST) ? 1 : 0;
     p.status = status_ptr();
     if (!p.status) return cudaErrorUnknown;
     p.next = a.next;

@@ -154,6 +154,9 @@ struct MegaArgs {
     void* mega_workspace = nullptr;
     int S = 0, H = 0, I = 0, NH = 0, NKV = 0, D = 0;
     float eps = 1e-6f;
+    // tensor parallel (world > 0): the pointers above are this rank's shards, NH / NKV / I the local sizes; the partial
+    // sums of o_proj and down are exchanged inside the kernel through the communication buffers of the link
+    TpLink link = {0, 0, {}, {}, 0, -1, -1, -1};
 };
 bool decode_mega_supported(const MegaArgs& a);  // shape inside what the kernel covers on the current device (and switched on)
 size_t decode_mega_workspace_bytes(int NKV, int D);

@@ -74,7 +74,8 @@ typedef struct CUstream_st* ezb_stream_t; /* same type as cudaStream_t */
 #define EZB_TUNE_MEGA_GATE 22         /* single-kernel layer: 1 = a producer stops behind its K/V stages until the QKV barrier is passed */
 #define EZB_TUNE_TP_WAIT_LIMIT_MS 23   /* fused exchange: budget of one wait for the peers' partial sums, ms at 2 GHz (default 5000)      */
 #define EZB_TUNE_TP_STRONG_STORES 24   /* fused exchange: 1 = publish cells with st.relaxed.sys instead of plain stores (default 0) */
-#define EZB_TUNE_COUNT 25
+#define EZB_TUNE_STREAM_EVICT_FIRST 25 /* weight streams carry the L2 evict-first policy: 0 = off, 1 = weights (default), 2 = also K/V in the single-kernel layer */
+#define EZB_TUNE_COUNT 26
 
 int ezb_version(void);
 const char* ezb_strerror(int code);

@@ -29,4 +29,4 @@ def test_fused_exchange_matches_nccl_and_the_oracle(world):
            "--master-port", str(29600 + world), str(ROOT / "tests" / "tp_fused_worker.py")]
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=480)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
-    assert res.stdout.count("identical_across_ranks=True") == 5, res.stdout
+    assert res.stdout.count("identical_across_ranks=True") == 7, res.stdout

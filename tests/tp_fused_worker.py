@@ -25,9 +25,11 @@ def main() -> int:
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     ok = True
-    # batch 1 and 3: gather and push inside the small-batch kernel; batch 16: row kernel + tensor-core kernel
-    # the last case is the benchmark's tensor-parallel configuration (Qwen3-32B shapes, batch 64) at a shorter cache
-    for sh, B, S in [(wl.QWEN3_VL_2B, 1, 700), (wl.QWEN3_8B, 3, 1025), (wl.QWEN3_VL_2B, 16, 400), (wl.QWEN3_32B, 64, 1536)]:
+    # batch 1: the rank-local layer and both exchanges in one persistent kernel (and, with that switched off, in the
+    # small-batch kernels); batch 3: gather and push inside the small-batch kernel; batch 16: row kernel + tensor-core
+    # kernel; the last case is the benchmark's tensor-parallel configuration (Qwen3-32B shapes, batch 64) at a shorter cache
+    for sh, B, S in [(wl.QWEN3_VL_2B, 1, 700), (wl.QWEN3_8B, 1, 2100), (wl.QWEN3_8B, 3, 1025), (wl.QWEN3_VL_2B, 16, 400),
+                     (wl.QWEN3_32B, 64, 1536)]:
         hidden, K0, V0, Wqkv, Wo, Wgu, Wd = wl.decode_layer_inputs(sh, B, S)
         heads = (sh.num_heads, sh.num_kv_heads, sh.head_dim)
         ref = (orc.qwen3_dense_decode_ref(hidden, K0.clone(), V0.clone(), Wqkv, Wo, Wgu, Wd, *heads, lean_attention=B >= 32)
@@ -43,6 +45,12 @@ def main() -> int:
         dist.barrier()
         outs = [fused(hid, Kl, Vl, *shards) for _ in range(6)]  # several epochs of the exchange
         torch.cuda.synchronize()
+        chained = outs[0]
+        if B == 1:  # the same exchange through the chained kernels: their arithmetic is the NCCL form's
+            _lib.set_tuning(mega=0)
+            chained = fused(hid, Kl, Vl, *shards)
+            torch.cuda.synchronize()
+            _lib.set_tuning(mega=1)
         status = _lib.device_status()
         gathered = [torch.empty_like(a) for _ in range(world)]
         dist.all_gather(gathered, outs[-1])
@@ -52,7 +60,8 @@ def main() -> int:
         if rank == 0:
             err_fused = ((outs[0].cpu().float() - ref.float()).norm() / ref.float().norm()).item()
             err_nccl = ((a.cpu().float() - ref.float()).norm() / ref.float().norm()).item()
-            good = err_fused < 1e-2 and err_nccl < 1e-2 and (world != 2 or torch.equal(a, outs[0]))
+            err_chained = ((chained.cpu().float() - ref.float()).norm() / ref.float().norm()).item()
+            good = err_fused < 1e-2 and err_nccl < 1e-2 and err_chained < 1e-2 and (world != 2 or torch.equal(a, chained))
             verdict *= int(good)
             print(f"tp={world} {sh.name} B={B} S={S}: rel_fro fused {err_fused:.3e} nccl {err_nccl:.3e} "
                   f"identical_across_ranks={same_on_all_ranks} repeatable={repeatable} status={status}", flush=True)
@@ -61,11 +70,20 @@ def main() -> int:
         torch.cuda.synchronize()
         dist.barrier()
         fused.close()
-    # the whole stack: three layers with norm weights and RoPE, second sums folded into the next layer
-    sh, B, S, NL = wl.QWEN3_VL_2B, 2, 300, 3
-    hid, layers, cos, sin = wl.decode_stack_inputs(sh, B, S, NL)
+    # the whole stack: three layers with norm weights and RoPE; batch 2: second sums folded into the next layer's
+    # first kernel; batch 1: one persistent kernel per layer
+    for B in (2, 1):
+        ok = run_stack_case(rank, world, B) and ok
+    dist.barrier()
+    sys.stdout.flush()
+    os._exit(0 if ok else 1)  # no NCCL teardown: see bench.py
+
+
+def run_stack_case(rank: int, world: int, B: int) -> bool:
     import copy
 
+    sh, S, NL = wl.QWEN3_VL_2B, 300, 3
+    hid, layers, cos, sin = wl.decode_stack_inputs(sh, B, S, NL)
     ref = orc.qwen3_decode_stack_ref(hid, copy.deepcopy(layers), sh.num_heads, sh.num_kv_heads, sh.head_dim, cos, sin) if rank == 0 else None
     local = [{k: (None if v is None else v.cuda()) for k, v in L.items()}
              for L in tpm.shard_stack(layers, sh.num_heads, sh.num_kv_heads, sh.head_dim, world, rank)]
@@ -82,13 +100,10 @@ def main() -> int:
         verdict *= int(err < 1e-2)
         print(f"tp={world} stack of {NL} layers B={B} S={S}: rel_fro {err:.3e} identical_across_ranks={good} status={status}", flush=True)
     dist.all_reduce(verdict, op=dist.ReduceOp.MIN)
-    ok = ok and bool(verdict.item())
     torch.cuda.synchronize()
     dist.barrier()
     stack.close()
-    dist.barrier()
-    sys.stdout.flush()
-    os._exit(0 if ok else 1)  # no NCCL teardown: see bench.py
+    return bool(verdict.item())
 
 
 if __name__ == "__main__":
