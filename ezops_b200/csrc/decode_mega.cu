@@ -53,7 +53,7 @@ static constexpr int kMegaRedBytes = 2 * kMegaRedGroup * kMegaConsumerWarps * 8 
 static constexpr int kMegaRowPad = 32;         // elements of padding behind a weight row in a stage (64 B: 128-bit loads of two rows never collide)
 static constexpr int kMegaResSlots = 256;      // output rows of one CTA in the H-row phases
 static constexpr int kMegaSubKeysMax = 256;    // keys of one attention sub-chunk (one K stage + one V stage)
-static constexpr int kMegaMaxSplits = 64;      // slices per kv head
+static constexpr int kMegaMaxSplits = 32;      // slices per kv head (the fold at the end reads them in two round trips)
 static constexpr int kCombineBatch = 10;       // slice records a combining thread fetches per round trip
 
 enum MegaCtrl : int { MB_QKV = 0, MB_ATTN = 1, MB_OPROJ = 2, MB_GATEUP = 3, MB_EXIT = 4, MB_TICKET0 = 8 };
@@ -258,67 +258,11 @@ __device__ __forceinline__ void mega_tp_push(const TpLink& l, int inbox, long lo
         tp_store_cell(l.inbox_peer[w] + ((long long)inbox * kTpSlots + l.rank) * l.slot_elems + elem, cell, l.strong_stores);
 }
 
-// Tensor-parallel form of the gate/up staging: x2 = bf16(hidden + bf16(sum over ranks of the o_proj partials in
-// inbox 0)), RMS-normalised into shared memory.  The poll of the cells (this rank's own included) is what orders this
-// phase behind the output projection of every CTA of every rank: no grid barrier in front of it.  The x2 values of the
-// CTA's own rows [o_r0, o_r1) are kept in res_s for the residual of the down projection.
-__device__ __forceinline__ void mega_stage_gather(const TpLink& lg, unsigned int epoch, const bf16* hidden, int K, const bf16* norm_w,
-                                                  float eps, bf16* xs, float* scratch, float* res_s, int o_r0, int o_r1,
-                                                  volatile int* abort_flag, unsigned int* status, int ct, int cw, int lane) {
-    const int nvec = K / 8;
-    const long long t0 = clock64();
-    float ssq = 0.f;
-    for (int i = ct; i < nvec; i += kMegaConsumerThreads) {
-        const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(hidden) + i);
-        float add[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        bool ok = !*abort_flag;
-        if (ok) {
-            if (lg.world <= 2) {
-                ok = tp_gather_from<2, 8>(lg, 0, false, epoch, (long long)i * 8, add, status, t0);
-            } else {
-                float lo[4] = {0.f, 0.f, 0.f, 0.f}, hi[4] = {0.f, 0.f, 0.f, 0.f};
-                ok = tp_gather_from<4, 4>(lg, 0, false, epoch, (long long)i * 8, lo, status, t0) &&
-                     tp_gather_from<4, 4>(lg, 0, false, epoch, (long long)i * 8 + 4, hi, status, t0);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) add[e] = lo[e], add[4 + e] = hi[e];
-            }
-        }
-        if (!ok) *abort_flag = 1;  // a peer never delivered: nothing of this CTA is stored or pushed from here on
-        uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            w[e] = pack_bf16(bf16_lo(w[e]) + round_bf16(add[2 * e]), bf16_hi(w[e]) + round_bf16(add[2 * e + 1]));
-            const float a = bf16_lo(w[e]), b = bf16_hi(w[e]);
-            ssq += a * a + b * b;
-            const int n = i * 8 + 2 * e;
-            if (n >= o_r0 && n < o_r1) res_s[n - o_r0] = a, res_s[n + 1 - o_r0] = b;  // o_r0, o_r1 are even
-        }
-        mega_store_x8(xs, i, w);
-    }
-    ssq = warp_sum(ssq);
-    if (lane == 0) scratch[cw] = ssq;
-    named_bar_sync(1, kMegaConsumerThreads);
-    float tot = 0.f;
-#pragma unroll
-    for (int w = 0; w < kMegaConsumerWarps; ++w) tot += scratch[w];
-    const float r = 1.0f / sqrtf(tot / (float)K + eps);
-    for (int i = ct; i < nvec; i += kMegaConsumerThreads) {
-        uint32_t w[4];
-        mega_load_x8(xs, i, w);
-        uint32_t nw[4] = {0u, 0u, 0u, 0u};
-        if (norm_w) {
-            const uint4 q = __ldg(reinterpret_cast<const uint4*>(norm_w) + i);
-            nw[0] = q.x, nw[1] = q.y, nw[2] = q.z, nw[3] = q.w;
-        }
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            float lo = bf16_lo(w[e]) * r, hi = bf16_hi(w[e]) * r;
-            if (norm_w) lo *= bf16_lo(nw[e]), hi *= bf16_hi(nw[e]);
-            w[e] = pack_bf16(lo, hi);
-        }
-        mega_store_x8(xs, i, w);
-    }
-    named_bar_sync(1, kMegaConsumerThreads);
+// add[0..1] += sum over ranks (in rank order) of the cells of rows n, n + 1 (n even) in `inbox` of this rank: the
+// poll that ends each of the two exchanges for the rows a CTA owns.
+__device__ __forceinline__ bool mega_tp_gather2(const TpLink& l, int inbox, unsigned int epoch, int n, float (&add)[2],
+                                                unsigned int* status, long long t0) {
+    return tp_gather_from<8, 2>(l, inbox, false, epoch, n, add, status, t0);
 }
 
 // Head RMSNorm (+ optional weight, + optional rotate-half RoPE) of one head held by a warp: lane owns
@@ -1047,17 +991,31 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_layer_b1_kernel(const 
                                res_s[n - s.o_r0] = __bfloat162float(x2v);  // the down projection adds onto this
                            },
                            trec, 32u);
+    if (LINK) {
+        // Two-level gather.  Every CTA needs all of x2, but polling H cells of every rank in 148 CTAs costs more L2
+        // traffic than the exchange itself.  So a CTA sums the ranks' partials only for the rows it owns, stores
+        // x2 = hidden + bf16(sum) for them (the same bits on every rank: rank order), and the grid barrier below then
+        // publishes the complete vector to everybody, exactly as on one GPU.
+        const int npair = (s.o_r1 - s.o_r0) / 2;
+        const long long t0 = clock64();
+        for (int pr = ct; pr < npair; pr += kMegaConsumerThreads) {
+            const int n = s.o_r0 + 2 * pr;
+            float add[2] = {0.f, 0.f};
+            if (*abort_flag || !mega_tp_gather2(p.link, 0, tp_e0, n, add, p.status, t0)) {
+                *abort_flag = 1;  // a peer never delivered: nothing of this CTA is stored or pushed from here on
+                break;
+            }
+            const uint32_t x2w = pack_bf16(res_s[n - s.o_r0] + round_bf16(add[0]), res_s[n + 1 - s.o_r0] + round_bf16(add[1]));
+            *reinterpret_cast<uint32_t*>(p.x2 + n) = x2w;
+            res_s[n - s.o_r0] = bf16_lo(x2w), res_s[n + 1 - s.o_r0] = bf16_hi(x2w);  // the down projection adds onto this
+        }
+    }
     trace_mark(trec, 5);
-    if (!LINK) mega_grid_barrier(p, c, MB_OPROJ);
+    mega_grid_barrier(p, c, MB_OPROJ);
 
     // ================================================================ phase 3: gate/up + SwiGLU
     trec = (ct == 0) ? trace_open(p.trace, 23u, cta_id) : nullptr;
-    if (LINK) {
-        mega_stage_gather(p.link, tp_e0, p.hidden, p.H, p.post_norm_w, p.eps, xs, norm_scratch, res_s, s.o_r0, s.o_r1, abort_flag,
-                          p.status, ct, cw, lane);
-    } else {
-        mega_stage_x<true>(p.x2, p.H, p.post_norm_w, p.eps, xs, norm_scratch, ct, cw, lane);
-    }
+    mega_stage_x<true>(p.x2, p.H, p.post_norm_w, p.eps, xs, norm_scratch, ct, cw, lane);
     trace_mark(trec, 3);
     mega_gemv_phase<true>(p, c, s.g_r0, s.g_r1, p.H, p.kc_h, s.nkc_h,
                           [&](int n, float v0, float v1) {
@@ -1094,16 +1052,18 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_layer_b1_kernel(const 
     if (LINK) {
         // out = x2 + bf16(sum over ranks of the down partials) for this CTA's rows: one thread per pair of rows polls
         // the pair's cells of every rank in inbox 1 (same bits on every rank: the sum runs in rank order)
+        trec = (ct == 0) ? trace_open(p.trace, 26u, cta_id) : nullptr;
         const int npair = (s.o_r1 - s.o_r0) / 2;
         const long long t0 = clock64();
         for (int pr = ct; pr < npair; pr += kMegaConsumerThreads) {
             const int n = s.o_r0 + 2 * pr;
             float add[2] = {0.f, 0.f};
-            const bool ok = !*abort_flag && tp_gather_from<8, 2>(p.link, 1, false, tp_e1, n, add, p.status, t0);
+            const bool ok = !*abort_flag && mega_tp_gather2(p.link, 1, tp_e1, n, add, p.status, t0);
             if (ok)
                 *reinterpret_cast<uint32_t*>(p.out + n) =
                     pack_bf16(res_s[n - s.o_r0] + round_bf16(add[0]), res_s[n + 1 - s.o_r0] + round_bf16(add[1]));
         }
+        trace_mark(trec, 5);
     }
 
 }
