@@ -95,7 +95,7 @@ static const int kTuningDefaults[EZB_TUNE_COUNT] = {
     0,    // EZB_TUNE_GEMV_WINDOW
     0,    // EZB_TUNE_L2_PREFETCH_ATTN_KB
     1,    // EZB_TUNE_TC
-    3,    // EZB_TUNE_ATTN_WAVES_UNIFORM
+    0,    // EZB_TUNE_ATTN_WAVES_UNIFORM
     0,    // EZB_TUNE_TP_POLL_ALL
     0,    // EZB_TUNE_TP_PULL
     1,    // EZB_TUNE_MEGA

@@ -526,13 +526,25 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
 // ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
-// Rows of equal length are cut into few, long splits (measured best at about 1.5 resident waves of
-// CTAs: less start-up, merge and combine work per key); ragged batches into more, shorter ones,
-// because every row is cut on the grid of the longest row and short splits balance better.
-int attn_chunk_keys(int B, int NKV, int S, bool ragged) {
+// Rows of equal length are cut so that all CTAs are resident together, in ONE wave: as many splits per (row, kv
+// head) as the resident slots allow, never more.  A second, partly filled wave costs a whole extra pass over a split
+// (Qwen3-8B layer, KV 4096, batch 2 / 4 / 8 / 16 / 32: 94.5 / 110.5 / 126.8 / 147.1 / 191.4 us with splits sized for
+// 1.5 waves, 89.5 / 107.4 / 124.6 / 141.2 / 181.6 with this rule; a sweep over every split length confirmed the
+// optimum at ~256 CTAs for each).  Ragged batches are cut into more, shorter splits, because every row is cut on
+// the grid of the longest row and short splits balance better.
+int attn_chunk_keys(int B, int NKV, int S, bool ragged, int D) {
     const long long total = (long long)B * NKV * S;
-    const long long target = (long long)sm_count() * max(1, tuning(ragged ? EZB_TUNE_ATTN_WAVES : EZB_TUNE_ATTN_WAVES_UNIFORM));
-    long long chunk = (total + target - 1) / target;
+    const int waves = tuning(ragged ? EZB_TUNE_ATTN_WAVES : EZB_TUNE_ATTN_WAVES_UNIFORM);
+    long long chunk;
+    if (!ragged && waves <= 0) {
+        const long long slots = (long long)sm_count() * (D <= 64 ? 4 : 2);  // resident CTAs: the ring is 3 x 2 x 64 keys x D
+        long long splits = slots / ((long long)B * NKV);
+        if (splits < 1) splits = 1;
+        chunk = (S + splits - 1) / splits;
+    } else {
+        const long long target = (long long)sm_count() * max(1, waves);
+        chunk = (total + target - 1) / target;
+    }
     chunk = (chunk + kTileKeys - 1) / kTileKeys * kTileKeys;
     long long floor_keys = max(kTileKeys, tuning(EZB_TUNE_ATTN_MIN_CHUNK) / kTileKeys * kTileKeys);
     if (chunk < floor_keys) chunk = floor_keys;
@@ -552,7 +564,7 @@ size_t attn_counters_bytes(int B, int H, int NKV) {
 
 size_t attn_workspace_bytes(int B, int H, int NKV, int S, int D) {
     const int G = H / NKV, nqt = (G + 15) / 16;
-    const int chunk = min(attn_chunk_keys(B, NKV, S, false), attn_chunk_keys(B, NKV, S, true));  // covers both cuts
+    const int chunk = min(attn_chunk_keys(B, NKV, S, false, D), attn_chunk_keys(B, NKV, S, true, D));  // covers both cuts
     const int nchunks = (S + chunk - 1) / chunk;
     const size_t items = (size_t)B * NKV * nqt * nchunks;
     return counters_bytes(B, NKV, nqt) + items * 16 * 2 * sizeof(float) + items * 16 * D * sizeof(float);
@@ -579,7 +591,7 @@ cudaError_t launch_attn_decode(const AttnArgs& a, cudaStream_t stream) {
     p.seq_lens = a.seq_lens;
     p.B = a.B, p.H = a.H, p.NKV = a.NKV, p.S = a.S, p.G = a.H / a.NKV;
     p.nqt = (p.G + 15) / 16;
-    p.chunk = attn_chunk_keys(a.B, a.NKV, a.S, a.seq_lens != nullptr);
+    p.chunk = attn_chunk_keys(a.B, a.NKV, a.S, a.seq_lens != nullptr, a.D);
     p.nchunks = (a.S + p.chunk - 1) / p.chunk;
     p.scale_log2e = 1.4426950408889634f / sqrtf((float)a.D);
     unsigned char* ws = reinterpret_cast<unsigned char*>(a.workspace);

@@ -30,6 +30,9 @@
 // and returns.
 #include <cuda.h>
 
+#include <cstring>
+#include <mutex>
+
 #include "launchers.h"
 
 namespace ezb {
@@ -533,7 +536,7 @@ static EncodeTiledFn encode_fn() {
 
 // 2-D bf16 row-major [rows, cols] with leading dimension ld; box = [64 cols, box_rows], 128-byte swizzle,
 // out-of-range elements read as zero.
-static bool make_map(CUtensorMap* map, const bf16* base, long long rows, long long cols, long long ld, int box_rows) {
+static bool encode_map(CUtensorMap* map, const bf16* base, long long rows, long long cols, long long ld, int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -543,6 +546,41 @@ static bool make_map(CUtensorMap* map, const bf16* base, long long rows, long lo
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<bf16*>(base), dims, strides, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// A descriptor is a pure function of (address, shape, leading dimension, box): a decode loop asks for the same few
+// dozen over and over (four weight matrices per layer and the activation buffers of the workspace), so they are
+// encoded once and kept in a small table (round-robin replacement; a hit costs a short scan under a mutex instead
+// of a driver call per operand and launch).
+struct MapKey {
+    const void* base;
+    long long rows, cols, ld;
+    int box_rows;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+    }
+};
+static constexpr int kMapCacheSize = 256;
+static bool make_map(CUtensorMap* map, const bf16* base, long long rows, long long cols, long long ld, int box_rows) {
+    struct Entry {
+        MapKey key;
+        alignas(64) CUtensorMap map;
+    };
+    static std::mutex mu;
+    static Entry* table = new Entry[kMapCacheSize]();  // never freed: lives as long as the library
+    static int used = 0, next = 0;
+    const MapKey key = {base, rows, cols, ld, box_rows};
+    std::lock_guard<std::mutex> lock(mu);
+    for (int i = 0; i < used; ++i)
+        if (table[i].key == key) {
+            std::memcpy(map, &table[i].map, sizeof(CUtensorMap));
+            return true;
+        }
+    if (!encode_map(map, base, rows, cols, ld, box_rows)) return false;
+    const int slot = used < kMapCacheSize ? used++ : (next = (next + 1) % kMapCacheSize);
+    table[slot].key = key;
+    std::memcpy(&table[slot].map, map, sizeof(CUtensorMap));
+    return true;
 }
 
 static int tc_batch_tile(int B) { return B <= 16 ? 16 : (B <= 32 ? 32 : 64); }

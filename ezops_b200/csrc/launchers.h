@@ -135,7 +135,7 @@ struct AttnArgs {
 };
 size_t attn_workspace_bytes(int B, int H, int NKV, int S, int D);
 size_t attn_counters_bytes(int B, int H, int NKV);  // leading part of the workspace that must be zero before a call
-int attn_chunk_keys(int B, int NKV, int S, bool ragged);  // keys per KV split chosen for this shape
+int attn_chunk_keys(int B, int NKV, int S, bool ragged, int D = 128);  // keys per KV split chosen for this shape
 cudaError_t launch_attn_decode(const AttnArgs& a, cudaStream_t stream);
 
 // ------------------------------------------------- whole layer, batch 1 ---

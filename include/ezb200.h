@@ -63,7 +63,7 @@ typedef struct CUstream_st* ezb_stream_t; /* same type as cudaStream_t */
 #define EZB_TUNE_GEMV_WINDOW 11     /* stages that may be requested but not landed, small-batch kernel (0 = ring depth) */
 #define EZB_TUNE_L2_PREFETCH_ATTN_KB 12 /* KB per CTA of the gate/up weights that the attention kernel pulls ahead (default 0) */
 #define EZB_TUNE_TC 13              /* 1: batched projections run on tcgen05 tensor cores (default 1)                   */
-#define EZB_TUNE_ATTN_WAVES_UNIFORM 14 /* as ATTN_WAVES, used when all rows have the same length (default 3)    */
+#define EZB_TUNE_ATTN_WAVES_UNIFORM 14 /* rows of equal length: 0 (default) = as many splits as fit in one resident wave; n > 0 = as ATTN_WAVES */
 #define EZB_TUNE_TP_POLL_ALL 15       /* fused exchange prologue: 0 = by world size (all ranks at once when > 2), 1 = always, 2 = never */
 #define EZB_TUNE_TP_PULL 16           /* fused exchange direction: 0 = push (default), 1 = pull (consumers read the peers' buffers) */
 #define EZB_TUNE_MEGA 17              /* 1: the batch-1 decode layer runs as one persistent kernel when the shape allows (default 1) */
