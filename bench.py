@@ -55,7 +55,7 @@ UNIT = "GB/s"
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--exchange", choices=["auto", "fused", "nccl"], default="auto",
+    ap.add_argument("--exchange", choices=["auto", "fused", "nccl", "peer"], default="auto",
                     help="N > 1: how the two sums over ranks of a layer are done")
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
@@ -74,6 +74,9 @@ def parse_args():
     ap.add_argument("--stack", action="store_true", help="same as --calls stack")
     ap.add_argument("--roofline-only", action="store_true",
                     help="run only the roofline leg (a few launches of the dominant kernel): the command an ncu capture wraps")
+    ap.add_argument("--exchange-only", action="store_true",
+                    help="N > 1: time only the two NCCL all-reduces of a layer ([batch, hidden] fp32 each), no compute: "
+                         "the collective's share of a step of --exchange nccl")
     ap.add_argument("--lead-in", type=int, default=200,
                     help="untimed steps issued directly in front of the timed ones (same stream, no host sync in between)")
     ap.add_argument("--no-cross-call-pdl", action="store_true",
@@ -222,13 +225,14 @@ def resolve_calls(args, n):
         return "layer"
     exchange = args.exchange
     if exchange == "auto":
-        exchange = "fused" if args.batch <= 8 else "nccl"
+        exchange = "fused" if args.batch <= 8 else "peer"
     return "stack" if n > 1 and exchange == "fused" else "layer"
 
 
 def workload_config(args, shape, n):
     return {
-        "workload": f"{shape.name} dense decode layer, batch {args.batch}, kv_len {args.seq_len}, bf16, tp{n}",
+        "workload": (f"{shape.name} dense decode layer, batch {args.batch}, kv_len {args.seq_len}, bf16, tp{n}"
+                     + (" - EXCHANGE ONLY: the layer's two all-reduces, no compute" if getattr(args, "exchange_only", False) else "")),
         "hidden": shape.hidden, "intermediate": shape.inter, "heads": f"{shape.num_heads}q/{shape.num_kv_heads}kv x {shape.head_dim}",
         "parallelism": f"tp{n}",
         "cache_policy": f"inputs larger than L2: steps rotate over {NUM_WEIGHT_SETS * n} weight+KV sets per GPU",
@@ -375,14 +379,29 @@ def main():
         # batch allows it, NCCL all-reduce between the three local parts otherwise.
         exchange = args.exchange
         if exchange == "auto":
-            # the fused exchange wins where a layer is latency-bound (batch <= 8); above that the peer stores of
-            # the tensor-core epilogue were measured slower than NCCL's all-reduce
-            exchange = "fused" if B <= 8 else "nccl"
+            # the sums inside the kernels win where a layer is latency-bound (batch <= 8); above that the three
+            # parts with the library's own all-reduce over peer memory in between (measured faster than NCCL's:
+            # Qwen3-32B batch 64 on 2 / 4 GPUs 318.7 / 231.6 us per layer against 329.8 / 243.9)
+            exchange = "fused" if B <= 8 else "peer"
         lay = tpm.TensorParallelDecodeLayer(B, S, H, I, NH, D, NKV, exchange=exchange)
-        launches_per_step = 6 if exchange == "fused" else 7
+        launches_per_step = 6 if exchange == "fused" else (10 if exchange == "peer" else 7)
 
         def layer(hidden, wset, out):
             return lay(hidden, *wset, out=out)
+
+        if args.exchange_only:
+            partial = torch.zeros(B, H, dtype=torch.float32, device=device)
+
+            def layer(hidden, wset, out):  # noqa: F811 - the layer's two sums over ranks and nothing else
+                if exchange == "peer":
+                    comm = lay._fused_comm(device)
+                    s = torch.cuda.current_stream().cuda_stream
+                    for which in (0, 1):
+                        _lib.check(_lib.load().ezb_tp_allreduce_f32(partial.data_ptr(), comm["bases"], tp, rank, which, B, H, s))
+                    return out
+                dist.all_reduce(partial)
+                dist.all_reduce(partial)
+                return out
 
     bufs = [torch.empty_like(hidden0) for _ in range(2)]
 
@@ -428,7 +447,7 @@ def main():
     got = layer(hidden0, (sets[0][0].clone(), sets[0][1].clone()) + sets[0][2:], torch.empty_like(hidden0))
     sync_all()
     check = None
-    if rank == 0:
+    if rank == 0 and not args.exchange_only:
         ref_set = sets[0] if tp == 1 else full0
         ref = ref_op._ref_forward(hidden0, ref_set[0].clone(), ref_set[1].clone(), *ref_set[2:])
         check = bool(ref_op.check(got, ref))
@@ -506,7 +525,14 @@ def main():
         dev_in, dev_out = torch.empty_like(hidden0), torch.empty_like(hidden0)
         stream = torch.cuda.current_stream()
 
+        # One GPU: the operator itself takes the pinned host buffers (copy in, layer, copy out as three kernels of
+        # one dependency chain, ezb_copy_pinned).  Tensor parallel: torch copies around the rank-local call.
+        host_io_by_op = tp == 1 and not args.stack
+
         def e2e_eager(i):
+            if host_io_by_op:
+                layer(host_in, sets[i % nsets], host_out)
+                return
             dev_in.copy_(host_in, non_blocking=True)
             layer(dev_in, sets[i % nsets], dev_out)
             host_out.copy_(dev_out, non_blocking=True)
@@ -552,9 +578,16 @@ def main():
         if world > 1:
             dist.all_reduce(e_ms, op=dist.ReduceOp.MAX)
         e_step = e_ms.item() / n_e2e
+        # the host-side result of an end-to-end step is the result of the same step issued on device tensors
+        e2e_step(0)
+        same = torch.empty_like(hidden0)
+        layer(hidden0, sets[0], same)
+        sync_all()
+        e2e_same = bool(torch.equal(host_out, same.cpu()))
         e2e = {"value": total_bytes / (e_step * 1e-3) / 1e9, "unit": UNIT, "us_per_step": e_step * 1e3, "steps": n_e2e,
-               "h2d_bytes_per_step": B * H * 2, "d2h_bytes_per_step": B * H * 2,
+               "h2d_bytes_per_step": B * H * 2, "d2h_bytes_per_step": B * H * 2, "result_equals_device_call": e2e_same,
                "launch": "one CUDA graph per step (copy in, operator call, copy out)" if e2e_graphs is not None else "eager",
+               "copies": "by the operator: pinned host tensors passed to the call (ezb_copy_pinned)" if host_io_by_op else "torch copy_ around the call",
                "note": "weights and KV cache are resident device state; per-step input/output cross PCIe"}
 
     peaks, peak_kind = measured_peaks()

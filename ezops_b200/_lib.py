@@ -66,6 +66,8 @@ SIGNATURES = {
     "ezb_qwen3_decode_layer_tp_attn": (c_int, [c_void_p] * 7 + [c_size_t] + [c_int] * 6 + [c_float, c_void_p]),
     "ezb_qwen3_decode_layer_tp_ffn": (c_int, [c_void_p] * 7 + [c_size_t] + [c_int] * 3 + [c_float, c_void_p]),
     "ezb_residual_add_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "ezb_copy_pinned": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p]),
+    "ezb_tp_allreduce_f32": (c_int, [c_void_p, POINTER(c_void_p), c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "ezb_attn_decode_paged": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t] + [c_int] * 7
                               + [c_void_p, c_void_p]),
     "ezb_qwen3_decode_stack_paged": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,

@@ -744,6 +744,35 @@ int ezb_qwen3_decode_layer_tp_ffn(const void* hidden, const float* summed_o, con
     return EZB_OK;
 }
 
+// The address a kernel uses for `p`: device memory as it is, pinned (page-locked, mapped) host memory through its
+// device alias; pageable host memory has none.
+static int device_view(const void* p, void** out, bool* is_host) {
+    cudaPointerAttributes at;
+    EZB_CUDA_TRY(cudaPointerGetAttributes(&at, p));
+    if (at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged) {
+        *out = const_cast<void*>(p), *is_host = false;
+        return EZB_OK;
+    }
+    if (at.type == cudaMemoryTypeHost && at.devicePointer) {
+        *out = at.devicePointer, *is_host = true;
+        return EZB_OK;
+    }
+    set_last_message("host buffers must be pinned (page-locked) memory: pageable memory has no device address");
+    return EZB_ERR_INVALID_ARGUMENT;
+}
+
+int ezb_copy_pinned(void* dst, const void* src, size_t bytes, ezb_stream_t stream) {
+    EZB_REQUIRE(dst && src && bytes >= 16 && bytes % 16 == 0, "null pointer, or a size that is not a positive multiple of 16");
+    EZB_REQUIRE(aligned16(dst) && aligned16(src), "pointers must be 16-byte aligned");
+    void *d = nullptr, *s = nullptr;
+    bool d_host = false, s_host = false;
+    if (int rc = device_view(dst, &d, &d_host)) return rc;
+    if (int rc = device_view(src, &s, &s_host)) return rc;
+    chain_begin();
+    EZB_CUDA_TRY(launch_pinned_copy(d, s, bytes, d_host, static_cast<cudaStream_t>(stream)));
+    return EZB_OK;
+}
+
 int ezb_vector_add_f32(const float* A, const float* B, float* C, long long n, ezb_stream_t stream) {
     EZB_REQUIRE(A && B && C && n >= 1, "null pointer or empty vector");
     EZB_CUDA_TRY(launch_vector_add_f32(A, B, C, n, static_cast<cudaStream_t>(stream)));
@@ -857,6 +886,18 @@ static int make_tp_link(TpLink& base, void* const* comm_bases_host, int world, i
         base.ctrl_peer[r] = static_cast<unsigned int*>(comm_bases_host[r]);
         base.inbox_peer[r] = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(comm_bases_host[r]) + kTpCtrlBytes);
     }
+    return EZB_OK;
+}
+
+int ezb_tp_allreduce_f32(void* buf, void* const* comm_bases_host, int world, int rank, int which, int B, int H,
+                         ezb_stream_t stream) {
+    EZB_REQUIRE(buf && aligned16(buf), "null or misaligned buffer");
+    EZB_REQUIRE(which == 0 || which == 1, "which must be 0 or 1");
+    EZB_REQUIRE(B >= 1 && H >= 1 && ((long long)B * H) % 4 == 0, "B * H must be a positive multiple of 4");
+    TpLink link;
+    if (int rc = make_tp_link(link, comm_bases_host, world, rank, B, H)) return rc;
+    chain_begin();
+    EZB_CUDA_TRY(launch_tp_allreduce(static_cast<float*>(buf), link, which, (long long)B * H, static_cast<cudaStream_t>(stream)));
     return EZB_OK;
 }
 

@@ -84,7 +84,7 @@ __device__ __forceinline__ bool tp_poisoned(const unsigned int* status) {
     return *reinterpret_cast<const volatile unsigned int*>(status) != 0u;
 }
 static constexpr int kTpEpoch = 0;
-static constexpr int kTpCtrlBytes = 256;
+static constexpr int kTpCtrlBytes = 256;  // epochs of the fused exchange [0..1], epochs and exit tickets of tp_allreduce.cu [2..5]
 static constexpr int kTpSlots = 8;
 
 __device__ __forceinline__ unsigned long long* tp_slot(const TpLink& l, int on_rank, int inbox, int slot) {

@@ -75,7 +75,9 @@ struct MegaParams {
     int nsp, sub_keys;
     int NS, l2_window;
     int inflight;  // stages that may be requested but not yet landed (0 = the whole ring)
-    int gate;      // 1: nothing behind this CTA's K/V stages is requested or prefetched before the QKV barrier has been passed
+    int gate;      // bit 0: nothing behind this CTA's K/V stages is requested or prefetched before the QKV barrier has been
+                   // passed; bit 1: no gate/up stage before the barrier behind o_proj; bit 2: no down stage before the
+                   // barrier behind gate/up
     unsigned int stage_bytes, act_bytes;
     long long wait_cycles;
     int evict_first;  // L2 evict-first policy on the streams: 1 = weights, 2 = weights and K/V
@@ -516,7 +518,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_layer_b1_kernel(const 
         }
         *abort_flag = 0;
         *cta_flag = 0;
-        *gate_open = p.gate ? 0 : 1;
+        *gate_open = 0;  // barriers passed by the consumers so far
         mbar_fence_init();
     }
     __syncthreads();
@@ -575,9 +577,11 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_layer_b1_kernel(const 
             ok = false;
         };
         for (int it = 0; it < total && ok; ++it) {
-            if (it >= s.e_att && !*gate_open) {
+            // barriers the consumers must have passed before stage `it` may be requested (0: none)
+            const int need = ((p.gate & 4) && it >= s.e_gu) ? 4 : ((p.gate & 2) && it >= s.e_o) ? 3 : ((p.gate & 1) && it >= s.e_att) ? 1 : 0;
+            if (*gate_open < need) {
                 const long long t0 = clock64();
-                while (!*gate_open && ok) {
+                while (*gate_open < need && ok) {
                     if (*abort_flag) ok = false;
                     else if (clock64() - t0 > p.wait_cycles) give_up(FAULT_GEMV_EMPTY_WAIT);
                 }
@@ -602,7 +606,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_layer_b1_kernel(const 
                         }
                         // The ring is full: keep HBM busy by pulling the stages behind it into L2.
                         if (pf < it) pf = it;
-                        if (*gate_open && pf < total && pf < it + p.l2_window) {
+                        if ((*gate_open || !(p.gate & 1)) && pf < total && pf < it + p.l2_window) {
                             issue(pf, true);
                             ++pf;
                             t0 = clock64();
@@ -975,6 +979,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_layer_b1_kernel(const 
     }
     trace_mark(trec, 5);
     mega_grid_barrier(p, c, MB_ATTN);
+    if (ct == 0) *gate_open = 2;
 
     // ================================================================ phase 2: output projection + residual
     trec = (ct == 0) ? trace_open(p.trace, 22u, cta_id) : nullptr;
@@ -1012,6 +1017,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_layer_b1_kernel(const 
     }
     trace_mark(trec, 5);
     mega_grid_barrier(p, c, MB_OPROJ);
+    if (ct == 0) *gate_open = 3;
 
     // ================================================================ phase 3: gate/up + SwiGLU
     trec = (ct == 0) ? trace_open(p.trace, 23u, cta_id) : nullptr;
@@ -1025,6 +1031,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_layer_b1_kernel(const 
                           trec, 33u);
     trace_mark(trec, 5);
     mega_grid_barrier(p, c, MB_GATEUP);
+    if (ct == 0) *gate_open = 4;
     // No CTA touches a barrier counter after this point.  The CTA that gets here last returns them to zero for the
     // next launch (which reads them only after this grid has finished); doing it now keeps it off the kernel's tail.
     if (ct == 0) {
@@ -1184,7 +1191,7 @@ cudaError_t launch_decode_mega(const MegaArgs& a, cudaStream_t stream) {
     p.evict_first = tuning(EZB_TUNE_STREAM_EVICT_FIRST);
     p.inflight = tuning(EZB_TUNE_MEGA_INFLIGHT);
     if (p.inflight < 0 || p.inflight >= p.NS) p.inflight = 0;
-    p.gate = tuning(EZB_TUNE_MEGA_GATE) ? 1 : 0;
+    p.gate = tuning(EZB_TUNE_MEGA_GATE) & 7;
     p.stage_bytes = (unsigned int)pl.stage_bytes, p.act_bytes = (unsigned int)pl.act_bytes;
     p.wait_cycles = wait_limit_cycles();
     p.status = status_ptr();

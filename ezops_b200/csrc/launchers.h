@@ -82,6 +82,11 @@ struct RowPrepArgs {
     TpLink link = {0, 0, {}, {}, 0, -1, -1, -1};  // gather_inbox >= 0: `add` is the sum of that inbox's slots
 };
 cudaError_t launch_row_prep(const RowPrepArgs& a, cudaStream_t stream);
+// In-place sum over ranks of a local fp32 buffer of n elements (n % 4 == 0, n <= link.slot_elems) through inbox
+// `which` of the ranks' communication buffers (tp_allreduce.cu).
+cudaError_t launch_tp_allreduce(float* buf, const TpLink& link, int which, long long n, cudaStream_t stream);
+// dst <- src, `bytes` a multiple of 16, both device-visible (device memory or the device alias of pinned host memory)
+cudaError_t launch_pinned_copy(void* dst, const void* src, size_t bytes, bool to_host, cudaStream_t stream);
 cudaError_t launch_rmsnorm_f32(const float* X, float* Out, int rows, int dim, float eps, cudaStream_t stream);
 
 struct RopeArgs {

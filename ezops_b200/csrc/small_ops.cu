@@ -109,6 +109,27 @@ __device__ __forceinline__ uint4 load_row8(const RowPrepParams& p, long long row
     return raw;
 }
 
+// Step input / output between pinned host memory and device memory, moved by a few CTAs instead of a copy engine:
+// as a kernel the copy is an ordinary link of a programmatic-dependent-launch chain (the layer behind a copy-in
+// starts streaming its weights while the input crosses PCIe; the copy-out is resident before the layer ends), and
+// a graph of {copy in, layer, copy out} needs no hand-over between the copy engines and the SMs.
+__global__ void __launch_bounds__(256) pinned_copy_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long long n16,
+                                                          int to_host) {
+    pdl_trigger();
+    pdl_wait();  // src may be what the kernel in front wrote; dst may be what it still reads
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (long long)gridDim.x * blockDim.x) dst[i] = src[i];
+    if (to_host) __threadfence_system();
+}
+
+cudaError_t launch_pinned_copy(void* dst, const void* src, size_t bytes, bool to_host, cudaStream_t stream) {
+    const long long n16 = (long long)(bytes / 16);
+    int grid = (int)((n16 + 255) / 256);
+    if (grid > 16) grid = 16;  // a step's activations are a few KB to a few hundred KB; PCIe is the limit, not SMs
+    if (grid < 1) grid = 1;
+    return launch_pdl(pinned_copy_kernel, dim3(grid), dim3(256), 0, stream, static_cast<const uint4*>(src), static_cast<uint4*>(dst),
+                      n16, to_host ? 1 : 0);
+}
+
 __global__ void __launch_bounds__(kRowThreads) row_prep_kernel(const RowPrepParams p) {
     __shared__ float scratch[8];
     pdl_trigger();

@@ -257,9 +257,32 @@ class Qwen3DenseDecodeSm100Kernel(BaseKernel):
             self._ws = _zeros_bytes(need, device)
         return self._ws
 
+    def _host_step(self, hidden, K_cache, V_cache, Wqkv, Wo, Wgu, Wd, out):
+        """The step's input and result live in PINNED host memory: copy in, layer, copy out as three kernels of one
+        dependency chain on the current stream (``ezb_copy_pinned``).  ``out`` is valid once the stream is
+        synchronised."""
+        if not hidden.is_pinned() or hidden.dtype != _BF16 or tuple(hidden.shape) != (self.B, self.H) or not hidden.is_contiguous():
+            raise ValueError(f"a host `hidden` must be a pinned contiguous bf16 tensor of shape {(self.B, self.H)}")
+        if out is None:
+            out = torch.empty_like(hidden).pin_memory()
+        if out.is_cuda or not out.is_pinned() or out.dtype != _BF16 or tuple(out.shape) != (self.B, self.H) or not out.is_contiguous():
+            raise ValueError("with a host `hidden`, `out` must be a pinned contiguous bf16 host tensor of the same shape")
+        dev = K_cache.device
+        if getattr(self, "_io", None) is None or self._io[0].device != dev:
+            self._io = (torch.empty(self.B, self.H, dtype=_BF16, device=dev), torch.empty(self.B, self.H, dtype=_BF16, device=dev))
+        d_in, d_out = self._io
+        nbytes = self.B * self.H * 2
+        _lib.check(self._lib.ezb_copy_pinned(d_in.data_ptr(), hidden.data_ptr(), nbytes, _stream()))
+        self(d_in, K_cache, V_cache, Wqkv, Wo, Wgu, Wd, out=d_out)
+        _lib.check(self._lib.ezb_copy_pinned(out.data_ptr(), d_out.data_ptr(), nbytes, _stream()))
+        return out
+
     def __call__(self, hidden, K_cache, V_cache, Wqkv, Wo, Wgu, Wd, out=None):
-        """``out`` (optional) receives the result in place."""
+        """``out`` (optional) receives the result in place.  ``hidden`` (and then ``out``) may be pinned host
+        tensors: see ``_host_step``."""
         B, S, H, I, NH, NKV, D = self.B, self.S, self.H, self.I, self.NH, self.NKV, self.D
+        if not hidden.is_cuda:
+            return self._host_step(hidden, K_cache, V_cache, Wqkv, Wo, Wgu, Wd, out)
         _require(hidden, "hidden", (B, H))
         _require(K_cache, "K_cache", (B, NKV, S, D)); _require(V_cache, "V_cache", (B, NKV, S, D))
         _require(Wqkv, "Wqkv", ((NH + 2 * NKV) * D, H)); _require(Wo, "Wo", (H, NH * D))

@@ -64,8 +64,8 @@ class TensorParallelDecodeLayer:
 
     def __init__(self, batch, seq_len, hidden_size, intermediate_size, num_heads, head_dim, num_kv_heads, group=None,
                  exchange: str = "nccl"):
-        if exchange not in ("nccl", "fused"):
-            raise ValueError(f"exchange must be 'nccl' or 'fused', got {exchange!r}")
+        if exchange not in ("nccl", "fused", "peer"):
+            raise ValueError(f"exchange must be 'nccl', 'fused' or 'peer', got {exchange!r}")
         self.exchange = exchange
         self._comm = None
         self.group = group
@@ -96,27 +96,44 @@ class TensorParallelDecodeLayer:
         return self._bufs
 
     # -- the three local parts (C ABI) and the exchange in between ------------
-    def _part_attn(self, hidden, K_l, V_l, Wqkv_l, Wo_l, bufs):
+    # ``po`` / ``so`` / ``pd`` / ``sd``: device addresses of the o_proj partial and its sum over ranks, and of the
+    # down partial and its sum; by default the buffers of ``bufs``, where NCCL sums a partial in place
+    def _part_attn(self, hidden, K_l, V_l, Wqkv_l, Wo_l, bufs, po=None):
         lib = _lib.load()
+        po = bufs["partial_o"].data_ptr() if po is None else po
         s = torch.cuda.current_stream().cuda_stream
         _lib.check(lib.ezb_qwen3_decode_layer_tp_attn(
             hidden.data_ptr(), K_l.data_ptr(), V_l.data_ptr(), Wqkv_l.data_ptr(), Wo_l.data_ptr(),
-            bufs["partial_o"].data_ptr(), bufs["ws1"].data_ptr(), bufs["ws1"].numel(),
+            po, bufs["ws1"].data_ptr(), bufs["ws1"].numel(),
             self.B, self.S, self.H, self.NH_l, self.NKV_l, self.D, self.rms_eps, s))
 
-    def _part_ffn(self, hidden, Wgu_l, Wd_l, bufs):
+    def _part_ffn(self, hidden, Wgu_l, Wd_l, bufs, so=None, pd=None):
         lib = _lib.load()
+        so = bufs["partial_o"].data_ptr() if so is None else so
+        pd = bufs["partial_d"].data_ptr() if pd is None else pd
         s = torch.cuda.current_stream().cuda_stream
         _lib.check(lib.ezb_qwen3_decode_layer_tp_ffn(
-            hidden.data_ptr(), bufs["partial_o"].data_ptr(), Wgu_l.data_ptr(), Wd_l.data_ptr(), bufs["x2"].data_ptr(),
-            bufs["partial_d"].data_ptr(), bufs["ws2"].data_ptr(), bufs["ws2"].numel(),
+            hidden.data_ptr(), so, Wgu_l.data_ptr(), Wd_l.data_ptr(), bufs["x2"].data_ptr(),
+            pd, bufs["ws2"].data_ptr(), bufs["ws2"].numel(),
             self.B, self.H, self.I_l, self.rms_eps, s))
 
-    def _part_out(self, out, bufs):
+    def _part_out(self, out, bufs, sd=None):
         lib = _lib.load()
+        sd = bufs["partial_d"].data_ptr() if sd is None else sd
         s = torch.cuda.current_stream().cuda_stream
-        _lib.check(lib.ezb_residual_add_f32(bufs["x2"].data_ptr(), bufs["partial_d"].data_ptr(), out.data_ptr(),
-                                            self.B, self.H, s))
+        _lib.check(lib.ezb_residual_add_f32(bufs["x2"].data_ptr(), sd, out.data_ptr(), self.B, self.H, s))
+
+    def _call_peer(self, hidden, K_l, V_l, Wqkv_l, Wo_l, Wgu_l, Wd_l, out, bufs):
+        """The three parts with this library's own in-place sum over ranks in between (``ezb_tp_allreduce_f32``:
+        two-shot over peer memory, epoch-tagged cells) instead of NCCL's all-reduce."""
+        lib = _lib.load()
+        comm = self._fused_comm(hidden.device)
+        s = torch.cuda.current_stream().cuda_stream
+        self._part_attn(hidden, K_l, V_l, Wqkv_l, Wo_l, bufs)
+        _lib.check(lib.ezb_tp_allreduce_f32(bufs["partial_o"].data_ptr(), comm["bases"], self.tp, self.rank, 0, self.B, self.H, s))
+        self._part_ffn(hidden, Wgu_l, Wd_l, bufs)
+        _lib.check(lib.ezb_tp_allreduce_f32(bufs["partial_d"].data_ptr(), comm["bases"], self.tp, self.rank, 1, self.B, self.H, s))
+        self._part_out(out, bufs)
 
     def _sum_over_ranks(self, t: torch.Tensor) -> None:
         if self.tp > 1:
@@ -181,6 +198,9 @@ class TensorParallelDecodeLayer:
             out = torch.empty_like(hidden)
         if self.exchange == "fused":
             self._call_fused(hidden, K_local, V_local, Wqkv_l, Wo_l, Wgu_l, Wd_l, out, bufs)
+            return out
+        if self.exchange == "peer":
+            self._call_peer(hidden, K_local, V_local, Wqkv_l, Wo_l, Wgu_l, Wd_l, out, bufs)
             return out
         self._part_attn(hidden, K_local, V_local, Wqkv_l, Wo_l, bufs)
         self._sum_over_ranks(bufs["partial_o"])

@@ -71,7 +71,7 @@ typedef struct CUstream_st* ezb_stream_t; /* same type as cudaStream_t */
 #define EZB_TUNE_WAIT_LIMIT_MS 19     /* budget of one device-side wait in the single-kernel layer and the cross-rank waits, ms at 2 GHz (default 1000) */
 #define EZB_TUNE_MEGA_STAGES 20       /* single-kernel layer: cap on the ring depth (0 = as many as fit)                            */
 #define EZB_TUNE_MEGA_INFLIGHT 21     /* single-kernel layer: stages that may be requested but not yet landed (0 = whole ring; default 2) */
-#define EZB_TUNE_MEGA_GATE 22         /* single-kernel layer: 1 = a producer stops behind its K/V stages until the QKV barrier is passed */
+#define EZB_TUNE_MEGA_GATE 22         /* single-kernel layer, bit mask: a producer stops 1 = behind its K/V stages until the QKV barrier is passed (default), 2 = behind Wo until the barrier after o_proj, 4 = behind gate/up until the barrier after it */
 #define EZB_TUNE_TP_WAIT_LIMIT_MS 23   /* fused exchange: budget of one wait for the peers' partial sums, ms at 2 GHz (default 5000)      */
 #define EZB_TUNE_TP_STRONG_STORES 24   /* fused exchange: 1 = publish cells with st.relaxed.sys instead of plain stores (default 0) */
 #define EZB_TUNE_STREAM_EVICT_FIRST 25 /* weight streams carry the L2 evict-first policy: 0 = off, 1 = weights (default), 2 = also K/V in the single-kernel layer */
@@ -258,6 +258,16 @@ int ezb_qwen3_decode_stack(const void* hidden, void* out, const ezb_layer_t* lay
  * by the last CTA to finish, so two calls give the same bits; the workspace
  * (ezb_reduce_workspace_bytes(), zero-filled once) holds the partials. */
 int ezb_vector_add_f32(const float* A, const float* B, float* C, long long n, ezb_stream_t stream);
+
+/* Host buffers at the boundary.  The reference's operators take the step's tensors where the caller has them
+ * (ezops/ops/base.py forward(*args)); a host application holds a decode step's input and result in host memory.
+ * ezb_copy_pinned moves `bytes` (a positive multiple of 16, both pointers 16-byte aligned) between PINNED host
+ * memory and device memory - either direction, or device to device - with a small kernel instead of a copy engine,
+ * so that {copy in, ezb_qwen3_decode_layer, copy out} on one stream is one programmatic-dependent-launch chain (and
+ * one CUDA graph without engine hand-overs): the layer streams its weights while the input crosses PCIe.  Pageable
+ * host memory is refused with EZB_ERR_INVALID_ARGUMENT (it has no device address).  The host may read a copied-out
+ * buffer after synchronising the stream.  No counterpart in the reference (its benchmarks keep tensors on the GPU). */
+int ezb_copy_pinned(void* dst, const void* src, size_t bytes, ezb_stream_t stream);
 int ezb_softmax_f32(const float* X, float* Out, int rows, int dim, ezb_stream_t stream);
 size_t ezb_reduce_workspace_bytes(void);
 int ezb_reduce_sum_f32(const float* A, float* Out, long long n, void* workspace, size_t workspace_bytes, ezb_stream_t stream);
@@ -340,6 +350,17 @@ int ezb_hbm_stream(int op, const void* b, const void* c, void* a, long long n_ve
  * neither covers return EZB_ERR_UNSUPPORTED_SHAPE (use the three-part form with
  * NCCL then). */
 size_t ezb_tp_comm_bytes(int B, int H);
+
+/* The sum over ranks between the three local parts as a kernel of this library instead of an NCCL all-reduce (no
+ * counterpart in the reference): buf (device, fp32 [B, H], 16-byte aligned) is summed IN PLACE over the ranks, in
+ * rank order, identical bits on every rank.  Uses the communication buffers of the fused exchange (same
+ * ezb_tp_comm_bytes(B, H), same mapping) and its epoch-tagged cells: two-shot (every rank sums the slice of elements
+ * it owns and hands the result to the others), 64 CTAs, plain peer stores, polls of local memory only, no flag and no
+ * fence.  Every rank calls it on its stream behind the part that wrote the partial; when the kernel has finished,
+ * buf holds the sum.  Ranks must make the same sequence of calls and alternate `which` (0: the sum after o_proj, 1:
+ * the sum after down); B * H a multiple of 4; waits are bounded (EZB_TUNE_TP_WAIT_LIMIT_MS, then fault 0x201). */
+int ezb_tp_allreduce_f32(void* buf, void* const* comm_bases_host, int world, int rank, int which, int B, int H,
+                         ezb_stream_t stream);
 int ezb_tp_comm_alloc(size_t bytes, void** out_host);
 int ezb_tp_comm_free(void* buffer);
 int ezb_ipc_export(void* buffer, void* handle64_host);

@@ -834,3 +834,78 @@ def test_fused_exchange_wait_runs_out_and_poisons_the_chain(ez):
     finally:
         torch.cuda.synchronize()
         _lib.check(lib.ezb_tp_comm_free(bufs[0]))
+
+
+# ------------------------------------------------ host buffers at the boundary ---
+@pytest.mark.parametrize("batch", [1, 5])
+def test_layer_takes_pinned_host_buffers(ez, batch):
+    """A host application holds the step's input and result in pinned host memory: the operator copies in, runs
+    the layer and copies out as one chain on the stream (ezb_copy_pinned); the result equals the device call bit for
+    bit, also when the three calls are replayed from a CUDA graph, and pageable memory is refused."""
+    from ezops_b200 import _lib
+    from ezops_b200 import workloads as wl
+
+    sh, S = wl.QWEN3_0_6B, 300
+    data = wl.decode_layer_inputs(sh, batch, S)
+    hidden, rest = data[0], dev(*data[1:])
+    op = ez.Qwen3DenseDecodeOp(batch, S, sh.hidden, sh.inter, sh.num_heads, sh.head_dim, backend="cuda", num_kv_heads=sh.num_kv_heads)
+    want = op(hidden.cuda(), *rest).cpu()
+    h_in, h_out = hidden.clone().pin_memory(), torch.zeros_like(hidden).pin_memory()
+    got = op._kernel(h_in, *rest, out=h_out)
+    torch.cuda.synchronize()
+    assert got is h_out and torch.equal(h_out, want)
+    # the same three calls from a graph, with a new input written by the host between replays
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            op._kernel(h_in, *rest, out=h_out)
+    for scale in (0.5, 2.0):
+        h_in.copy_((hidden.float() * scale).to(torch.bfloat16))
+        want = op(h_in.cuda(), *rest).cpu()
+        h_out.zero_()
+        g.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(h_out, want)
+    # pageable host memory has no device address: refused, nothing launched
+    lib = _lib.load()
+    pageable = torch.zeros(batch, sh.hidden, dtype=torch.bfloat16)
+    rc = lib.ezb_copy_pinned(rest[0].data_ptr(), pageable.data_ptr(), pageable.numel() * 2, torch.cuda.current_stream().cuda_stream)
+    assert rc == _lib.EZB_ERR_INVALID_ARGUMENT
+    assert b"pinned" in lib.ezb_last_error_message()
+    with pytest.raises(ValueError, match="pinned"):
+        op._kernel(pageable, *rest)
+
+
+@pytest.mark.parametrize("batch", [1, 4, 16, 40])
+def test_tp_peer_allreduce_world_one_matches_the_three_part_form(ez, batch):
+    """The library's own sum over ranks (ezb_tp_allreduce_f32) with one rank: the partial goes through the
+    communication buffer and comes back unchanged, so the layer equals the three-part form bit for bit, call after
+    call (the flags' epochs advance) and from a CUDA graph."""
+    from ezops_b200 import _lib
+    from ezops_b200 import tp as tpm
+    from ezops_b200 import workloads as wl
+
+    sh, S = wl.QWEN3_VL_2B, 333
+    data = dev(*wl.decode_layer_inputs(sh, batch, S))
+    args = (batch, S, sh.hidden, sh.inter, sh.num_heads, sh.head_dim, sh.num_kv_heads)
+    want = tpm.TensorParallelDecodeLayer(*args)(*data)
+    lay = tpm.TensorParallelDecodeLayer(*args, exchange="peer")
+    try:
+        for _ in range(3):
+            assert torch.equal(lay(*data), want)
+        out = torch.empty_like(want)
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                lay(*data, out=out)
+        for _ in range(3):
+            out.zero_()
+            g.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(out, want)
+        assert _lib.device_status() == 0
+    finally:
+        torch.cuda.synchronize()
+        lay.close()

@@ -103,3 +103,14 @@ def test_per_operator_benchmark_scripts_keep_the_reference_command_line():
     res = subprocess.run([sys.executable, str(bench_dir / "bench_gemv.py"), "-k", "triton"], capture_output=True, text=True, timeout=120,
                          cwd=str(bench_dir))
     assert "Unknown backends: triton" in res.stdout and "Available: cuda" in res.stdout
+
+
+def test_gemv_timeline_script_parses_its_command_line_without_a_gpu():
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    script = Path(__file__).resolve().parent.parent / "benchmarks" / "gemv_isolated_timeline.py"
+    res = subprocess.run([sys.executable, str(script), "--help"], capture_output=True, text=True, timeout=180)
+    assert res.returncode == 0, res.stderr[-500:]
+    assert "--rows" in res.stdout and "--launches" in res.stdout
