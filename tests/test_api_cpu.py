@@ -84,6 +84,17 @@ def test_c_abi_rejects_bad_arguments_without_a_gpu():
         _lib.check(_lib.EZB_ERR_WORKSPACE)
     assert lib.ezb_qwen3_decode_layer_workspace_bytes(1, 4096, 4096, 12288, 32, 8, 128) > 0
     assert lib.ezb_set_tuning(99, 1) == _lib.EZB_ERR_INVALID_ARGUMENT
+    # host-buffer copy: sizes and alignment are checked before any CUDA call
+    assert lib.ezb_copy_pinned(None, fake, 64, None) == _lib.EZB_ERR_INVALID_ARGUMENT
+    assert lib.ezb_copy_pinned(fake, fake, 24, None) == _lib.EZB_ERR_INVALID_ARGUMENT  # not a multiple of 16
+    assert lib.ezb_copy_pinned(fake, odd, 64, None) == _lib.EZB_ERR_INVALID_ARGUMENT
+    # the library's all-reduce: buffer, exchange index, size and the ranks' buffers are checked before any launch
+    bases = (ctypes.c_void_p * 2)(0x2000, 0x4000)
+    assert lib.ezb_tp_allreduce_f32(None, bases, 2, 0, 0, 4, 64, None) == _lib.EZB_ERR_INVALID_ARGUMENT
+    assert lib.ezb_tp_allreduce_f32(fake, bases, 2, 0, 2, 4, 64, None) == _lib.EZB_ERR_INVALID_ARGUMENT  # which must be 0 or 1
+    assert lib.ezb_tp_allreduce_f32(fake, bases, 2, 0, 0, 1, 6, None) == _lib.EZB_ERR_INVALID_ARGUMENT   # B * H % 4
+    assert lib.ezb_tp_allreduce_f32(fake, bases, 2, 2, 0, 4, 64, None) == _lib.EZB_ERR_INVALID_ARGUMENT  # rank outside the world
+    assert lib.ezb_tp_allreduce_f32(fake, bases, 9, 0, 0, 4, 64, None) == _lib.EZB_ERR_INVALID_ARGUMENT  # more than 8 ranks
 
 
 def test_constructor_validation_matches_the_reference_contract():

@@ -97,6 +97,17 @@ def test_two_rank_tensor_parallel_layer_on_gloo(tmp_path):
         assert float(err) < 1e-2 and same == "1"
 
 
+def test_exchange_names_are_checked():
+    import pytest
+
+    from ezops_b200 import tp as tpm
+
+    for name in ("nccl", "fused", "peer"):
+        assert tpm.TensorParallelDecodeLayer(1, 64, 256, 512, 4, 64, 2, exchange=name).exchange == name
+    with pytest.raises(ValueError, match="exchange"):
+        tpm.TensorParallelDecodeLayer(1, 64, 256, 512, 4, 64, 2, exchange="mpi")
+
+
 def test_shard_shapes_and_errors():
     sys.path.insert(0, str(ROOT))
     import pytest
