@@ -525,8 +525,9 @@ def main():
         dev_in, dev_out = torch.empty_like(hidden0), torch.empty_like(hidden0)
         stream = torch.cuda.current_stream()
 
-        # One GPU: the operator itself takes the pinned host buffers (copy in, layer, copy out as three kernels of
-        # one dependency chain, ezb_copy_pinned).  Tensor parallel: torch copies around the rank-local call.
+        # One GPU: the operator itself takes the pinned host buffers (a copy-in kernel, ezb_copy_pinned, and the layer
+        # as one dependency chain; the layer's last kernel stores the result into the pinned buffer).  Tensor
+        # parallel: torch copies around the rank-local call.
         host_io_by_op = tp == 1 and not args.stack
 
         def e2e_eager(i):
@@ -587,7 +588,8 @@ def main():
         e2e = {"value": total_bytes / (e_step * 1e-3) / 1e9, "unit": UNIT, "us_per_step": e_step * 1e3, "steps": n_e2e,
                "h2d_bytes_per_step": B * H * 2, "d2h_bytes_per_step": B * H * 2, "result_equals_device_call": e2e_same,
                "launch": "one CUDA graph per step (copy in, operator call, copy out)" if e2e_graphs is not None else "eager",
-               "copies": "by the operator: pinned host tensors passed to the call (ezb_copy_pinned)" if host_io_by_op else "torch copy_ around the call",
+               "copies": ("by the operator: pinned host tensors passed to the call (copy-in kernel ezb_copy_pinned; the layer's last "
+                          "kernel stores the result into the pinned buffer)") if host_io_by_op else "torch copy_ around the call",
                "note": "weights and KV cache are resident device state; per-step input/output cross PCIe"}
 
     peaks, peak_kind = measured_peaks()

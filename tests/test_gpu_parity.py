@@ -837,8 +837,9 @@ def test_fused_exchange_wait_runs_out_and_poisons_the_chain(ez):
 
 
 # ------------------------------------------------ host buffers at the boundary ---
+@pytest.mark.parametrize("direct", [True, False])
 @pytest.mark.parametrize("batch", [1, 5])
-def test_layer_takes_pinned_host_buffers(ez, batch):
+def test_layer_takes_pinned_host_buffers(ez, batch, direct):
     """A host application holds the step's input and result in pinned host memory: the operator copies in, runs
     the layer and copies out as one chain on the stream (ezb_copy_pinned); the result equals the device call bit for
     bit, also when the three calls are replayed from a CUDA graph, and pageable memory is refused."""
@@ -849,6 +850,7 @@ def test_layer_takes_pinned_host_buffers(ez, batch):
     data = wl.decode_layer_inputs(sh, batch, S)
     hidden, rest = data[0], dev(*data[1:])
     op = ez.Qwen3DenseDecodeOp(batch, S, sh.hidden, sh.inter, sh.num_heads, sh.head_dim, backend="cuda", num_kv_heads=sh.num_kv_heads)
+    op._kernel.direct_host_output = direct  # the last kernel stores into the host buffer | a copy-out kernel does
     want = op(hidden.cuda(), *rest).cpu()
     h_in, h_out = hidden.clone().pin_memory(), torch.zeros_like(hidden).pin_memory()
     got = op._kernel(h_in, *rest, out=h_out)
