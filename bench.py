@@ -534,6 +534,12 @@ def main():
             if host_io_by_op:
                 layer(host_in, sets[i % nsets], host_out)
                 return
+            if tp > 1:
+                # the same two steps through the C ABI: a copy-in kernel, then the rank-local call with the pinned
+                # result buffer as its output (device-addressable: the last kernel stores into it)
+                _lib.check(lib_.ezb_copy_pinned(dev_in.data_ptr(), host_in.data_ptr(), B * H * 2, torch.cuda.current_stream().cuda_stream))
+                layer(dev_in, sets[i % nsets], host_out)
+                return
             dev_in.copy_(host_in, non_blocking=True)
             layer(dev_in, sets[i % nsets], dev_out)
             host_out.copy_(dev_out, non_blocking=True)
@@ -589,7 +595,9 @@ def main():
                "h2d_bytes_per_step": B * H * 2, "d2h_bytes_per_step": B * H * 2, "result_equals_device_call": e2e_same,
                "launch": "one CUDA graph per step (copy in, operator call, copy out)" if e2e_graphs is not None else "eager",
                "copies": ("by the operator: pinned host tensors passed to the call (copy-in kernel ezb_copy_pinned; the layer's last "
-                          "kernel stores the result into the pinned buffer)") if host_io_by_op else "torch copy_ around the call",
+                          "kernel stores the result into the pinned buffer)") if host_io_by_op else
+                         ("copy-in kernel ezb_copy_pinned, then the rank-local call with the pinned result buffer as its output" if tp > 1
+                          else "torch copy_ around the call"),
                "note": "weights and KV cache are resident device state; per-step input/output cross PCIe"}
 
     peaks, peak_kind = measured_peaks()
