@@ -214,53 +214,72 @@ __global__ void __launch_bounds__(128) qk_norm_rope_kernel(const RopeParams p) {
     const int b = unit / heads, hh = unit - b * heads;
     const bool is_q = hh < p.NQ;
     const int h = is_q ? hh : hh - p.NQ;
-    const int pos = p.positions ? p.positions[b] : p.position;
+    const int half = p.D / 2;
+    const bf16* in = is_q ? p.q + ((long long)b * p.NQ + h) * p.D : p.k + ((long long)b * p.NKV + h) * p.D;
+    const bf16* w = is_q ? p.qw : p.kw;
+    const bf16* vin = is_q ? nullptr : p.v + ((long long)b * p.NKV + h) * p.D;
+
+    // The kernel is a chain of memory latencies, not bytes.  Everything that does not depend on the token's position
+    // (the head, its norm weights, the v row) is requested together with the position itself; only the rotary
+    // table rows wait for it: two dependent round trips instead of three.
+    const int pos = p.positions ? __ldg(p.positions + b) : p.position;
+    float x1[kRopeMaxPairsPerLane], x2[kRopeMaxPairsPerLane], w1[kRopeMaxPairsPerLane], w2[kRopeMaxPairsPerLane];
+    bf16 v1[kRopeMaxPairsPerLane], v2[kRopeMaxPairsPerLane];
+#pragma unroll
+    for (int j = 0; j < kRopeMaxPairsPerLane; ++j) {
+        const int i = lane + j * 32;
+        x1[j] = x2[j] = w1[j] = w2[j] = 0.f;
+        v1[j] = v2[j] = __float2bfloat16_rn(0.f);
+        if (i < half) {
+            x1[j] = __bfloat162float(in[i]);
+            x2[j] = __bfloat162float(in[i + half]);
+            w1[j] = __bfloat162float(__ldg(w + i));
+            w2[j] = __bfloat162float(__ldg(w + i + half));
+            if (!is_q) v1[j] = vin[i], v2[j] = vin[i + half];
+        }
+    }
     if (pos < 0 || pos >= p.S) {
         if (lane == 0) report_fault(p.status, 0x301u);
         return;
     }
-    const int half = p.D / 2;
-    const bf16* in = is_q ? p.q + ((long long)b * p.NQ + h) * p.D : p.k + ((long long)b * p.NKV + h) * p.D;
-    const bf16* w = is_q ? p.qw : p.kw;
     const bf16* c = p.cos + (long long)pos * p.D;
     const bf16* s = p.sin + (long long)pos * p.D;
-
-    float x1[kRopeMaxPairsPerLane], x2[kRopeMaxPairsPerLane];
-    float ssq = 0.f;
+    float c1[kRopeMaxPairsPerLane], c2[kRopeMaxPairsPerLane], s1[kRopeMaxPairsPerLane], s2[kRopeMaxPairsPerLane];
 #pragma unroll
     for (int j = 0; j < kRopeMaxPairsPerLane; ++j) {
         const int i = lane + j * 32;
-        x1[j] = x2[j] = 0.f;
+        c1[j] = c2[j] = s1[j] = s2[j] = 0.f;
         if (i < half) {
-            x1[j] = __bfloat162float(in[i]);
-            x2[j] = __bfloat162float(in[i + half]);
-            ssq = __fadd_rn(ssq, __fadd_rn(__fmul_rn(x1[j], x1[j]), __fmul_rn(x2[j], x2[j])));
+            c1[j] = __bfloat162float(__ldg(c + i)), c2[j] = __bfloat162float(__ldg(c + i + half));
+            s1[j] = __bfloat162float(__ldg(s + i)), s2[j] = __bfloat162float(__ldg(s + i + half));
         }
     }
+    float ssq = 0.f;
+#pragma unroll
+    for (int j = 0; j < kRopeMaxPairsPerLane; ++j)
+        if (lane + j * 32 < half) ssq = __fadd_rn(ssq, __fadd_rn(__fmul_rn(x1[j], x1[j]), __fmul_rn(x2[j], x2[j])));
     ssq = warp_sum(ssq);
     const float r = 1.0f / sqrtf(__fadd_rn(ssq / (float)p.D, p.eps));
 
     bf16* out = is_q ? p.q_out + ((long long)b * p.NQ + h) * p.D : p.k_out + ((long long)b * p.NKV + h) * p.D;
     bf16* kslot = is_q ? nullptr : p.K_cache + (((long long)b * p.NKV + h) * p.S + pos) * p.D;
     bf16* vslot = is_q ? nullptr : p.V_cache + (((long long)b * p.NKV + h) * p.S + pos) * p.D;
-    const bf16* vin = is_q ? nullptr : p.v + ((long long)b * p.NKV + h) * p.D;
 #pragma unroll
     for (int j = 0; j < kRopeMaxPairsPerLane; ++j) {
         const int i = lane + j * 32;
         if (i < half) {
-            const float n1 = __fmul_rn(__fmul_rn(x1[j], r), __bfloat162float(w[i]));
-            const float n2 = __fmul_rn(__fmul_rn(x2[j], r), __bfloat162float(w[i + half]));
-            const float o1 = __fadd_rn(__fmul_rn(n1, __bfloat162float(c[i])), __fmul_rn(-n2, __bfloat162float(s[i])));
-            const float o2 =
-                __fadd_rn(__fmul_rn(n2, __bfloat162float(c[i + half])), __fmul_rn(n1, __bfloat162float(s[i + half])));
+            const float n1 = __fmul_rn(__fmul_rn(x1[j], r), w1[j]);
+            const float n2 = __fmul_rn(__fmul_rn(x2[j], r), w2[j]);
+            const float o1 = __fadd_rn(__fmul_rn(n1, c1[j]), __fmul_rn(-n2, s1[j]));
+            const float o2 = __fadd_rn(__fmul_rn(n2, c2[j]), __fmul_rn(n1, s2[j]));
             const bf16 r1 = __float2bfloat16_rn(o1), r2 = __float2bfloat16_rn(o2);
             out[i] = r1;
             out[i + half] = r2;
             if (!is_q) {
                 kslot[i] = r1;
                 kslot[i + half] = r2;
-                vslot[i] = vin[i];
-                vslot[i + half] = vin[i + half];
+                vslot[i] = v1[j];
+                vslot[i + half] = v2[j];
             }
         }
     }
