@@ -911,3 +911,62 @@ def test_tp_peer_allreduce_world_one_matches_the_three_part_form(ez, batch):
     finally:
         torch.cuda.synchronize()
         lay.close()
+
+
+def test_peer_allreduce_wait_runs_out_and_leaves_the_buffer_alone(ez):
+    """The library's all-reduce with a peer that never delivers (a world of two, both communication buffers on this
+    GPU, nobody playing rank 1, budget 2 ms): the kernel returns, the status word reads 0x201, the buffer still
+    holds the rank's own partial, a second call while the fault stands returns at once, and after clearing the word
+    a world-of-one call is healthy (the sum of one rank is the partial itself)."""
+    import ctypes
+
+    from ezops_b200 import _lib
+
+    lib = _lib.load()
+    B, H = 16, 2048
+    nbytes = lib.ezb_tp_comm_bytes(B, H)
+    bufs = [ctypes.c_void_p(), ctypes.c_void_p()]
+    for b in bufs:
+        _lib.check(lib.ezb_tp_comm_alloc(nbytes, ctypes.byref(b)))
+    part = torch.randn(B, H, device="cuda")
+    keep = part.clone()
+    s = torch.cuda.current_stream().cuda_stream
+
+    def call(world, which):
+        bases = (ctypes.c_void_p * world)(*[b.value for b in bufs[:world]])
+        return lib.ezb_tp_allreduce_f32(part.data_ptr(), bases, world, 0, which, B, H, s)
+
+    try:
+        _lib.set_tuning(tp_wait_limit_ms=2)
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        assert call(2, 0) == _lib.EZB_OK  # the call only enqueues; the fault is found on the device
+        t1.record()
+        torch.cuda.synchronize()
+        assert t0.elapsed_time(t1) < 500.0
+        word = ctypes.c_uint(0)
+        assert lib.ezb_device_status(ctypes.byref(word), 0) == _lib.EZB_ERR_DEVICE_FAULT and word.value == 0x201
+        assert torch.equal(part, keep), "a rank that gave up must not publish a sum"
+        t0.record()
+        assert call(2, 1) == _lib.EZB_OK  # poisoned: returns at once
+        t1.record()
+        torch.cuda.synchronize()
+        assert t0.elapsed_time(t1) < 50.0 and torch.equal(part, keep)
+        assert _lib.device_status() == 0x201  # reads and clears
+    finally:
+        _lib.set_tuning(tp_wait_limit_ms=5000)
+        torch.cuda.synchronize()
+        _lib.device_status()
+        for b in bufs:
+            _lib.check(lib.ezb_tp_comm_free(b))
+    one = ctypes.c_void_p()
+    _lib.check(lib.ezb_tp_comm_alloc(nbytes, ctypes.byref(one)))
+    bufs = [one]
+    try:
+        for which in (0, 1, 0):
+            assert call(1, which) == _lib.EZB_OK
+        torch.cuda.synchronize()
+        assert _lib.device_status() == 0 and torch.equal(part, keep)
+    finally:
+        torch.cuda.synchronize()
+        _lib.check(lib.ezb_tp_comm_free(one))
