@@ -21,7 +21,8 @@
 // exchange on two GPUs (NCCL: 27 alone, but faster than that inside the layer), a fence per polling thread 43 us.
 // A rank can overwrite a peer's cells only after the peer has consumed them: the other exchange of the layer, in
 // which every rank needs every other rank's cells, lies in between (ranks make the same sequence of calls, which
-// alternates `which`).  Every wait is bounded (EZB_TUNE_TP_WAIT_LIMIT_MS); one that runs out records
+// alternates `which`).  The epochs are this kernel's own words of the control block, so a communication buffer must
+// not be shared with the fused exchange (a cell left by one could carry the tag the other waits for).  Every wait is bounded (EZB_TUNE_TP_WAIT_LIMIT_MS); one that runs out records
 // FAULT_AR_FLAG_WAIT and the thread stops storing; a recorded fault makes later exchanges return at once.
 #include "launchers.h"
 

@@ -358,7 +358,9 @@ size_t ezb_tp_comm_bytes(int B, int H);
  * it owns and hands the result to the others), 64 CTAs, plain peer stores, polls of local memory only, no flag and no
  * fence.  Every rank calls it on its stream behind the part that wrote the partial; when the kernel has finished,
  * buf holds the sum.  Ranks must make the same sequence of calls and alternate `which` (0: the sum after o_proj, 1:
- * the sum after down); B * H a multiple of 4; waits are bounded (EZB_TUNE_TP_WAIT_LIMIT_MS, then fault 0x201). */
+ * the sum after down); B * H a multiple of 4; waits are bounded (EZB_TUNE_TP_WAIT_LIMIT_MS, then fault 0x201).
+ * A communication buffer serves EITHER this entry point OR the fused entry points above, never both: the two keep
+ * separate epoch counters, and a cell left by one could carry the tag the other waits for. */
 int ezb_tp_allreduce_f32(void* buf, void* const* comm_bases_host, int world, int rank, int which, int B, int H,
                          ezb_stream_t stream);
 int ezb_tp_comm_alloc(size_t bytes, void** out_host);
