@@ -14,19 +14,23 @@ and KV caches (1.6 GB), so no step finds its inputs in L2.  The timed steps are
 enqueued directly behind ``--lead-in`` untimed ones (no host synchronisation in
 between), so with several ranks the processes' launch skew is absorbed before the
 first timed step and the clock samples describe the load the steps run under.
-At one GPU and batch 1 a step is ONE kernel launch (the whole layer as a
-persistent kernel); ``roofline`` then describes that kernel and
-``weight_streaming_leg`` the stand-alone GEMV kernel the other paths are built on.
+At batch 1 a step is ONE kernel launch per GPU (the whole layer as a persistent
+kernel; with several ranks both sums over ranks happen inside it, over NVLink peer
+memory); at one GPU ``roofline`` describes that kernel and ``weight_streaming_leg``
+the stand-alone GEMV kernel the other paths are built on.  Above batch 8 the ranks
+run three local parts with the library's own all-reduce kernel in between
+(``--exchange nccl`` puts NCCL there; ``--exchange-only`` times the sums alone).
 The process returns normally (exit hooks run); with several ranks the process
 group is destroyed under a guard timer.
 
 Further legs, all outside the timed region of ``value``:
-  e2e          the same layer through the operator API with the step's input in
-               pinned host memory: H2D of hidden, the op call, D2H of the output,
-               stream sync, every step (weights and KV cache are resident state).
-  roofline     the dominant kernel (the weight-streaming GEMV, 4 of the 5
-               launches and 96 % of the bytes) timed alone on a gate/up-sized
-               weight, against the measured HBM copy peak.
+  e2e          the same layer through the operator API with the step's input and
+               result in pinned host memory: a copy-in kernel, the layer (whose last
+               kernel stores into the pinned result buffer), stream sync and a host
+               read, every step (weights and KV cache are resident state).
+  roofline     one GPU, batch 1: the single-kernel layer, from the timed region
+               itself; otherwise the weight-streaming GEMV timed alone on a
+               gate/up-sized weight; both against the measured HBM copy peak.
   cpu_baseline the CPU oracle (torch on the host cores) on the same layer.
 ``--impl reference`` times that CPU path as its own arm.
 """
